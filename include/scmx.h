@@ -1,0 +1,157 @@
+/* scmx.h — C ABI of libscmx.so: the SC-MXFP4 W4A8 hot path on NVIDIA B200 (sm_100a).
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer.  Nothing is allocated or freed across the ABI: outputs and scratch
+ *     buffers are preallocated by the caller.
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it and nothing synchronises.
+ *   - Return value: 0 on success, a negative SCMX_E* code otherwise; scmx_last_error_string() describes the last
+ *     failure on the calling thread.  Shapes are validated on the host before anything is launched.
+ *   - Matrices are row-major; weights are [N, K] (out_features, in_features) with K contiguous, activations [M, K].
+ *   - "bf16" buffers hold bfloat16 bit patterns (uint16_t).
+ *   - Each declaration cites the reference interface (file:line inside shinyoungkang1/mxfp4-int8-m5) it replaces.
+ */
+#ifndef SCMX_H_
+#define SCMX_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SCMX_OK 0
+#define SCMX_EINVAL (-1)   /* bad shape / argument */
+#define SCMX_EFORMAT (-2)  /* unsupported weight format */
+#define SCMX_ECUDA (-3)    /* CUDA runtime / driver error (launch failure, tensor-map encode failure) */
+#define SCMX_EDEVICE (-4)  /* a bounded device-side wait ran out; the kernel returned early and set its status word */
+#define SCMX_ELIMIT (-5)   /* size beyond a documented fixed limit */
+
+/* Weight format: q[n,k] = +-code_mag[idx] * mult[bcode[n, k / block]]  (e2e/sc_format.py:26-41, `Format`). */
+typedef struct scmx_format {
+    int32_t block;        /* weights per block code along K; multiple of 8 */
+    int32_t bc_bits;      /* bits per block code: 1, 2, 4 or 8 */
+    int32_t n_mult;       /* entries used in mult[] (<= 2^bc_bits, <= 16) */
+    int32_t code_mag[8];  /* magnitude of element index 0..7 */
+    int32_t mult[16];     /* integer block multipliers; max(code_mag) * max(mult) <= 127 */
+} scmx_format;
+
+const char* scmx_last_error_string(void);
+int scmx_abi_version(void);
+
+/* ---- quantize / pack -------------------------------------------------------------------------------------- */
+
+/* SC-MXFP4 quantizer + packer of an [N,K] matrix (K % 128 == 0) in float64 arithmetic.
+ * Replaces sc_format.quantize (e2e/sc_format.py:105-111) = make_testcase.pack (sim/make_testcase.py:26-44) over
+ * mx_int8.block_exponents(rule="search") / constrain_spread / dequant_mx / embed_int8 (sim/mx_int8.py:39-109).
+ * w_dtype: 0 = float32, 1 = float64, 2 = bfloat16.  Outputs: codes u32 [N*K/8], bcodes u8 [N, K/128],
+ * wscale f32 [N] = 2^(E_lo-1); optional qw int8 [N,K] and row_exp int32 [N] = E_lo (may be NULL). */
+int scmx_quantize_sc_mxfp4(const void* w, int w_dtype, int64_t N, int64_t K, uint32_t* codes, uint8_t* bcodes,
+                           float* wscale, int8_t* qw, int32_t* row_exp, void* stream);
+
+/* Integer-exact format family quantizer in float32 arithmetic (row base search x per-block multiplier search).
+ * Replaces formats.quantize (sim/formats.py:64-107) + pack_format.pack_parts (e2e/pack_format.py:53-76).
+ * w float32 [N,K]; K/block <= 128 blocks per row and a multiple of 8.  Outputs as above; wscale = row base. */
+int scmx_quantize_family(const float* w, int64_t N, int64_t K, const scmx_format* fmt, int base_grid,
+                         uint32_t* codes, uint8_t* bcodes, float* wscale, int8_t* qw, void* stream);
+
+/* Packed codes -> INT8 operand [N,K].  Replaces sc_kernels.unpack_i8 (e2e/sc_kernels.py:34-50,480-483). */
+int scmx_unpack_i8(const uint32_t* codes, const uint8_t* bcodes, int64_t N, int64_t K, const scmx_format* fmt,
+                   int8_t* wq, void* stream);
+
+/* ---- activation row kernels --------------------------------------------------------------------------------- */
+
+/* Per-token symmetric INT8: s = amax/127, q = clamp(rint(x * (1/s))), rows [M, Mp) zeroed.
+ * Replaces sc_kernels.act_quant (e2e/sc_kernels.py:200-229,554-563).  x bf16 [M,K], K % 8 == 0. */
+int scmx_act_quant(const uint16_t* x, int64_t M, int64_t K, int64_t Mp, int8_t* xq, float* xs, void* stream);
+
+/* RMSNorm (weight nw bf16 [K]) then per-token INT8; xn (bf16 [Mp,K], may be NULL) receives the normalized rows.
+ * Replaces sc_kernels.rmsnorm_quant / rmsnorm_quant_n (e2e/sc_kernels.py:123-174,527-533,619-626). */
+int scmx_rmsnorm_quant(const uint16_t* x, const uint16_t* nw, float eps, int64_t M, int64_t K, int64_t Mp,
+                       int8_t* xq, float* xs, uint16_t* xn, void* stream);
+
+/* h = res + T(acc * xscale[m] * wscale[n]) from INT32 accumulators [Mp,N].
+ * Replaces sc_kernels.res_epilogue (e2e/sc_kernels.py:191-197,547-551). */
+int scmx_res_epilogue(const int32_t* acc, const float* xscale, const float* wscale, const uint16_t* res, int64_t Mp,
+                      int64_t N, uint16_t* h, void* stream);
+
+/* SwiGLU of the bf16-rounded gate | up halves of INT32 accumulators [Mp, 2F], then per-token INT8 -> [Mp,F].
+ * Replaces sc_kernels.swiglu_quant (e2e/sc_kernels.py:279-315,585-594). */
+int scmx_swiglu_quant(const int32_t* acc, const float* xscale, const float* wscale, int64_t Mp, int64_t F,
+                      int8_t* xq, float* xs, void* stream);
+
+/* Elementwise sc_swiglu(g, u) on bf16 arrays of n elements (e2e/sc_kernels.py:319-328); used by the exhaustive
+ * gate-value check the reference runs in e2e/test_sc_kernels.py:80-93. */
+int scmx_swiglu(const uint16_t* g, const uint16_t* u, int64_t n, uint16_t* out, void* stream);
+
+/* ---- dense prefill GEMM (tcgen05 kind::i8) -------------------------------------------------------------------- */
+
+/* out = epilogue(xq [M,K] . wq [N,K]^T).  epi 0: int32 [M,N] (mm_i8_i32, e2e/sc_kernels.py:53-71,486-495);
+ * epi 1: bf16 T((float(acc)*xscale[m])*wscale[n]); epi 2: bf16 T(res + T(...)); epi 3: SwiGLU of interleaved
+ * gate/up column groups -> bf16 [M, N/2]  (mm_epi, e2e/sc_kernels.py:79-115,498-508).
+ * K % 16 == 0, N % 32 == 0, all row pitches 16-byte aligned.  status: device int32[4], zero-filled by the caller
+ * once; non-zero afterwards means a bounded wait inside the kernel ran out (results invalid). */
+int scmx_mm_i8(const int8_t* xq, const int8_t* wq, int64_t M, int64_t N, int64_t K, int epi, const float* xscale,
+               const float* wscale, const uint16_t* res, void* out, int32_t* status, void* stream);
+
+/* Process-wide tuning hint for the N tile of the GEMM kernels: 0 = automatic, 128 or 256.  Counterpart of the
+ * module-level tile constants TM, TN, NSG, GROUP_M (e2e/sc_kernels.py:25) and the `tile=` arguments. */
+int scmx_set_gemm_tile(int bn);
+
+/* ---- grouped MoE GEMM ------------------------------------------------------------------------------------------- */
+
+/* Counting sort of M*topk assignments by expert with segment offsets and M-tile starts.
+ * Replaces sc_moe.route_sort (e2e/sc_moe.py:114-155).  inds int32 [M,topk]; outputs pos int32 [M*topk],
+ * tok int32 [M*topk + tm], esorted int32 [M*topk], off int32 [E+1], tstart int32 [E+1].  E <= 1024. */
+int scmx_route_sort(const int32_t* inds, int64_t M, int topk, int E, int tm, int32_t* pos, int32_t* tok,
+                    int32_t* esorted, int32_t* off, int32_t* tstart, void* stream);
+
+/* Router: softmax over E logits per token then the topk largest (ties to the lower expert id), scores not
+ * renormalised.  Replaces the MLX ops of e2e/fused_olmoe.py:216-220.  logits f32 [M,E]; inds int32 [M,topk];
+ * scores bf16 [M,topk]; scores_f32 (may be NULL) f32 [M,topk]. */
+int scmx_router_topk(const float* logits, int64_t M, int E, int topk, int32_t* inds, uint16_t* scores,
+                     float* scores_f32, void* stream);
+
+/* Row gather: dst_q[p] = xq[tok[p]] for p < rows_q, dst_s[p] = xs[tok[p]] for p < rows_s
+ * (the `xq[tok_p], xs[tok_p[:R]]` of e2e/fused_olmoe.py:230). */
+int scmx_gather_rows(const int8_t* xq, const float* xs, const int32_t* tok, int64_t rows_q, int64_t rows_s, int64_t K,
+                     int8_t* dst_q, float* dst_s, void* stream);
+
+/* Grouped GEMM over expert segments from pre-unpacked INT8 weights wq [E*N, K]; rows [off[e], off[e+1]) of xq use
+ * expert e.  Replaces sc_moe.moe_mm_i8 (e2e/sc_moe.py:97-107,188-200).  epi 0/1/3 as scmx_mm_i8 with
+ * wscale f32 [E,N].  tm must be 128 (the M tile of the kernel; off/tstart must come from route_sort with that tm). */
+int scmx_moe_mm_i8(const int8_t* xq, int64_t R, const int8_t* wq, const float* wscale, const int32_t* off,
+                   const int32_t* tstart, int E, int64_t N, int64_t K, int epi, const float* xscale, void* out,
+                   int tm, int32_t* status, void* stream);
+
+/* Grouped GEMM straight from packed weights: codes u32 [E, N*K/8], bcodes u8 [E, N, K*bc_bits/(8*block)].
+ * Replaces sc_moe.moe_mm (e2e/sc_moe.py:19-92,169-185).  Expert weights are decoded to INT8 in groups of
+ * `experts_per_pass` experts into `scratch` (caller-provided, >= 2 * experts_per_pass * N * K bytes, two rotating
+ * halves that stay L2-resident) and consumed by the tcgen05 grouped kernel. */
+int scmx_moe_mm(const int8_t* xq, int64_t R, const uint32_t* codes, const uint8_t* bcodes, const float* wscale,
+                const int32_t* off, const int32_t* tstart, int E, int64_t N, int64_t K, const scmx_format* fmt, int epi,
+                const float* xscale, void* out, int tm, int experts_per_pass, int8_t* scratch, int64_t scratch_bytes,
+                int32_t* status, void* stream);
+
+/* Weighted sequential-bf16 sum of the topk expert rows + residual (+ next RMSNorm + INT8 when quant != 0).
+ * Replaces fused_olmoe.moe_combine (e2e/fused_olmoe.py:45-97).  y bf16 [R,K], pos int32 [M*topk], scores bf16
+ * [M,topk], res bf16 [Mp,K] -> h bf16 [Mp,K], xq int8 [Mp,K], xs f32 [Mp]. */
+int scmx_moe_combine(const uint16_t* y, const int32_t* pos, const uint16_t* scores, const uint16_t* res,
+                     const uint16_t* nw, float eps, int64_t M, int64_t Mp, int64_t K, int topk, int quant,
+                     uint16_t* h, int8_t* xq, float* xs, void* stream);
+
+/* ---- batch-1 decode GEMV ------------------------------------------------------------------------------------------ */
+
+/* y[slot, n] = epilogue(xscale * wscale[n] * sum_k xq[k] q[n,k]) reading the packed codes directly.
+ * Replaces sc_decode.gemv (e2e/sc_decode.py:19-183,208-238) with pro = 0.  n_slots = 1 and eidx = NULL: dense.
+ * MoE: slot j uses expert eidx[j] (or `shared` for slot n_routed when shared >= 0) and input row j * xstride.
+ * epi 1/2/3 as scmx_mm_i8 (epi 2 reads res bf16 [N]); epi 0 writes the exact int32 totals.
+ * K % 128 == 0, N % 4 == 0.  pdl != 0 launches with programmatic stream serialization so the weight loads of
+ * this call overlap the tail of the previous kernel on the stream. */
+int scmx_gemv(const int8_t* xq, const float* xscale, const uint32_t* codes, const uint8_t* bcodes, const float* wscale,
+              int64_t N, int64_t K, const scmx_format* fmt, int epi, const uint16_t* res, const int32_t* eidx,
+              int n_routed, int shared, int xstride, void* out, int pdl, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SCMX_H_ */

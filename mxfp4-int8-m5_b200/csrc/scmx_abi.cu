@@ -1,0 +1,52 @@
+// Error reporting, ABI version and weight-format validation shared by every entry point of libscmx.
+#include <stdarg.h>
+#include <string.h>
+#include "scmx_common.cuh"
+
+namespace scmx {
+
+static thread_local char g_err[512] = "no error";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int make_dev_format(const scmx_format* fmt, DevFormat* out) {
+    SCMX_REQUIRE(fmt != nullptr, SCMX_EINVAL, "format is NULL");
+    SCMX_REQUIRE(fmt->block >= 8 && fmt->block % 8 == 0, SCMX_EFORMAT, "format.block=%d must be a multiple of 8",
+                 fmt->block);
+    SCMX_REQUIRE(fmt->bc_bits == 1 || fmt->bc_bits == 2 || fmt->bc_bits == 4 || fmt->bc_bits == 8, SCMX_EFORMAT,
+                 "format.bc_bits=%d must be 1, 2, 4 or 8", fmt->bc_bits);
+    SCMX_REQUIRE(fmt->n_mult >= 1 && fmt->n_mult <= 16 && fmt->n_mult <= (1 << fmt->bc_bits), SCMX_EFORMAT,
+                 "format.n_mult=%d does not fit %d-bit block codes (max 16)", fmt->n_mult, fmt->bc_bits);
+    int cmax = 0, mmax = 0;
+    for (int i = 0; i < 8; ++i) {
+        SCMX_REQUIRE(fmt->code_mag[i] >= 0, SCMX_EFORMAT, "negative code magnitude");
+        cmax = fmt->code_mag[i] > cmax ? fmt->code_mag[i] : cmax;
+    }
+    for (int i = 0; i < fmt->n_mult; ++i) {
+        SCMX_REQUIRE(fmt->mult[i] >= 1, SCMX_EFORMAT, "block multiplier must be >= 1");
+        mmax = fmt->mult[i] > mmax ? fmt->mult[i] : mmax;
+    }
+    SCMX_REQUIRE(cmax * mmax <= 127, SCMX_EFORMAT, "max(code_mag) * max(mult) = %d does not fit INT8", cmax * mmax);
+    memset(out, 0, sizeof(*out));
+    for (int i = 0; i < 4; ++i) {
+        out->mag_lo |= (uint32_t)fmt->code_mag[i] << (8 * i);
+        out->mag_hi |= (uint32_t)fmt->code_mag[4 + i] << (8 * i);
+        out->neg_lo |= ((uint32_t)(-fmt->code_mag[i]) & 0xFFu) << (8 * i);
+        out->neg_hi |= ((uint32_t)(-fmt->code_mag[4 + i]) & 0xFFu) << (8 * i);
+    }
+    for (int i = 0; i < 16; ++i) out->mult4[i / 4] |= (uint32_t)(i < fmt->n_mult ? fmt->mult[i] : 1) << (8 * (i % 4));
+    out->block = fmt->block;
+    out->bc_bits = fmt->bc_bits;
+    out->blocks_per_byte = 8 / fmt->bc_bits;
+    return SCMX_OK;
+}
+
+}  // namespace scmx
+
+extern "C" const char* scmx_last_error_string(void) { return scmx::g_err; }
+extern "C" int scmx_abi_version(void) { return 1; }

@@ -1,0 +1,555 @@
+// INT8 x INT8 -> INT32 GEMM for the W4A8 prefill path on sm_100a: tcgen05.mma kind::i8 with the accumulators in
+// tensor memory, operands staged in shared memory by TMA, and the scaling epilogue fused.  One kernel serves the
+// dense GEMM (xq [M,K] . wq [N,K]^T) and the grouped mixture-of-experts GEMM (row segments per expert).
+//
+// Persistent, warp-specialised CTA (one per SM, 192 threads):
+//   warp 0      TMA producer: for every K block of 128 bytes loads a 128 x 128 tile of A and a BN x 128 tile of B into
+//               one of STAGES shared-memory stages (128-byte swizzle), completing on the stage's "full" mbarrier.
+//   warp 1      MMA issuer: one elected thread issues 4 tcgen05.mma (M128 x N BN x K32) per stage into one of two
+//               TMEM accumulators (BN columns each), tcgen05.commit frees the stage ("empty" mbarrier) and, after the
+//               last K block, publishes the accumulator ("tmem_full").  Also owns TMEM allocation.
+//   warps 2..5  epilogue: each warp reads its 32 TMEM lanes with tcgen05.ld (32 columns at a time), applies
+//               T((float(acc) * xscale[m]) * wscale[n]) (+ residual, or SwiGLU on interleaved gate/up columns) and
+//               stores; then releases the accumulator ("tmem_empty") so the next tile's MMAs overlap this epilogue.
+//
+// Tiles are visited m-fastest so that concurrently running CTAs share B tiles through L2.  No cluster launch, no
+// multicast: every CTA fetches its own tiles.  Every mbarrier wait is bounded by a wall-clock limit; when it runs
+// out the kernel records where in `status`, lets in-flight copies land, frees its TMEM and returns.
+#include <cuda.h>
+#include "scmx_common.cuh"
+
+namespace scmx {
+
+constexpr int BM = 128;          // rows of A per tile = TMEM lanes
+constexpr int BK = 128;          // K bytes per stage = one 128-byte swizzle row
+constexpr int UMMA_K = 32;       // K per tcgen05.mma kind::i8
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // 2 s
+
+struct GemmArgs {
+    int M, N, K;                 // dense: rows of xq; grouped: total sorted rows R
+    int epi;
+    const float* xscale;
+    const float* wscale;
+    const uint16_t* res;
+    void* out;
+    const int32_t* off;          // grouped only (E > 0)
+    const int32_t* tstart;
+    int E;
+    int e_begin, e_end;          // grouped: experts handled by this launch; B rows are relative to e_begin
+    int32_t* status;
+};
+
+// ---- PTX wrappers ----------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: 0 = barrier phase completed, 1 = the time limit ran out, 2 = another role of this CTA gave up first.
+__device__ __forceinline__ int mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return 0;
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return 0;
+        if (*abort_flag) return 2;
+        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; return 1; }
+    }
+}
+// Barrier among the 128 epilogue threads only (named barrier 1).
+__device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]^T, INT8 operands, INT32 accumulate.
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrive on an mbarrier once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives lane (base + i), registers = columns.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, stored with the 128-byte swizzle:
+// start address >> 4 in bits [0,14); leading byte offset (unused for swizzled K-major) = 1 in [16,30);
+// stride byte offset = 1024 (eight rows) >> 4 in [32,46); descriptor version 1 in [46,48); layout 2 = SWIZZLE_128B
+// in [61,64).  Advancing K by 32 bytes inside the swizzle row adds 2 to the start-address field.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor, kind::i8: D = S32 (2 at [4,6)), A and B signed INT8 (1 at [7,10) and [10,13)), both K-major
+// (bits 15, 16 zero), N >> 3 at [17,23), M >> 4 at [24,29).
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// ---- tile scheduler ---------------------------------------------------------------------------------------------------
+struct Tile {
+    int row0;        // first A row (TMA coordinate; also first output row)
+    int row_end;     // rows >= row_end are not stored
+    int n0;          // first output column
+    int brow;        // first B row (TMA coordinate)
+    int wrow;        // index of wscale[n0]
+};
+
+template <int BN>
+__device__ __forceinline__ int num_tiles(const GemmArgs& a, int& tiles_m, int& slot0) {
+    const int tiles_n = (a.N + BN - 1) / BN;
+    if (a.E == 0) {
+        tiles_m = (a.M + BM - 1) / BM;
+        slot0 = 0;
+    } else {
+        slot0 = a.tstart[a.e_begin];
+        tiles_m = a.tstart[a.e_end] - slot0;
+    }
+    return tiles_m * tiles_n;
+}
+
+template <int BN>
+__device__ __forceinline__ Tile get_tile(const GemmArgs& a, int t, int tiles_m, int slot0) {
+    Tile tl;
+    const int mt = t % tiles_m, nt = t / tiles_m;
+    tl.n0 = nt * BN;
+    if (a.E == 0) {
+        tl.row0 = mt * BM;
+        tl.row_end = a.M;
+        tl.brow = tl.n0;
+        tl.wrow = tl.n0;
+    } else {
+        const int s = slot0 + mt;
+        int lo = a.e_begin, hi = a.e_end;      // largest e in [e_begin, e_end) with tstart[e] <= s
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (a.tstart[mid] <= s) lo = mid; else hi = mid;
+        }
+        tl.row0 = a.off[lo] + (s - a.tstart[lo]) * BM;
+        tl.row_end = a.off[lo + 1];
+        tl.brow = (lo - a.e_begin) * a.N + tl.n0;
+        tl.wrow = lo * a.N + tl.n0;
+    }
+    return tl;
+}
+
+// ---- the kernel -----------------------------------------------------------------------------------------------------------
+template <int BN, int STAGES>
+struct Smem {
+    static constexpr int A_BYTES = BM * BK;
+    static constexpr int B_BYTES = BN * BK;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int BAR_OFF = STAGES * STAGE_BYTES;                 // full[STAGES], empty[STAGES], tfull[2], tempty[2]
+    static constexpr int MISC_OFF = BAR_OFF + 8 * (2 * STAGES + 4);      // tmem base (u32), abort flag (int)
+    static constexpr int WS_OFF = MISC_OFF + 16;                         // wscale staging [2][BN] float
+    static constexpr int TOTAL = WS_OFF + 2 * BN * 4 + 1024;             // + slack for 1024-byte alignment
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(192, 1) gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                          const __grid_constant__ CUtensorMap tmB, const GemmArgs a) {
+    using L = Smem<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bar_full = sbase + L::BAR_OFF, bar_empty = bar_full + 8 * STAGES;
+    const uint32_t bar_tfull = bar_empty + 8 * STAGES, bar_tempty = bar_tfull + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::MISC_OFF);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::MISC_OFF + 4);
+    float* ws_stage = reinterpret_cast<float*>(smem + L::WS_OFF);
+    constexpr uint32_t TMEM_COLS = 2 * BN;     // 256 or 512: a power of two >= 32
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar_tfull + 8 * i, 1);
+            mbar_init(bar_tempty + 8 * i, 4);      // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    int tiles_m, slot0;
+    const int total = num_tiles<BN>(a, tiles_m, slot0);
+    const int num_kb = (a.K + BK - 1) / BK;
+    int fail = 0;
+
+    if (warp == 0) {
+        // ------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int t = blockIdx.x; t < total && fail == 0; t += gridDim.x) {
+                const Tile tl = get_tile<BN>(a, t, tiles_m, slot0);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (int w = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag)) { fail = w == 1 ? 1 : -1; break; }
+                    const uint32_t sa = sbase + stage * L::STAGE_BYTES, sb = sa + L::A_BYTES;
+                    mbar_expect_tx(bar_full + 8 * stage, L::STAGE_BYTES);
+                    tma_load_2d(sa, &tmA, kb * BK, tl.row0, bar_full + 8 * stage);
+                    tma_load_2d(sb, &tmB, kb * BK, tl.brow, bar_full + 8 * stage);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(BM, BN);
+            int stage = 0;
+            uint32_t phase = 0, acc = 0, acc_phase = 0;
+            for (int t = blockIdx.x; t < total && fail == 0; t += gridDim.x) {
+                if (int w = mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag)) { fail = w == 1 ? 2 : -1; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (int w = mbar_wait(bar_full + 8 * stage, phase, abort_flag)) { fail = w == 1 ? 3 : -1; break; }
+                    tc_fence_after();
+                    const uint32_t sa = sbase + stage * L::STAGE_BYTES, sb = sa + L::A_BYTES;
+                    const uint64_t da = umma_desc(sa), db = umma_desc(sb);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_i8(d_tmem, da + (uint64_t)(k * (UMMA_K >> 4)), db + (uint64_t)(k * (UMMA_K >> 4)), idesc,
+                                (kb | k) != 0 ? 1u : 0u);
+                    umma_commit(bar_empty + 8 * stage);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (fail) break;
+                umma_commit(bar_tfull + 8 * acc);
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1;
+            }
+        }
+    } else {
+        // ------------------------------------------------ epilogue warps 2..5; TMEM lane quarter = warp % 4
+        const int q = warp & 3;
+        const int et = threadIdx.x - 64;          // 0..127 among the epilogue threads
+        uint32_t acc = 0, acc_phase = 0;
+        for (int t = blockIdx.x; t < total && fail == 0; t += gridDim.x) {
+            const Tile tl = get_tile<BN>(a, t, tiles_m, slot0);
+            float* ws = ws_stage + acc * BN;
+            if (a.epi != 0) {
+                for (int i = et; i < BN; i += 128) ws[i] = (tl.n0 + i < a.N) ? a.wscale[tl.wrow + i] : 0.0f;
+            }
+            if (int w = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) fail = w == 1 ? 4 : -1;
+            // the 128 epilogue threads agree on giving up (and see the staged scales) before anyone touches TMEM
+            epilogue_bar();
+            if (*abort_flag) { if (!fail) fail = -1; break; }
+            tc_fence_after();
+            const int row = tl.row0 + 32 * q + lane;
+            const bool row_ok = row < tl.row_end;
+            const float xs = (a.epi != 0 && row_ok) ? a.xscale[row] : 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + acc * BN + c * 32 + ((uint32_t)(32 * q) << 16), r);
+                tmem_ld_wait();
+                const int n = tl.n0 + c * 32;
+                if (!row_ok || n >= a.N) continue;
+                if (a.epi == 0) {
+                    uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<int32_t*>(a.out) + (size_t)row * a.N + n);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) o[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                } else if (a.epi == 3) {
+                    uint32_t pk[8];
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) {
+                        const float4 w4 = *reinterpret_cast<const float4*>(ws + c * 32 + 4 * g);
+                        const float g0 = scale_acc((int)r[4 * g], xs, w4.x), g1 = scale_acc((int)r[4 * g + 1], xs, w4.y);
+                        const float u0 = scale_acc((int)r[4 * g + 2], xs, w4.z), u1 = scale_acc((int)r[4 * g + 3], xs, w4.w);
+                        pk[g] = f32_to_bf16(swiglu_bf16(g0, u0)) | ((uint32_t)f32_to_bf16(swiglu_bf16(g1, u1)) << 16);
+                    }
+                    uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(a.out) + (size_t)row * (a.N / 2) + n / 2);
+                    o[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    o[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                } else {
+                    uint32_t pk[16];
+                    uint32_t rr[16];
+                    if (a.epi == 2) {
+                        const uint4* rp = reinterpret_cast<const uint4*>(a.res + (size_t)row * a.N + n);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint4 v = rp[j];
+                            rr[4 * j] = v.x; rr[4 * j + 1] = v.y; rr[4 * j + 2] = v.z; rr[4 * j + 3] = v.w;
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const float2 w2 = *reinterpret_cast<const float2*>(ws + c * 32 + 2 * j);
+                        float y0 = scale_acc((int)r[2 * j], xs, w2.x), y1 = scale_acc((int)r[2 * j + 1], xs, w2.y);
+                        if (a.epi == 2) {
+                            y0 = __fadd_rn(__uint_as_float(rr[j] << 16), y0);
+                            y1 = __fadd_rn(__uint_as_float(rr[j] & 0xFFFF0000u), y1);
+                        }
+                        pk[j] = f32_to_bf16(y0) | ((uint32_t)f32_to_bf16(y1) << 16);
+                    }
+                    uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(a.out) + (size_t)row * a.N + n);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) o[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1;
+        }
+    }
+
+    // ---- shutdown: record a failed wait, let in-flight copies land, free TMEM
+    // status[0]: 1 producer waited for a free stage, 2 MMA waited for a free accumulator, 3 MMA waited for operands,
+    // 4 epilogue waited for an accumulator; status[1] CTA, status[2] thread.  Secondary give-ups (fail < 0) are not recorded.
+    if (fail > 0) {
+        if (atomicCAS(a.status, 0, fail) == 0) {
+            a.status[1] = blockIdx.x;
+            a.status[2] = threadIdx.x;
+        }
+    }
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (*abort_flag) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);   // 0.2 ms for outstanding TMA writes
+        __syncthreads();
+    }
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+
+// ---- host side ------------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// INT8 matrix [rows, K] row-major, box = 128 bytes of K x box_rows rows, 128-byte swizzle, zero fill outside.
+static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    SCMX_REQUIRE(fn != nullptr, SCMX_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)K};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    SCMX_REQUIRE(r == CUDA_SUCCESS, SCMX_ECUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rows=%lld K=%lld)", (int)r,
+                 (long long)rows, (long long)K);
+    return SCMX_OK;
+}
+
+static int g_bn_override = 0;      // 0 = choose per problem
+static int g_num_sms = 0;
+
+static int num_sms() {
+    if (!g_num_sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (g_num_sms <= 0) g_num_sms = 148;
+    }
+    return g_num_sms;
+}
+
+template <int BN, int STAGES>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& a, int grid, cudaStream_t st) {
+    using L = Smem<BN, STAGES>;
+    static bool configured = false;
+    if (!configured) {
+        SCMX_CUDA_OK(cudaFuncSetAttribute(gemm_i8_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+        configured = true;
+    }
+    gemm_i8_kernel<BN, STAGES><<<grid, 192, L::TOTAL, st>>>(tmA, tmB, a);
+    SCMX_LAUNCH_OK("gemm_i8_kernel");
+    return SCMX_OK;
+}
+
+static int run_gemm(const int8_t* xq, int64_t a_rows, const int8_t* wq, int64_t b_rows, GemmArgs& a, cudaStream_t st) {
+    int bn = g_bn_override ? g_bn_override : (a.N >= 256 ? 256 : 128);
+    CUtensorMap tmA, tmB;
+    int rc = make_map(&tmA, xq, a_rows, a.K, BM);
+    if (rc) return rc;
+    rc = make_map(&tmB, wq, b_rows, a.K, bn);
+    if (rc) return rc;
+    int grid = num_sms();
+    if (a.E == 0) {
+        const int64_t tiles = ((a.M + BM - 1) / BM) * (int64_t)((a.N + bn - 1) / bn);
+        if (tiles < grid) grid = (int)tiles;
+    }
+    if (bn == 256) return launch_gemm<256, 4>(tmA, tmB, a, grid, st);
+    return launch_gemm<128, 6>(tmA, tmB, a, grid, st);
+}
+
+static int check_common(const char* who, int64_t N, int64_t K, int epi, const float* xscale, const float* wscale,
+                        const void* out, const int32_t* status) {
+    SCMX_REQUIRE(N > 0 && N % 32 == 0 && N < (1ll << 30), SCMX_EINVAL, "%s: N=%lld must be a positive multiple of 32", who,
+                 (long long)N);
+    SCMX_REQUIRE(K > 0 && K % 16 == 0 && K < (1ll << 30), SCMX_EINVAL, "%s: K=%lld must be a positive multiple of 16", who,
+                 (long long)K);
+    SCMX_REQUIRE(epi >= 0 && epi <= 3, SCMX_EINVAL, "%s: epi=%d outside 0..3", who, epi);
+    SCMX_REQUIRE(epi == 0 || (xscale && wscale), SCMX_EINVAL, "%s: epi %d needs xscale and wscale", who, epi);
+    SCMX_REQUIRE(out && status, SCMX_EINVAL, "%s: out / status is NULL", who);
+    SCMX_REQUIRE((reinterpret_cast<uintptr_t>(out) & 15) == 0, SCMX_EINVAL, "%s: out must be 16-byte aligned", who);
+    SCMX_REQUIRE(epi != 3 || N % 64 == 0, SCMX_EINVAL, "%s: epi 3 needs N %% 64 == 0", who);
+    return SCMX_OK;
+}
+
+}  // namespace scmx
+
+using namespace scmx;
+
+extern "C" int scmx_set_gemm_tile(int bn) {
+    SCMX_REQUIRE(bn == 0 || bn == 128 || bn == 256, SCMX_EINVAL, "set_gemm_tile: bn=%d (0 = automatic, 128 or 256)", bn);
+    g_bn_override = bn;
+    return SCMX_OK;
+}
+
+extern "C" int scmx_mm_i8(const int8_t* xq, const int8_t* wq, int64_t M, int64_t N, int64_t K, int epi, const float* xscale,
+                          const float* wscale, const uint16_t* res, void* out, int32_t* status, void* stream) {
+    int rc = check_common("mm_i8", N, K, epi, xscale, wscale, out, status);
+    if (rc) return rc;
+    SCMX_REQUIRE(M >= 0 && M < (1ll << 30), SCMX_EINVAL, "mm_i8: M=%lld out of range", (long long)M);
+    SCMX_REQUIRE(epi != 2 || res, SCMX_EINVAL, "mm_i8: epi 2 needs res");
+    SCMX_REQUIRE((reinterpret_cast<uintptr_t>(xq) & 15) == 0 && (reinterpret_cast<uintptr_t>(wq) & 15) == 0 &&
+                     (!res || (reinterpret_cast<uintptr_t>(res) & 15) == 0),
+                 SCMX_EINVAL, "mm_i8: xq, wq and res must be 16-byte aligned");
+    if (M == 0) return SCMX_OK;
+    GemmArgs a = {};
+    a.M = (int)M; a.N = (int)N; a.K = (int)K; a.epi = epi; a.xscale = xscale; a.wscale = wscale; a.res = res; a.out = out;
+    a.status = status;
+    return run_gemm(xq, M, wq, N, a, (cudaStream_t)stream);
+}
+
+extern "C" int scmx_moe_mm_i8(const int8_t* xq, int64_t R, const int8_t* wq, const float* wscale, const int32_t* off,
+                              const int32_t* tstart, int E, int64_t N, int64_t K, int epi, const float* xscale, void* out,
+                              int tm, int32_t* status, void* stream) {
+    int rc = check_common("moe_mm_i8", N, K, epi, xscale, wscale, out, status);
+    if (rc) return rc;
+    SCMX_REQUIRE(epi != 2, SCMX_EINVAL, "moe_mm_i8: epi must be 0, 1 or 3");
+    SCMX_REQUIRE(tm == BM, SCMX_EINVAL, "moe_mm_i8: tm=%d, the kernel's M tile is %d (pass tm=%d to route_sort)", tm, BM, BM);
+    SCMX_REQUIRE(E >= 1 && E <= 65536 && R >= 0 && R < (1ll << 30) && off && tstart, SCMX_EINVAL, "moe_mm_i8: bad E / R / offsets");
+    SCMX_REQUIRE((int64_t)E * N < (1ll << 31), SCMX_ELIMIT, "moe_mm_i8: E*N too large");
+    if (R == 0) return SCMX_OK;
+    GemmArgs a = {};
+    a.M = (int)R; a.N = (int)N; a.K = (int)K; a.epi = epi; a.xscale = xscale; a.wscale = wscale; a.out = out;
+    a.off = off; a.tstart = tstart; a.E = E; a.e_begin = 0; a.e_end = E; a.status = status;
+    return run_gemm(xq, R, wq, (int64_t)E * N, a, (cudaStream_t)stream);
+}
+
+extern "C" int scmx_moe_mm(const int8_t* xq, int64_t R, const uint32_t* codes, const uint8_t* bcodes, const float* wscale,
+                           const int32_t* off, const int32_t* tstart, int E, int64_t N, int64_t K, const scmx_format* fmt,
+                           int epi, const float* xscale, void* out, int tm, int experts_per_pass, int8_t* scratch,
+                           int64_t scratch_bytes, int32_t* status, void* stream) {
+    int rc = check_common("moe_mm", N, K, epi, xscale, wscale, out, status);
+    if (rc) return rc;
+    DevFormat f;
+    rc = make_dev_format(fmt, &f);
+    if (rc) return rc;
+    SCMX_REQUIRE(epi != 2, SCMX_EINVAL, "moe_mm: epi must be 0, 1 or 3");
+    SCMX_REQUIRE(tm == BM, SCMX_EINVAL, "moe_mm: tm=%d, the kernel's M tile is %d (pass tm=%d to route_sort)", tm, BM, BM);
+    SCMX_REQUIRE(E >= 1 && E <= 65536 && R >= 0 && R < (1ll << 30) && off && tstart, SCMX_EINVAL, "moe_mm: bad E / R / offsets");
+    SCMX_REQUIRE(experts_per_pass >= 1, SCMX_EINVAL, "moe_mm: experts_per_pass must be >= 1");
+    const int64_t half = (int64_t)experts_per_pass * N * K;
+    SCMX_REQUIRE(scratch && scratch_bytes >= 2 * half, SCMX_EINVAL,
+                 "moe_mm: scratch of %lld bytes is smaller than 2 * experts_per_pass * N * K = %lld", (long long)scratch_bytes,
+                 (long long)(2 * half));
+    SCMX_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & 1023) == 0, SCMX_EINVAL, "moe_mm: scratch must be 1024-byte aligned");
+    if (R == 0) return SCMX_OK;
+    const int64_t wpe = N * K / 8;                              // code words per expert
+    const int64_t bpe = N * (K / (f.block * f.blocks_per_byte));  // block-code bytes per expert
+    int pass = 0;
+    for (int e0 = 0; e0 < E; e0 += experts_per_pass, ++pass) {
+        const int e1 = e0 + experts_per_pass < E ? e0 + experts_per_pass : E;
+        int8_t* buf = scratch + (pass & 1) * half;
+        rc = scmx_unpack_i8(codes + e0 * wpe, bcodes + e0 * bpe, (int64_t)(e1 - e0) * N, K, fmt, buf, stream);
+        if (rc) return rc;
+        GemmArgs a = {};
+        a.M = (int)R; a.N = (int)N; a.K = (int)K; a.epi = epi; a.xscale = xscale; a.wscale = wscale; a.out = out;
+        a.off = off; a.tstart = tstart; a.E = E; a.e_begin = e0; a.e_end = e1; a.status = status;
+        rc = run_gemm(xq, R, buf, (int64_t)(e1 - e0) * N, a, (cudaStream_t)stream);
+        if (rc) return rc;
+    }
+    return SCMX_OK;
+}

@@ -1,0 +1,248 @@
+// Batch-1 W4A8 decode GEMV reading the packed 4-bit codes directly.  HBM-bound: no tensor cores.
+//
+// A warp owns 4 consecutive output rows and a slice of K.  Per step a lane streams 16 bytes (32 codes) of each of
+// its rows with one 128-bit load; all loads of a warp (4 rows x STEPS steps) are issued before any is consumed so
+// that enough bytes are in flight to cover DRAM latency.  Codes are expanded in registers: a byte permute looks up
+// the magnitudes of four codes at once, a second byte permute picks x or -x per code according to the sign bit,
+// and DP4A accumulates; the per-block integer multiplier is applied to the block sum.  Lane totals are exact INT32
+// and are reduced with shuffles, across K-splits through shared memory.  The epilogue is the GEMM's
+// (scale, + residual, SwiGLU), so GEMV and GEMM produce the same bits.
+//
+// With programmatic dependent launch the weight loads are issued before griddepcontrol.wait: they do not depend on
+// the previous kernel, so they overlap its tail; activations, scales and expert ids are read after the wait.
+#include "scmx_common.cuh"
+
+namespace scmx {
+
+struct GemvArgs {
+    const int8_t* xq;
+    const float* xscale;
+    const uint32_t* codes;
+    const uint8_t* bcodes;
+    const float* wscale;
+    const uint16_t* res;
+    const int32_t* eidx;
+    void* out;
+    int N, K, epi, n_routed, shared, xstride;
+    int sk;            // K splits (warps per row group)
+    int rg;            // row groups per CTA
+    int bc_row_bytes;
+    DevFormat f;
+};
+
+__device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// per-byte negation of four INT8 in -127..127
+__device__ __forceinline__ uint32_t neg4(uint32_t x) { return __vneg4(x); }
+
+template <int STEPS, bool B32>
+__global__ void __launch_bounds__(256) gemv_kernel(const GemvArgs a) {
+    __shared__ int part[8 * 4];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int ks = wid % a.sk, rgi = wid / a.sk;
+    const int n0 = (blockIdx.x * a.rg + rgi) * 4;
+    const int slot = blockIdx.y;
+    const bool rows_ok = n0 < a.N;
+    const int K = a.K, wpr = K / 8;
+
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    int ex = 0;
+    if (a.eidx) {   // expert ids come from the previous kernel: wait before anything else
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        ex = (a.shared >= 0 && slot == a.n_routed) ? a.shared : a.eidx[slot];
+    }
+    const uint32_t* codes = a.codes + (size_t)ex * a.N * wpr;
+    const uint8_t* bcodes = a.bcodes + (size_t)ex * a.N * a.bc_row_bytes;
+
+    uint4 w[STEPS][4];
+    uint32_t bc[STEPS][4];
+    int k0s[STEPS];
+#pragma unroll
+    for (int s = 0; s < STEPS; ++s) {
+        const int k0 = ((ks + s * a.sk) * 32 + lane) * 32;
+        k0s[s] = (rows_ok && k0 < K) ? k0 : -1;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            w[s][r] = make_uint4(0, 0, 0, 0);
+            bc[s][r] = 0;
+            if (k0s[s] >= 0) {
+                w[s][r] = ldg_stream(reinterpret_cast<const uint4*>(codes + (size_t)(n0 + r) * wpr + k0 / 8));
+                const uint8_t* rb = bcodes + (size_t)(n0 + r) * a.bc_row_bytes;
+                if (B32) {
+                    const int blk = k0 / a.f.block;
+                    bc[s][r] = rb[blk / a.f.blocks_per_byte];
+                } else {
+                    // the lane's 32 codes span 32/block blocks whose codes fit one aligned 32-bit field
+                    const int bit0 = (k0 / a.f.block) * a.f.bc_bits;
+                    uint32_t v = 0;
+                    const int nbytes = (32 / a.f.block * a.f.bc_bits + 7) / 8;
+                    for (int i = 0; i < nbytes; ++i) v |= (uint32_t)rb[bit0 / 8 + i] << (8 * i);
+                    bc[s][r] = v >> (bit0 % 8);
+                }
+            }
+        }
+    }
+    if (!a.eidx) asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    const int8_t* xq = a.xq + (size_t)slot * a.xstride * K;
+    int tot[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int s = 0; s < STEPS; ++s) {
+        if (k0s[s] < 0) continue;
+        const uint4 xa = *reinterpret_cast<const uint4*>(xq + k0s[s]);
+        const uint4 xb = *reinterpret_cast<const uint4*>(xq + k0s[s] + 16);
+        const uint32_t x[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+        uint32_t xn[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) xn[j] = neg4(x[j]);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const uint32_t ww[4] = {w[s][r].x, w[s][r].y, w[s][r].z, w[s][r].w};
+            if (B32) {
+                const int blk = k0s[s] / a.f.block;
+                const uint32_t code = (bc[s][r] >> (a.f.bc_bits * (blk % a.f.blocks_per_byte))) & ((1u << a.f.bc_bits) - 1u);
+                int bs = 0;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t sel = ww[j] & 0x77777777u;
+                    const uint32_t ssel = ((ww[j] >> 1) & 0x44444444u) | 0x32103210u;
+                    bs = __dp4a((int)__byte_perm(x[2 * j], xn[2 * j], ssel), (int)__byte_perm(a.f.mag_lo, a.f.mag_hi, sel), bs);
+                    bs = __dp4a((int)__byte_perm(x[2 * j + 1], xn[2 * j + 1], ssel >> 16),
+                                (int)__byte_perm(a.f.mag_lo, a.f.mag_hi, sel >> 16), bs);
+                }
+                tot[r] += bs * (int)fmt_mult(a.f, code);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int bi = (8 * j) / a.f.block;   // block index inside the lane's 32 codes
+                    const uint32_t code = (bc[s][r] >> (a.f.bc_bits * bi)) & ((1u << a.f.bc_bits) - 1u);
+                    const uint32_t sel = ww[j] & 0x77777777u;
+                    const uint32_t ssel = ((ww[j] >> 1) & 0x44444444u) | 0x32103210u;
+                    int bs = __dp4a((int)__byte_perm(x[2 * j], xn[2 * j], ssel), (int)__byte_perm(a.f.mag_lo, a.f.mag_hi, sel), 0);
+                    bs = __dp4a((int)__byte_perm(x[2 * j + 1], xn[2 * j + 1], ssel >> 16),
+                                (int)__byte_perm(a.f.mag_lo, a.f.mag_hi, sel >> 16), bs);
+                    tot[r] += bs * (int)fmt_mult(a.f, code);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) tot[r] = warp_sum(tot[r]);
+    if (a.sk > 1) {
+        if (lane == 0) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r) part[wid * 4 + r] = tot[r];
+        }
+        __syncthreads();
+        if (ks != 0) return;
+        for (int j = 1; j < a.sk; ++j) {
+#pragma unroll
+            for (int r = 0; r < 4; ++r) tot[r] += part[(wid + j) * 4 + r];
+        }
+    }
+    if (lane != 0 || !rows_ok) return;
+    const float* ws = a.wscale + (size_t)ex * a.N + n0;
+    if (a.epi == 0) {
+        int32_t* o = reinterpret_cast<int32_t*>(a.out) + (size_t)slot * a.N + n0;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) o[r] = tot[r];
+        return;
+    }
+    const float xs = a.xscale[(size_t)slot * a.xstride];
+    float y[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) y[r] = scale_acc(tot[r], xs, ws[r]);
+    uint16_t* out = reinterpret_cast<uint16_t*>(a.out);
+    if (a.epi == 1) {
+        uint16_t* o = out + (size_t)slot * a.N + n0;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) o[r] = f32_to_bf16(y[r]);
+    } else if (a.epi == 2) {
+        uint16_t* o = out + (size_t)slot * a.N + n0;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) o[r] = f32_to_bf16(__fadd_rn(bf16_to_f32(a.res[n0 + r]), y[r]));
+    } else {
+        uint16_t* o = out + (size_t)slot * (a.N / 2) + n0 / 2;
+        o[0] = f32_to_bf16(swiglu_bf16(y[0], y[2]));
+        o[1] = f32_to_bf16(swiglu_bf16(y[1], y[3]));
+    }
+}
+
+template <int STEPS, bool B32>
+static cudaError_t launch_gemv(const GemvArgs& a, dim3 grid, int threads, int pdl, cudaStream_t st) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, gemv_kernel<STEPS, B32>, a);
+}
+
+}  // namespace scmx
+
+using namespace scmx;
+
+extern "C" int scmx_gemv(const int8_t* xq, const float* xscale, const uint32_t* codes, const uint8_t* bcodes,
+                         const float* wscale, int64_t N, int64_t K, const scmx_format* fmt, int epi, const uint16_t* res,
+                         const int32_t* eidx, int n_routed, int shared, int xstride, void* out, int pdl, void* stream) {
+    GemvArgs a;
+    int rc = make_dev_format(fmt, &a.f);
+    if (rc) return rc;
+    SCMX_REQUIRE(K > 0 && K % 128 == 0 && K <= (1 << 20), SCMX_EINVAL, "gemv: K=%lld must be a multiple of 128", (long long)K);
+    SCMX_REQUIRE(N > 0 && N % 4 == 0 && N < (1ll << 30), SCMX_EINVAL, "gemv: N=%lld must be a multiple of 4", (long long)N);
+    SCMX_REQUIRE(epi >= 0 && epi <= 3, SCMX_EINVAL, "gemv: epi=%d outside 0..3", epi);
+    SCMX_REQUIRE(epi != 2 || res != nullptr, SCMX_EINVAL, "gemv: epi 2 needs res");
+    SCMX_REQUIRE(epi == 0 || xscale != nullptr, SCMX_EINVAL, "gemv: xscale is NULL");
+    SCMX_REQUIRE(K % (a.f.block * a.f.blocks_per_byte) == 0, SCMX_EINVAL,
+                 "gemv: K=%lld not a multiple of block*codes_per_byte=%d", (long long)K, a.f.block * a.f.blocks_per_byte);
+    SCMX_REQUIRE(a.f.block % 32 == 0 || 32 % a.f.block == 0, SCMX_EFORMAT, "gemv: block=%d must divide or be a multiple of 32",
+                 a.f.block);
+    SCMX_REQUIRE((reinterpret_cast<uintptr_t>(codes) & 15) == 0 && (reinterpret_cast<uintptr_t>(xq) & 15) == 0, SCMX_EINVAL,
+                 "gemv: codes and xq must be 16-byte aligned");
+    int slots = 1;
+    if (eidx) {
+        SCMX_REQUIRE(n_routed >= 0 && n_routed + (shared >= 0 ? 1 : 0) >= 1, SCMX_EINVAL, "gemv: no slots");
+        slots = n_routed + (shared >= 0 ? 1 : 0);
+    }
+    SCMX_REQUIRE(xstride == 0 || xstride == 1, SCMX_EINVAL, "gemv: xstride must be 0 or 1");
+    a.xq = xq; a.xscale = xscale; a.codes = codes; a.bcodes = bcodes; a.wscale = wscale; a.res = res; a.eidx = eidx;
+    a.out = out; a.N = (int)N; a.K = (int)K; a.epi = epi; a.n_routed = n_routed; a.shared = shared; a.xstride = xstride;
+    a.bc_row_bytes = (int)(K / (a.f.block * a.f.blocks_per_byte));
+    const int ksteps = (int)((K + 1023) / 1024);
+    // A warp streams `steps` K-steps of 1024 codes for its 4 rows; the remaining K-steps are split over `sk` warps of
+    // the CTA.  Prefer more loads in flight per warp (larger steps) only while the grid still has >= 16 warps per SM.
+    const int64_t groups64 = N / 4;
+    int steps = 1, sk = ksteps;
+    for (int cand = 4; cand >= 1; cand >>= 1) {
+        const int csk = (ksteps + cand - 1) / cand;
+        if (csk <= 8 && (cand == 1 || groups64 * csk >= 148 * 16)) { steps = cand; sk = csk; break; }
+    }
+    while (sk > 8 && steps < 4) { steps *= 2; sk = (ksteps + steps - 1) / steps; }
+    SCMX_REQUIRE(sk <= 8, SCMX_ELIMIT, "gemv: K=%lld too large (max 32768)", (long long)K);
+    a.sk = sk;
+    a.rg = 8 / sk < 1 ? 1 : 8 / sk;
+    const int groups = (int)(N / 4);
+    if (a.rg > groups) a.rg = groups;
+    dim3 grid((groups + a.rg - 1) / a.rg, slots);
+    const int threads = 32 * a.rg * a.sk;
+    const bool b32 = a.f.block % 32 == 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+    if (steps == 1) e = b32 ? launch_gemv<1, true>(a, grid, threads, pdl, st) : launch_gemv<1, false>(a, grid, threads, pdl, st);
+    else if (steps == 2) e = b32 ? launch_gemv<2, true>(a, grid, threads, pdl, st) : launch_gemv<2, false>(a, grid, threads, pdl, st);
+    else e = b32 ? launch_gemv<4, true>(a, grid, threads, pdl, st) : launch_gemv<4, false>(a, grid, threads, pdl, st);
+    if (e != cudaSuccess) {
+        set_error("gemv launch failed: %s", cudaGetErrorString(e));
+        return SCMX_ECUDA;
+    }
+    return SCMX_OK;
+}

@@ -1,0 +1,140 @@
+// MoE routing on the device: router softmax + top-k, and the counting sort of token-expert assignments by expert
+// with segment offsets and M-tile starts (the inputs of the grouped GEMM's tile scheduler).
+#include <float.h>
+#include "scmx_common.cuh"
+
+namespace scmx {
+
+// One CTA sorts all R = M*topk assignments: shared-memory histogram, serial prefix over E <= 1024 experts, then a
+// scatter where every assignment takes the next free row of its expert.  Row order inside an expert segment is
+// arbitrary (atomics), which changes no result because every sorted row is computed independently.
+__global__ void __launch_bounds__(1024) route_sort_kernel(const int32_t* __restrict__ inds, int R, int topk, int E, int tm,
+                                                          int32_t* __restrict__ pos, int32_t* __restrict__ tok,
+                                                          int32_t* __restrict__ esorted, int32_t* __restrict__ off,
+                                                          int32_t* __restrict__ tstart) {
+    __shared__ unsigned cnt[1024];
+    __shared__ unsigned cur[1024];
+    const int tid = threadIdx.x, nt = blockDim.x;
+    for (int e = tid; e < E; e += nt) cnt[e] = 0;
+    __syncthreads();
+    for (int i = tid; i < R; i += nt) {
+        const unsigned e = (unsigned)inds[i];
+        if (e < (unsigned)E) atomicAdd(&cnt[e], 1u);
+    }
+    __syncthreads();
+    if (tid < 32) {
+        // warp-level exclusive scan over experts in chunks of 32
+        unsigned o = 0, t = 0;
+        for (int base = 0; base < E; base += 32) {
+            const int e = base + tid;
+            const unsigned c = e < E ? cnt[e] : 0u;
+            const unsigned ti = (c + tm - 1) / tm;
+            unsigned so = c, st = ti;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const unsigned a = __shfl_up_sync(0xffffffffu, so, d), b = __shfl_up_sync(0xffffffffu, st, d);
+                if (tid >= d) { so += a; st += b; }
+            }
+            if (e < E) {
+                off[e] = (int)(o + so - c);
+                tstart[e] = (int)(t + st - ti);
+                cur[e] = o + so - c;
+            }
+            o += __shfl_sync(0xffffffffu, so, 31);
+            t += __shfl_sync(0xffffffffu, st, 31);
+        }
+        if (tid == 0) { off[E] = (int)o; tstart[E] = (int)t; }
+    }
+    __syncthreads();
+    for (int i = tid; i < R; i += nt) {
+        const unsigned e = (unsigned)inds[i];
+        if (e < (unsigned)E) {
+            const unsigned p = atomicAdd(&cur[e], 1u);
+            pos[i] = (int)p;
+            tok[p] = i / topk;
+            esorted[p] = (int)e;
+        }
+    }
+    for (int p = R + tid; p < R + tm; p += nt) tok[p] = 0;   // padding rows gather token 0 and are never stored
+}
+
+// One warp per token: softmax over E logits in float32, then topk rounds of warp arg-max (ties -> lower expert id).
+__global__ void __launch_bounds__(256) router_topk_kernel(const float* __restrict__ logits, int64_t M, int E, int topk,
+                                                          int32_t* __restrict__ inds, uint16_t* __restrict__ scores,
+                                                          float* __restrict__ scores_f32) {
+    const int lane = threadIdx.x & 31;
+    const int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= M) return;
+    const float* lg = logits + t * E;
+    constexpr int PER = 32;                 // E <= 1024
+    float p[PER];
+    float mx = -FLT_MAX;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int e = j * 32 + lane;
+        p[j] = e < E ? lg[e] : -FLT_MAX;
+        mx = fmaxf(mx, p[j]);
+    }
+    mx = warp_max(mx);
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int e = j * 32 + lane;
+        p[j] = e < E ? expf(__fsub_rn(p[j], mx)) : 0.0f;
+        sum += p[j];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int e = j * 32 + lane;
+        p[j] = e < E ? __fdiv_rn(p[j], sum) : -1.0f;
+    }
+    for (int r = 0; r < topk; ++r) {
+        float bv = -1.0f;
+        int be = 0x7fffffff;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            const int e = j * 32 + lane;
+            if (p[j] > bv) { bv = p[j]; be = e; }    // ascending e per lane: first maximum wins
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+            if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
+        }
+        if (lane == 0) {
+            inds[t * topk + r] = be;
+            scores[t * topk + r] = f32_to_bf16(bv);
+            if (scores_f32) scores_f32[t * topk + r] = bv;
+        }
+#pragma unroll
+        for (int j = 0; j < PER; ++j)
+            if (j * 32 + lane == be) p[j] = -1.0f;
+    }
+}
+
+}  // namespace scmx
+
+using namespace scmx;
+
+extern "C" int scmx_route_sort(const int32_t* inds, int64_t M, int topk, int E, int tm, int32_t* pos, int32_t* tok,
+                               int32_t* esorted, int32_t* off, int32_t* tstart, void* stream) {
+    SCMX_REQUIRE(M >= 0 && topk >= 1 && tm >= 1, SCMX_EINVAL, "route_sort: need M >= 0, topk >= 1, tm >= 1");
+    SCMX_REQUIRE(E >= 1 && E <= 1024, SCMX_ELIMIT, "route_sort: E=%d outside 1..1024", E);
+    SCMX_REQUIRE(M * topk < (1ll << 30), SCMX_ELIMIT, "route_sort: M*topk too large");
+    route_sort_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(inds, (int)(M * topk), topk, E, tm, pos, tok, esorted, off, tstart);
+    SCMX_LAUNCH_OK("route_sort_kernel");
+    return SCMX_OK;
+}
+
+extern "C" int scmx_router_topk(const float* logits, int64_t M, int E, int topk, int32_t* inds, uint16_t* scores,
+                                float* scores_f32, void* stream) {
+    SCMX_REQUIRE(M >= 0 && E >= 1 && E <= 1024 && topk >= 1 && topk <= E, SCMX_EINVAL,
+                 "router_topk: need 1 <= topk <= E <= 1024 (E=%d topk=%d)", E, topk);
+    if (M == 0) return SCMX_OK;
+    router_topk_kernel<<<(unsigned)((M + 7) / 8), 256, 0, (cudaStream_t)stream>>>(logits, M, E, topk, inds, scores, scores_f32);
+    SCMX_LAUNCH_OK("router_topk_kernel");
+    return SCMX_OK;
+}

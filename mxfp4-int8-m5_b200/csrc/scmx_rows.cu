@@ -1,0 +1,405 @@
+// HBM-bound row kernels of the W4A8 path: weight unpack, per-token INT8 activation quantization, RMSNorm + quant,
+// residual / SwiGLU epilogues on INT32 accumulators, MoE combine, row gather.  One CTA per activation row;
+// 128-bit loads; reductions by warp shuffle + shared memory.
+#include "scmx_common.cuh"
+
+namespace scmx {
+
+// ---- unpack: thread = one uint4 of codes (32 weights) ------------------------------------------------------------
+__global__ void __launch_bounds__(256) unpack_kernel(const uint4* __restrict__ codes, const uint8_t* __restrict__ bcodes,
+                                                     int64_t n_vec, int vec_per_row, int bc_row_bytes, DevFormat f,
+                                                     uint4* __restrict__ wq) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_vec) return;
+    const int64_t n = i / vec_per_row;
+    const int k0 = (int)(i % vec_per_row) * 32;
+    const uint4 c = codes[i];
+    const uint32_t w[4] = {c.x, c.y, c.z, c.w};
+    const uint8_t* bc = bcodes + n * bc_row_bytes;
+    uint32_t o[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int blk = (k0 + 8 * j) / f.block;
+        const uint32_t m = fmt_mult(f, block_code(bc, blk, f.bc_bits, f.blocks_per_byte));
+        const uint32_t plo = lut_scale(f.mag_lo, m), phi = lut_scale(f.mag_hi, m);
+        decode_word(w[j], plo, phi, lut_negate(plo), lut_negate(phi), o[2 * j], o[2 * j + 1]);
+    }
+    wq[2 * i] = make_uint4(o[0], o[1], o[2], o[3]);
+    wq[2 * i + 1] = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+// ---- helpers: a row of K values processed by the CTA in vectors of 8 --------------------------------------------
+__device__ __forceinline__ void load8_bf16(const uint16_t* p, float v[8]) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        v[2 * j] = __uint_as_float(w[j] << 16);
+        v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+    }
+}
+__device__ __forceinline__ void store8_i8(int8_t* p, const int q[8]) {
+    uint2 o;
+    o.x = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
+    o.y = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
+    *reinterpret_cast<uint2*>(p) = o;
+}
+__device__ __forceinline__ void store8_bf16(uint16_t* p, const float v[8]) {
+    uint4 o;
+    o.x = f32_to_bf16(v[0]) | ((uint32_t)f32_to_bf16(v[1]) << 16);
+    o.y = f32_to_bf16(v[2]) | ((uint32_t)f32_to_bf16(v[3]) << 16);
+    o.z = f32_to_bf16(v[4]) | ((uint32_t)f32_to_bf16(v[5]) << 16);
+    o.w = f32_to_bf16(v[6]) | ((uint32_t)f32_to_bf16(v[7]) << 16);
+    *reinterpret_cast<uint4*>(p) = o;
+}
+
+// ---- act_quant -------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) act_quant_kernel(const uint16_t* __restrict__ x, int64_t M, int K,
+                                                        int8_t* __restrict__ xq, float* __restrict__ xs) {
+    __shared__ float red[33];
+    const int64_t row = blockIdx.x;
+    int8_t* qrow = xq + row * K;
+    if (row >= M) {   // padded rows: zero codes, zero scale
+        for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) *reinterpret_cast<uint2*>(qrow + k) = make_uint2(0, 0);
+        if (threadIdx.x == 0) xs[row] = 0.0f;
+        return;
+    }
+    const uint16_t* xrow = x + row * K;
+    float amax = 0.0f;
+    for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+        float v[8];
+        load8_bf16(xrow + k, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    }
+    amax = block_max(amax, red);
+    float s, qi;
+    quant_scale(amax, s, qi);
+    for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+        float v[8];
+        int q[8];
+        load8_bf16(xrow + k, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) q[j] = quant_code(v[j], qi);
+        store8_i8(qrow + k, q);
+    }
+    if (threadIdx.x == 0) xs[row] = s;
+}
+
+// ---- RMSNorm + quant (optionally writing the normalized bf16 row) -----------------------------------------------
+// inv = 1 / sqrt(float(sum x^2) / K + eps): the sum of squares is accumulated in float64 (exact for bf16 inputs of
+// ordinary dynamic range, hence independent of the reduction order), the reciprocal square root in float64.
+__device__ __forceinline__ float rms_inverse(double ss, int K, float eps) {
+    const float m = __fadd_rn(__fdiv_rn((float)ss, (float)K), eps);
+    return (float)(1.0 / sqrt((double)m));
+}
+
+__global__ void __launch_bounds__(256) rmsnorm_quant_kernel(const uint16_t* __restrict__ x,
+                                                            const uint16_t* __restrict__ nw, float eps, int64_t M, int K,
+                                                            int8_t* __restrict__ xq, float* __restrict__ xs,
+                                                            uint16_t* __restrict__ xn) {
+    __shared__ float red[33];
+    __shared__ double dred[33];
+    const int64_t row = blockIdx.x;
+    int8_t* qrow = xq + row * K;
+    if (row >= M) {
+        for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+            *reinterpret_cast<uint2*>(qrow + k) = make_uint2(0, 0);
+            if (xn) *reinterpret_cast<uint4*>(xn + row * K + k) = make_uint4(0, 0, 0, 0);
+        }
+        if (threadIdx.x == 0) xs[row] = 0.0f;
+        return;
+    }
+    const uint16_t* xrow = x + row * K;
+    double ss = 0.0;
+    for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+        float v[8];
+        load8_bf16(xrow + k, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += (double)v[j] * (double)v[j];
+    }
+    ss = block_sum(ss, dred);
+    const float inv = rms_inverse(ss, K, eps);
+    float amax = 0.0f;
+    for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+        float v[8], w[8];
+        load8_bf16(xrow + k, v);
+        load8_bf16(nw + k, w);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            v[j] = rbf(__fmul_rn(w[j], rbf(__fmul_rn(v[j], inv))));
+            amax = fmaxf(amax, fabsf(v[j]));
+        }
+        if (xn) store8_bf16(xn + row * K + k, v);
+    }
+    amax = block_max(amax, red);
+    float s, qi;
+    quant_scale(amax, s, qi);
+    for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+        float v[8], w[8];
+        int q[8];
+        load8_bf16(xrow + k, v);
+        load8_bf16(nw + k, w);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) q[j] = quant_code(rbf(__fmul_rn(w[j], rbf(__fmul_rn(v[j], inv)))), qi);
+        store8_i8(qrow + k, q);
+    }
+    if (threadIdx.x == 0) xs[row] = s;
+}
+
+// ---- residual epilogue on INT32 accumulators ---------------------------------------------------------------------
+__global__ void __launch_bounds__(256) res_epilogue_kernel(const int32_t* __restrict__ acc, const float* __restrict__ xscale,
+                                                           const float* __restrict__ wscale,
+                                                           const uint16_t* __restrict__ res, int64_t total4, int N,
+                                                           uint16_t* __restrict__ h) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total4) return;
+    const int64_t e = i * 4;
+    const int64_t m = e / N;
+    const int n = (int)(e % N);
+    const int4 a = *reinterpret_cast<const int4*>(acc + e);
+    const float4 ws = *reinterpret_cast<const float4*>(wscale + n);
+    const uint2 r = *reinterpret_cast<const uint2*>(res + e);
+    const float xsm = xscale[m];
+    const float y0 = rbf(__fadd_rn(__uint_as_float(r.x << 16), scale_acc(a.x, xsm, ws.x)));
+    const float y1 = rbf(__fadd_rn(__uint_as_float(r.x & 0xFFFF0000u), scale_acc(a.y, xsm, ws.y)));
+    const float y2 = rbf(__fadd_rn(__uint_as_float(r.y << 16), scale_acc(a.z, xsm, ws.z)));
+    const float y3 = rbf(__fadd_rn(__uint_as_float(r.y & 0xFFFF0000u), scale_acc(a.w, xsm, ws.w)));
+    uint2 o;
+    o.x = f32_to_bf16(y0) | ((uint32_t)f32_to_bf16(y1) << 16);
+    o.y = f32_to_bf16(y2) | ((uint32_t)f32_to_bf16(y3) << 16);
+    *reinterpret_cast<uint2*>(h + e) = o;
+}
+
+// ---- SwiGLU of gate | up accumulators, then per-token INT8 ----------------------------------------------------------
+__global__ void __launch_bounds__(256) swiglu_quant_kernel(const int32_t* __restrict__ acc, const float* __restrict__ xscale,
+                                                           const float* __restrict__ wscale, int F, int8_t* __restrict__ xq,
+                                                           float* __restrict__ xs) {
+    __shared__ float red[33];
+    const int64_t row = blockIdx.x;
+    const int32_t* ar = acc + row * 2 * (int64_t)F;
+    const float xsr = xscale[row];
+    float amax = 0.0f;
+    for (int c = threadIdx.x * 4; c < F; c += blockDim.x * 4) {
+        const int4 g4 = *reinterpret_cast<const int4*>(ar + c);
+        const int4 u4 = *reinterpret_cast<const int4*>(ar + F + c);
+        const float4 wg = *reinterpret_cast<const float4*>(wscale + c);
+        const float4 wu = *reinterpret_cast<const float4*>(wscale + F + c);
+        amax = fmaxf(amax, fabsf(swiglu_bf16(scale_acc(g4.x, xsr, wg.x), scale_acc(u4.x, xsr, wu.x))));
+        amax = fmaxf(amax, fabsf(swiglu_bf16(scale_acc(g4.y, xsr, wg.y), scale_acc(u4.y, xsr, wu.y))));
+        amax = fmaxf(amax, fabsf(swiglu_bf16(scale_acc(g4.z, xsr, wg.z), scale_acc(u4.z, xsr, wu.z))));
+        amax = fmaxf(amax, fabsf(swiglu_bf16(scale_acc(g4.w, xsr, wg.w), scale_acc(u4.w, xsr, wu.w))));
+    }
+    amax = block_max(amax, red);
+    float s, qi;
+    quant_scale(amax, s, qi);
+    for (int c = threadIdx.x * 4; c < F; c += blockDim.x * 4) {
+        const int4 g4 = *reinterpret_cast<const int4*>(ar + c);
+        const int4 u4 = *reinterpret_cast<const int4*>(ar + F + c);
+        const float4 wg = *reinterpret_cast<const float4*>(wscale + c);
+        const float4 wu = *reinterpret_cast<const float4*>(wscale + F + c);
+        const int q0 = quant_code(swiglu_bf16(scale_acc(g4.x, xsr, wg.x), scale_acc(u4.x, xsr, wu.x)), qi);
+        const int q1 = quant_code(swiglu_bf16(scale_acc(g4.y, xsr, wg.y), scale_acc(u4.y, xsr, wu.y)), qi);
+        const int q2 = quant_code(swiglu_bf16(scale_acc(g4.z, xsr, wg.z), scale_acc(u4.z, xsr, wu.z)), qi);
+        const int q3 = quant_code(swiglu_bf16(scale_acc(g4.w, xsr, wg.w), scale_acc(u4.w, xsr, wu.w)), qi);
+        *reinterpret_cast<uint32_t*>(xq + row * F + c) =
+            (q0 & 0xFF) | ((q1 & 0xFF) << 8) | ((q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
+    }
+    if (threadIdx.x == 0) xs[row] = s;
+}
+
+__global__ void swiglu_kernel(const uint16_t* __restrict__ g, const uint16_t* __restrict__ u, int64_t n,
+                              uint16_t* __restrict__ out) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = f32_to_bf16(swiglu_bf16(bf16_to_f32(g[i]), bf16_to_f32(u[i])));
+}
+
+// ---- MoE combine ------------------------------------------------------------------------------------------------------
+// acc_j = rbf(rbf(y[pos[t*k+j]] * sc_j) + acc_{j-1}), h = T(res + acc); then (QUANT) RMSNorm + INT8 of h.
+template <int TOPK_MAX>
+__global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t* __restrict__ y, const int32_t* __restrict__ pos,
+                                                          const uint16_t* __restrict__ scores,
+                                                          const uint16_t* __restrict__ res, const uint16_t* __restrict__ nw,
+                                                          float eps, int64_t M, int K, int topk, int quant,
+                                                          uint16_t* __restrict__ h, int8_t* __restrict__ xq,
+                                                          float* __restrict__ xs) {
+    __shared__ float red[33];
+    __shared__ double dred[33];
+    __shared__ int s_pos[TOPK_MAX];
+    __shared__ float s_sc[TOPK_MAX];
+    const int64_t row = blockIdx.x;
+    const bool live = row < M;
+    if (live && threadIdx.x < topk) {
+        s_pos[threadIdx.x] = pos[row * topk + threadIdx.x];
+        s_sc[threadIdx.x] = bf16_to_f32(scores[row * topk + threadIdx.x]);
+    }
+    __syncthreads();
+    const uint16_t* rrow = res + row * K;
+    uint16_t* hrow = h + row * K;
+    double ss = 0.0;
+    for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+        float r[8], a[8];
+        load8_bf16(rrow + k, r);
+        if (live) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a[j] = 0.0f;
+            for (int t = 0; t < topk; ++t) {
+                float v[8];
+                load8_bf16(y + (int64_t)s_pos[t] * K + k, v);
+                const float sc = s_sc[t];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) a[j] = rbf(__fadd_rn(rbf(__fmul_rn(v[j], sc)), a[j]));
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) r[j] = rbf(__fadd_rn(r[j], a[j]));
+        }
+        store8_bf16(hrow + k, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += (double)r[j] * (double)r[j];
+    }
+    if (!quant) return;
+    int8_t* qrow = xq + row * K;
+    __syncthreads();   // h row written by this CTA is re-read below
+    ss = block_sum(ss, dred);
+    const float inv = rms_inverse(ss, K, eps);
+    float amax = 0.0f;
+    for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+        float v[8], w[8];
+        load8_bf16(hrow + k, v);
+        load8_bf16(nw + k, w);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(rbf(__fmul_rn(w[j], rbf(__fmul_rn(v[j], inv))))));
+    }
+    amax = block_max(amax, red);
+    float s, qi;
+    quant_scale(amax, s, qi);
+    for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+        float v[8], w[8];
+        int q[8];
+        load8_bf16(hrow + k, v);
+        load8_bf16(nw + k, w);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) q[j] = quant_code(rbf(__fmul_rn(w[j], rbf(__fmul_rn(v[j], inv)))), qi);
+        store8_i8(qrow + k, q);
+    }
+    if (threadIdx.x == 0) xs[row] = s;
+}
+
+// ---- row gather --------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) gather_rows_kernel(const int8_t* __restrict__ xq, const float* __restrict__ xs,
+                                                          const int32_t* __restrict__ tok, int64_t rows_s, int K,
+                                                          int8_t* __restrict__ dq, float* __restrict__ ds) {
+    const int64_t p = blockIdx.x;
+    const int t = tok[p];
+    const uint4* src = reinterpret_cast<const uint4*>(xq + (int64_t)t * K);
+    uint4* dst = reinterpret_cast<uint4*>(dq + p * K);
+    for (int i = threadIdx.x; i < K / 16; i += blockDim.x) dst[i] = src[i];
+    if (threadIdx.x == 0 && p < rows_s) ds[p] = xs[t];
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace scmx
+
+using namespace scmx;
+
+extern "C" int scmx_unpack_i8(const uint32_t* codes, const uint8_t* bcodes, int64_t N, int64_t K, const scmx_format* fmt,
+                              int8_t* wq, void* stream) {
+    DevFormat f;
+    int rc = make_dev_format(fmt, &f);
+    if (rc) return rc;
+    SCMX_REQUIRE(N >= 0 && K > 0 && K % 32 == 0 && K % (f.block * f.blocks_per_byte) == 0, SCMX_EINVAL,
+                 "unpack_i8: K=%lld must be a multiple of 32 and of block*codes_per_byte=%d", (long long)K,
+                 f.block * f.blocks_per_byte);
+    SCMX_REQUIRE(f.block % 8 == 0 && (32 % f.block == 0 || f.block % 32 == 0), SCMX_EFORMAT,
+                 "unpack_i8: block=%d must divide or be a multiple of 32", f.block);
+    SCMX_REQUIRE(aligned16(codes) && aligned16(wq), SCMX_EINVAL, "unpack_i8: codes and wq must be 16-byte aligned");
+    if (N == 0) return SCMX_OK;
+    const int64_t n_vec = N * K / 32;
+    const int bc_row = (int)(K / (f.block * f.blocks_per_byte));
+    unpack_kernel<<<(unsigned)((n_vec + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        reinterpret_cast<const uint4*>(codes), bcodes, n_vec, (int)(K / 32), bc_row, f, reinterpret_cast<uint4*>(wq));
+    SCMX_LAUNCH_OK("unpack_kernel");
+    return SCMX_OK;
+}
+
+extern "C" int scmx_act_quant(const uint16_t* x, int64_t M, int64_t K, int64_t Mp, int8_t* xq, float* xs, void* stream) {
+    SCMX_REQUIRE(M >= 0 && Mp >= M && K > 0 && K % 8 == 0 && K <= (1 << 20), SCMX_EINVAL,
+                 "act_quant: need 0 <= M <= Mp and K %% 8 == 0 (M=%lld Mp=%lld K=%lld)", (long long)M, (long long)Mp,
+                 (long long)K);
+    SCMX_REQUIRE(aligned16(x) && aligned16(xq) && K % 8 == 0, SCMX_EINVAL, "act_quant: x and xq must be 16-byte aligned");
+    if (Mp == 0) return SCMX_OK;
+    act_quant_kernel<<<(unsigned)Mp, 256, 0, (cudaStream_t)stream>>>(x, M, (int)K, xq, xs);
+    SCMX_LAUNCH_OK("act_quant_kernel");
+    return SCMX_OK;
+}
+
+extern "C" int scmx_rmsnorm_quant(const uint16_t* x, const uint16_t* nw, float eps, int64_t M, int64_t K, int64_t Mp,
+                                  int8_t* xq, float* xs, uint16_t* xn, void* stream) {
+    SCMX_REQUIRE(M >= 0 && Mp >= M && K > 0 && K % 8 == 0 && K <= (1 << 20), SCMX_EINVAL,
+                 "rmsnorm_quant: need 0 <= M <= Mp and K %% 8 == 0 (M=%lld Mp=%lld K=%lld)", (long long)M,
+                 (long long)Mp, (long long)K);
+    SCMX_REQUIRE(aligned16(x) && aligned16(nw) && aligned16(xq) && (!xn || aligned16(xn)), SCMX_EINVAL,
+                 "rmsnorm_quant: buffers must be 16-byte aligned");
+    if (Mp == 0) return SCMX_OK;
+    rmsnorm_quant_kernel<<<(unsigned)Mp, 256, 0, (cudaStream_t)stream>>>(x, nw, eps, M, (int)K, xq, xs, xn);
+    SCMX_LAUNCH_OK("rmsnorm_quant_kernel");
+    return SCMX_OK;
+}
+
+extern "C" int scmx_res_epilogue(const int32_t* acc, const float* xscale, const float* wscale, const uint16_t* res,
+                                 int64_t Mp, int64_t N, uint16_t* h, void* stream) {
+    SCMX_REQUIRE(Mp >= 0 && N > 0 && N % 4 == 0, SCMX_EINVAL, "res_epilogue: N=%lld must be a multiple of 4", (long long)N);
+    SCMX_REQUIRE(aligned16(acc) && aligned16(wscale) && aligned16(res) && aligned16(h), SCMX_EINVAL,
+                 "res_epilogue: buffers must be 16-byte aligned");
+    const int64_t total4 = Mp * N / 4;
+    if (total4 == 0) return SCMX_OK;
+    res_epilogue_kernel<<<(unsigned)((total4 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(acc, xscale, wscale, res,
+                                                                                            total4, (int)N, h);
+    SCMX_LAUNCH_OK("res_epilogue_kernel");
+    return SCMX_OK;
+}
+
+extern "C" int scmx_swiglu_quant(const int32_t* acc, const float* xscale, const float* wscale, int64_t Mp, int64_t F,
+                                 int8_t* xq, float* xs, void* stream) {
+    SCMX_REQUIRE(Mp >= 0 && F > 0 && F % 4 == 0, SCMX_EINVAL, "swiglu_quant: F=%lld must be a multiple of 4", (long long)F);
+    SCMX_REQUIRE(aligned16(acc) && aligned16(wscale) && aligned16(xq), SCMX_EINVAL,
+                 "swiglu_quant: buffers must be 16-byte aligned");
+    if (Mp == 0) return SCMX_OK;
+    swiglu_quant_kernel<<<(unsigned)Mp, 256, 0, (cudaStream_t)stream>>>(acc, xscale, wscale, (int)F, xq, xs);
+    SCMX_LAUNCH_OK("swiglu_quant_kernel");
+    return SCMX_OK;
+}
+
+extern "C" int scmx_swiglu(const uint16_t* g, const uint16_t* u, int64_t n, uint16_t* out, void* stream) {
+    SCMX_REQUIRE(n >= 0, SCMX_EINVAL, "swiglu: negative length");
+    if (n == 0) return SCMX_OK;
+    swiglu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(g, u, n, out);
+    SCMX_LAUNCH_OK("swiglu_kernel");
+    return SCMX_OK;
+}
+
+extern "C" int scmx_moe_combine(const uint16_t* y, const int32_t* pos, const uint16_t* scores, const uint16_t* res,
+                                const uint16_t* nw, float eps, int64_t M, int64_t Mp, int64_t K, int topk, int quant,
+                                uint16_t* h, int8_t* xq, float* xs, void* stream) {
+    SCMX_REQUIRE(M >= 0 && Mp >= M && K > 0 && K % 8 == 0, SCMX_EINVAL, "moe_combine: need M <= Mp and K %% 8 == 0");
+    SCMX_REQUIRE(topk >= 1 && topk <= 32, SCMX_ELIMIT, "moe_combine: topk=%d outside 1..32", topk);
+    SCMX_REQUIRE(aligned16(y) && aligned16(res) && aligned16(h) && (!quant || (aligned16(xq) && aligned16(nw))),
+                 SCMX_EINVAL, "moe_combine: buffers must be 16-byte aligned");
+    if (Mp == 0) return SCMX_OK;
+    moe_combine_kernel<32><<<(unsigned)Mp, 256, 0, (cudaStream_t)stream>>>(y, pos, scores, res, nw, eps, M, (int)K, topk,
+                                                                             quant, h, xq, xs);
+    SCMX_LAUNCH_OK("moe_combine_kernel");
+    return SCMX_OK;
+}
+
+extern "C" int scmx_gather_rows(const int8_t* xq, const float* xs, const int32_t* tok, int64_t rows_q, int64_t rows_s,
+                                int64_t K, int8_t* dst_q, float* dst_s, void* stream) {
+    SCMX_REQUIRE(rows_q >= 0 && rows_s <= rows_q && K > 0 && K % 16 == 0, SCMX_EINVAL,
+                 "gather_rows: need rows_s <= rows_q and K %% 16 == 0");
+    SCMX_REQUIRE(aligned16(xq) && aligned16(dst_q), SCMX_EINVAL, "gather_rows: buffers must be 16-byte aligned");
+    if (rows_q == 0) return SCMX_OK;
+    gather_rows_kernel<<<(unsigned)rows_q, 128, 0, (cudaStream_t)stream>>>(xq, xs, tok, rows_s, (int)K, dst_q, dst_s);
+    SCMX_LAUNCH_OK("gather_rows_kernel");
+    return SCMX_OK;
+}

@@ -1,0 +1,38 @@
+"""Batch-1 decode GEMV that reads the packed SC-MXFP4 weights directly, with the call signature of the reference's
+e2e/sc_decode.py `gemv`.  The kernel accumulates exact INT32 totals (DP4A) and applies the GEMM's epilogues, so
+decode and prefill produce the same bits.  Prologues pro=1 / pro=2 (activation quantization / RMSNorm + quantization
+of a bf16 input row) run as the separate row kernel followed by the GEMV, which computes the same values."""
+import torch
+
+from . import _lib
+from . import sc_format as F
+from . import sc_kernels as S
+
+USE_PDL = True   # programmatic dependent launch: weight loads overlap the previous kernel's tail
+
+
+def gemv(xq, codes, bcodes, xscale, wscale, N, epi, dtype=torch.bfloat16, res=None, nsg=None, eidx=None, xstride=0,
+         pro=0, nw=None, eps=None, rows=None, vpl=None, shared=None, splitk=None):
+    """W4A8 GEMV.  pro=0: xq int8 [K] (or [S, K] with xstride=1) and xscale; pro=1: xq is a bf16 row (or rows),
+    quantized per token first; pro=2: RMSNorm(nw, eps) + INT8 first.  Output: EPI 1: bf16 [N]; 2: bf16 [N] = res + y;
+    3: bf16 [N / 2] (interleaved gate/up rows); 0: int32 [N] exact totals.
+    MoE (eidx int32 [S] given): codes [E, ...], bcodes [E, N, ...], wscale [E, N]; output row j uses expert eidx[j] and
+    input row j if xstride = 1 (else the single input row) -> [S, N or N/2].  shared = e: one more slot uses expert e.
+    nsg / rows / vpl / splitk are Metal tile hints: accepted and ignored."""
+    if pro:
+        x2 = xq.reshape(-1, xq.shape[-1])
+        xq, xscale = (S.act_quant(x2, x2.shape[0]) if pro == 1 else S.rmsnorm_quant(x2, nw, eps, x2.shape[0]))
+    _lib.require_cuda(xq, codes, bcodes, xscale, wscale, res, eidx)
+    K = xq.shape[-1]
+    nslot = 0 if eidx is None else eidx.numel()
+    S_ = 1 if eidx is None else nslot + (shared is not None)
+    assert K % 128 == 0 and N % 4 == 0 and epi in (0, 1, 2, 3)
+    assert dtype == torch.bfloat16
+    no = N // 2 if epi == 3 else N
+    out = torch.empty(S_ * no, dtype=torch.int32 if epi == 0 else torch.bfloat16, device=xq.device)
+    if eidx is not None:
+        eidx = eidx.to(torch.int32)
+    _lib.call("scmx_gemv", _lib.ptr(xq), _lib.ptr(xscale), _lib.ptr(codes), _lib.ptr(bcodes), _lib.ptr(wscale), N, K,
+              F.DEFAULT.c_struct(), epi, _lib.ptr(res) if epi == 2 else None, _lib.ptr(eidx), nslot,
+              -1 if shared is None else int(shared), xstride, _lib.ptr(out), int(USE_PDL), _lib.stream())
+    return out if eidx is None else out.reshape(S_, no)

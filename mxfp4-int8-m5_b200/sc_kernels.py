@@ -1,0 +1,154 @@
+"""Prefill-side kernels of the W4A8 path as torch functions, with the call signatures of the reference's
+e2e/sc_kernels.py: every function takes M rows and writes Mp >= M rows (rows >= M are zero), returns freshly
+allocated CUDA tensors, and accepts (and ignores) the reference's Metal tuning arguments `deps`, `tile`, `nt`.
+
+  act_quant, unpack_i8, mm_i8_i32, mm_epi, rmsnorm_quant, rmsnorm_quant_n, res_norm_quant, res_epilogue,
+  swiglu_quant, interleave_gate_up, pad_rows, set_format
+
+All arithmetic happens in libscmx (CUDA, sm_100a); the GEMMs are tcgen05 kind::i8 kernels.
+"""
+import numpy as np
+import torch
+
+from . import _lib
+from . import sc_format as F
+
+TM, TN, NSG, GROUP_M = 128, 256, 4, 8   # M tile of the GEMM kernel (row padding unit); the rest are informational
+
+
+def set_format(fmt):
+    """Switch every kernel (unpack, grouped expert GEMM, GEMV) to another weight format (sc_format.Format)."""
+    F.DEFAULT = fmt
+
+
+def pad_rows(M):
+    return -(-M // TM) * TM
+
+
+def _bf16(x):
+    assert x.dtype == torch.bfloat16, "activations are bfloat16"
+    return x
+
+
+def unpack_i8(codes, bcodes, N, K, deps=()):
+    """Packed codes + block codes -> INT8 operand [N, K]."""
+    _lib.require_cuda(codes, bcodes)
+    wq = torch.empty((N, K), dtype=torch.int8, device=codes.device)
+    _lib.call("scmx_unpack_i8", _lib.ptr(codes), _lib.ptr(bcodes), N, K, F.DEFAULT.c_struct(), _lib.ptr(wq), _lib.stream())
+    return wq
+
+
+def act_quant(x, Mp=None, nt=256, deps=()):
+    """x bf16 [M, K] -> (xq int8 [Mp, K], xscale f32 [Mp]): per-token symmetric INT8, rows >= M zero."""
+    _lib.require_cuda(x)
+    M, K = _bf16(x).shape
+    Mp = Mp or pad_rows(M)
+    xq = torch.empty((Mp, K), dtype=torch.int8, device=x.device)
+    xs = torch.empty(Mp, dtype=torch.float32, device=x.device)
+    _lib.call("scmx_act_quant", _lib.ptr(x), M, K, Mp, _lib.ptr(xq), _lib.ptr(xs), _lib.stream())
+    return xq, xs
+
+
+def _eps(eps):
+    return float(eps.reshape(-1)[0].item()) if isinstance(eps, torch.Tensor) else float(eps)
+
+
+def rmsnorm_quant(x, w, eps, Mp=None, deps=()):
+    """x [M, K] -> (xq int8 [Mp, K], xscale f32 [Mp]) of rms_norm(x, w, eps)."""
+    xq, xs, _ = _rmsnorm_quant(x, w, eps, Mp, False)
+    return xq, xs
+
+
+def rmsnorm_quant_n(x, w, eps, Mp=None, deps=()):
+    """rmsnorm_quant that also returns the normalized bf16 rows: (xq, xscale, xn [Mp, K])."""
+    return _rmsnorm_quant(x, w, eps, Mp, True)
+
+
+def _rmsnorm_quant(x, w, eps, Mp, want_n):
+    _lib.require_cuda(x, w)
+    M, K = _bf16(x).shape
+    assert w.shape == (K,) and w.dtype == torch.bfloat16
+    Mp = Mp or pad_rows(M)
+    xq = torch.empty((Mp, K), dtype=torch.int8, device=x.device)
+    xs = torch.empty(Mp, dtype=torch.float32, device=x.device)
+    xn = torch.empty((Mp, K), dtype=torch.bfloat16, device=x.device) if want_n else None
+    _lib.call("scmx_rmsnorm_quant", _lib.ptr(x), _lib.ptr(w), _eps(eps), M, K, Mp, _lib.ptr(xq), _lib.ptr(xs),
+              _lib.ptr(xn), _lib.stream())
+    return xq, xs, xn
+
+
+def mm_i8_i32(xq, wq, deps=(), tile=None):
+    """INT8 [M, K] x INT8 [N, K]^T -> INT32 [M, N] (exact)."""
+    _lib.require_cuda(xq, wq)
+    (M, K), N = xq.shape, wq.shape[0]
+    assert xq.dtype == torch.int8 and wq.dtype == torch.int8 and wq.shape[1] == K
+    assert M % TM == 0 and N % 32 == 0, (M, N, TM)
+    acc = torch.empty((M, N), dtype=torch.int32, device=xq.device)
+    _lib.call("scmx_mm_i8", _lib.ptr(xq), _lib.ptr(wq), M, N, K, 0, None, None, None, _lib.ptr(acc),
+              _lib.ptr(_lib.status_buffer()), _lib.stream())
+    return acc
+
+
+def mm_epi(xq, wq, xscale, wscale, epi, dtype=torch.bfloat16, res=None, deps=(), tile=None):
+    """INT8 GEMM + fused epilogue (EPI 1: scaled bf16, 2: + residual, 3: SwiGLU of interleaved gate/up -> [M, N/2])."""
+    _lib.require_cuda(xq, wq, xscale, wscale, res)
+    (M, K), N = xq.shape, wq.shape[0]
+    assert dtype == torch.bfloat16, "outputs are bfloat16"
+    assert epi in (1, 2, 3)
+    assert M % TM == 0 and N % 32 == 0 and (epi != 2 or tuple(res.shape) == (M, N)), (M, N, TM)
+    assert xscale.shape == (M,) and wscale.shape == (N,)
+    out = torch.empty((M, N // 2 if epi == 3 else N), dtype=torch.bfloat16, device=xq.device)
+    _lib.call("scmx_mm_i8", _lib.ptr(xq), _lib.ptr(wq), M, N, K, epi, _lib.ptr(xscale), _lib.ptr(wscale),
+              _lib.ptr(res) if epi == 2 else None, _lib.ptr(out), _lib.ptr(_lib.status_buffer()), _lib.stream())
+    return out
+
+
+def interleave_gate_up(Fdim):
+    """Row permutation of [gate (F rows); up (F rows)] into groups g_2p, g_2p+1, u_2p, u_2p+1 for EPI 3."""
+    p = np.arange(Fdim // 2)
+    return np.stack([2 * p, 2 * p + 1, Fdim + 2 * p, Fdim + 2 * p + 1], 1).reshape(-1)
+
+
+def res_epilogue(acc, xscale, wscale, res, deps=()):
+    """h = res + bf16(acc * xscale * wscale) from INT32 accumulators."""
+    _lib.require_cuda(acc, xscale, wscale, res)
+    Mp, N = acc.shape
+    assert res.shape == (Mp, N) and res.dtype == torch.bfloat16 and acc.dtype == torch.int32
+    h = torch.empty((Mp, N), dtype=torch.bfloat16, device=acc.device)
+    _lib.call("scmx_res_epilogue", _lib.ptr(acc), _lib.ptr(xscale), _lib.ptr(wscale), _lib.ptr(res), Mp, N, _lib.ptr(h),
+              _lib.stream())
+    return h
+
+
+def res_norm_quant(acc, xscale, wscale, res, w, eps, deps=()):
+    """h = res + bf16(acc * xscale * wscale); returns (h [Mp, K], xq, xscale') of rms_norm(h)."""
+    h = res_epilogue(acc, xscale, wscale, res)
+    xq, xs = rmsnorm_quant(h, w, eps, h.shape[0])
+    return h, xq, xs
+
+
+def swiglu_quant(acc, xscale, wscale, dtype=torch.bfloat16, nt=512, deps=()):
+    """acc int32 [Mp, 2F] (gate | up) -> (xq int8 [Mp, F], xscale f32 [Mp]) of swiglu(bf16 gate, bf16 up)."""
+    _lib.require_cuda(acc, xscale, wscale)
+    Mp, F2 = acc.shape
+    Fd = F2 // 2
+    assert acc.dtype == torch.int32 and Fd % 4 == 0
+    xq = torch.empty((Mp, Fd), dtype=torch.int8, device=acc.device)
+    xs = torch.empty(Mp, dtype=torch.float32, device=acc.device)
+    _lib.call("scmx_swiglu_quant", _lib.ptr(acc), _lib.ptr(xscale), _lib.ptr(wscale), Mp, Fd, _lib.ptr(xq), _lib.ptr(xs),
+              _lib.stream())
+    return xq, xs
+
+
+def sc_swiglu(g, u):
+    """Elementwise bf16-stepwise SiLU(g) * u (the device function of the EPI 3 epilogue) on bf16 tensors."""
+    _lib.require_cuda(g, u)
+    assert g.dtype == torch.bfloat16 and u.dtype == torch.bfloat16 and g.shape == u.shape
+    out = torch.empty_like(g)
+    _lib.call("scmx_swiglu", _lib.ptr(g), _lib.ptr(u), g.numel(), _lib.ptr(out), _lib.stream())
+    return out
+
+
+def set_gemm_tile(bn=0):
+    """Tuning hint for the GEMM N tile (0 automatic, 128, 256)."""
+    _lib.call("scmx_set_gemm_tile", bn)

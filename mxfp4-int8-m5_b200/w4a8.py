@@ -1,0 +1,58 @@
+"""Unfused W4A8 linear layer and weight packing, mirroring the reference's e2e/w4a8_mlx.py (W4A8Linear, pack_linear)
+and the row-concatenated PackedWeight of e2e/fused_qwen3.py:35-59, as torch modules over libscmx."""
+import numpy as np
+import torch
+
+from . import sc_format as F
+from . import sc_kernels as S
+
+
+def pack_linear(w):
+    """(N, K) float weights -> (codes uint32 [N*K/8], shifts uint8 [N, K/32], wscale f32 [N]) as NumPy: the byte-shift
+    layout of the reference's pack_linear (one shift byte per 32-block)."""
+    codes, bc, ws, _ = F.quantize(np.asarray(w, dtype=np.float64))
+    shifts = ((bc[..., None] >> (2 * np.arange(4, dtype=np.uint8))) & 3).reshape(bc.shape[0], -1).astype(np.uint8)
+    return codes, shifts, ws
+
+
+class PackedWeight:
+    """Row concatenation of packed matrices (exact: the format is per output row), optional row permutation
+    (e.g. interleave_gate_up for the SwiGLU epilogue); holds CUDA tensors."""
+
+    def __init__(self, parts, perm=None, resident=False, device="cuda"):
+        codes = np.concatenate([np.asarray(p[0], np.uint32).reshape(p[1].shape[0], -1) for p in parts])
+        bc = np.concatenate([np.asarray(p[1], np.uint8) for p in parts])
+        ws = np.concatenate([np.asarray(p[2], np.float32) for p in parts])
+        if perm is not None:
+            codes, bc, ws = codes[perm], bc[perm], ws[perm]
+        self.N, self.K = codes.shape[0], codes.shape[1] * 8
+        self.codes, self.bcodes, self.wscale = F.to_device(codes.reshape(-1), bc, ws, device)
+        self.wq = S.unpack_i8(self.codes, self.bcodes, self.N, self.K) if resident else None
+
+    def int8(self):
+        return self.wq if self.wq is not None else S.unpack_i8(self.codes, self.bcodes, self.N, self.K)
+
+
+class W4A8Linear(torch.nn.Module):
+    """Bias-free linear y = x W^T with SC-MXFP4 weights computed as INT8 x INT8 on the tensor cores:
+    act_quant -> (unpack) -> tcgen05 GEMM with the scaling epilogue.  resident_int8=True keeps the unpacked INT8
+    operand in memory instead of decoding it per call."""
+
+    def __init__(self, codes, shifts, wscale, resident_int8=False, device="cuda"):
+        super().__init__()
+        shifts = np.asarray(shifts, np.uint8)
+        self.N, self.K = shifts.shape[0], shifts.shape[1] * 32
+        c, b, s = F.from_shift_layout(np.asarray(codes, np.uint32), shifts, wscale)
+        self.codes, self.bcodes, self.wscale = F.to_device(c, b, s, device)
+        self.wq = S.unpack_i8(self.codes, self.bcodes, self.N, self.K) if resident_int8 else None
+
+    def int8_weight(self):
+        return self.wq if self.wq is not None else S.unpack_i8(self.codes, self.bcodes, self.N, self.K)
+
+    def forward(self, x):
+        lead, K = x.shape[:-1], x.shape[-1]
+        x2 = x.reshape(-1, K).to(torch.bfloat16).contiguous()
+        M = x2.shape[0]
+        xq, xs = S.act_quant(x2)                      # pads to a multiple of the M tile; padded rows are zero
+        y = S.mm_epi(xq, self.int8_weight(), xs, self.wscale, 1)
+        return y[:M].reshape(*lead, self.N).to(x.dtype)

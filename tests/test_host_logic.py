@@ -1,0 +1,89 @@
+"""CPU: host-side logic of the package (layout helpers, Format checks), the C-ABI library's exports, and the
+argument validation every entry point performs before touching the GPU."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol(scmx):
+    hdr = open(os.path.join(ROOT, "include", "scmx.h")).read()
+    declared = set(re.findall(r"\b(scmx_[a-z0-9_]+)\s*\(", hdr))
+    assert len(declared) >= 18
+    h = ctypes.CDLL(scmx._lib.LIB_PATH)
+    for name in declared:
+        assert hasattr(h, name), f"{name} declared in include/scmx.h but not exported"
+    assert declared == set(scmx._lib.SIGNATURES), "python binding and header disagree"
+    assert scmx._lib.lib().scmx_abi_version() == 1
+
+
+def test_pack_rows_decode_against_reference_vectors(scmx, golden):
+    F = scmx.sc_format
+    fmt = F.Format(block=16, mult=(1, 2, 3, 4, 5, 6, 8, 10), bc_bits=4)
+    cc, bb, _ = F.pack_rows(golden["generic_code4"], golden["generic_bcode"], np.ones(8), fmt)
+    assert np.array_equal(cc, golden["generic_codes"]) and np.array_equal(bb, golden["generic_bcodes"])
+    assert np.array_equal(F.decode_numpy(cc, bb, 8, 256, fmt), golden["generic_q"])
+    for tag in "abc":
+        qw = golden[f"quantize_{tag}_qw"]
+        assert np.array_equal(F.decode_numpy(golden[f"quantize_{tag}_codes"], golden[f"quantize_{tag}_bcodes"], *qw.shape), qw)
+
+
+def test_from_shift_layout_roundtrip(scmx, golden):
+    F = scmx.sc_format
+    bc = golden["quantize_a_bcodes"]
+    shifts = ((bc[..., None] >> (2 * np.arange(4, dtype=np.uint8))) & 3).reshape(bc.shape[0], -1)
+    c, b, s = F.from_shift_layout(golden["quantize_a_codes"], shifts, golden["quantize_a_wscale"])
+    assert np.array_equal(b, bc) and np.array_equal(c, golden["quantize_a_codes"])
+
+
+def test_format_checks(scmx):
+    F = scmx.sc_format
+    assert F.DEFAULT.bits_per_weight(4096) == pytest.approx(4 + 2 / 32 + 32 / 4096)
+    with pytest.raises(AssertionError):
+        F.Format(block=12)
+    with pytest.raises(AssertionError):
+        F.Format(mult=(1, 2, 4, 8, 16))          # does not fit 2-bit block codes
+    with pytest.raises(AssertionError):
+        F.Format(mult=(1, 2, 4, 11))             # 12 * 11 > 127
+    f = F.Format(block=16, mult=(1, 2, 3, 4, 5, 6, 8, 10), bc_bits=4).c_struct()
+    assert (f.block, f.bc_bits, f.n_mult, f.mult[7]) == (16, 4, 8, 10)
+
+
+def test_interleave_and_padding(scmx, golden):
+    S = scmx.sc_kernels
+    assert np.array_equal(S.interleave_gate_up(768), golden["perm_768"])
+    assert [S.pad_rows(m) for m in (1, 128, 129, 200)] == [128, 128, 256, 256]
+
+
+def test_entry_points_validate_before_launch(scmx):
+    """Bad shapes and formats are rejected on the host with an error string; nothing reaches the GPU."""
+    L = scmx._lib
+    lib = L.lib()
+    fmt = scmx.sc_format.DEFAULT.c_struct()
+    bad = scmx.sc_format.DEFAULT.c_struct()
+    bad.mult[3] = 11
+    assert lib.scmx_act_quant(None, 4, 7, 4, None, None, None) == -1
+    assert b"K % 8" in lib.scmx_last_error_string()
+    assert lib.scmx_unpack_i8(None, None, 4, 256, bad, None, None) == -2
+    assert b"INT8" in lib.scmx_last_error_string()
+    assert lib.scmx_quantize_sc_mxfp4(None, 0, 4, 100, None, None, None, None, None, None) == -1
+    assert lib.scmx_mm_i8(None, None, 128, 100, 256, 0, None, None, None, None, None, None) == -1
+    assert lib.scmx_mm_i8(None, None, 128, 128, 256, 1, None, None, None, ctypes.c_void_p(16), ctypes.c_void_p(16), None) == -1
+    assert lib.scmx_gemv(None, None, None, None, None, 6, 256, fmt, 1, None, None, 0, -1, 0, None, 0, None) == -1
+    assert lib.scmx_route_sort(None, 4, 2, 2000, 128, None, None, None, None, None, None) == -5
+    assert lib.scmx_moe_mm_i8(None, 10, None, None, ctypes.c_void_p(16), ctypes.c_void_p(16), 4, 128, 256, 0, None,
+                              ctypes.c_void_p(16), 64, ctypes.c_void_p(16), None) == -1
+    assert b"tm=64" in lib.scmx_last_error_string()
+    assert lib.scmx_set_gemm_tile(64) == -1 and lib.scmx_set_gemm_tile(0) == 0
+    with pytest.raises(L.ScmxError):
+        L.call("scmx_act_quant", None, 4, 7, 4, None, None, None)
+
+
+def test_no_cpu_fallback(scmx):
+    import torch
+    with pytest.raises(TypeError):
+        scmx.sc_kernels.act_quant(torch.zeros(4, 64, dtype=torch.bfloat16))
