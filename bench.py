@@ -1,0 +1,455 @@
+"""Benchmark of the SC-MXFP4 W4A8 hot path on B200.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload dense|moe]
+
+One step = one pass of the hot path over one batch of synthetic input.  Default workload (N = 1): the
+Qwen3-1.7B-shaped dense prefill, 28 layers x {qkv 4096x2048, o 2048x2048, gate|up 12288x2048, down 2048x6144} at
+M = 2048 tokens, every projection SC-MXFP4-packed from N(0, 0.02) weights; per layer the chain is
+rmsnorm_quant -> qkv GEMM (EPI 1) | act_quant -> o GEMM (+residual) -> rmsnorm_quant -> gate|up GEMM (SwiGLU) ->
+act_quant -> down GEMM (+residual), each GEMM preceded by the 4-bit -> INT8 weight decode.  The metric is W4A8 GEMM
+TOPS = 2 * M * sum(N K) * layers / step time (algorithmic ops only).  The same JSON line also reports the decode GEMV
+(GB/s over the 717.9 MB of packed weights) and one OLMoE-shaped MoE half-block (tokens/s).
+
+`--impl reference` times the CPU restatement of the reference's NumPy path (oracle/) on the host cores.
+"""
+import argparse
+import importlib
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN = dict(layers=28, M=2048, groups=dict(qkv=(4096, 2048), o=(2048, 2048), gu=(12288, 2048), down=(2048, 6144)))
+OLMOE = dict(layers=16, tokens=4096, D=2048, F=1024, E=64, topk=8)
+
+
+def qwen_ops(M=QWEN["M"], layers=QWEN["layers"]):
+    return 2 * M * sum(n * k for n, k in QWEN["groups"].values()) * layers
+
+
+def gemv_bytes(n, k):
+    """Algorithmic bytes of one SC-MXFP4 GEMV: codes + 2-bit block codes + row scales + xq, xs + bf16 out."""
+    return n * k // 2 + n * k // 128 + 4 * n + k + 4 + 2 * n
+
+
+# ------------------------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx, self.proc, self.path = gpu_index, None, None
+
+    def __enter__(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms",
+                                          "100", "-i", str(self.idx)], stdout=open(self.path, "w"),
+                                         stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            self.proc.wait()
+
+    def summary(self):
+        out = dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0)
+        if not self.path or not os.path.exists(self.path):
+            return out
+        sm, mx, reasons = [], [], set()
+        for line in open(self.path):
+            f = [c.strip() for c in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if sm:
+            busy = [s for s in sm if s > 0.5 * max(sm)] or sm
+            out.update(sm_mhz=float(np.median(busy)), sm_max_mhz=max(mx), samples=len(sm))
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def peaks():
+    p = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        m = json.load(open(path))
+        p.update(hbm_gbs=m["hbm_gbs"], bf16_tflops=m["bf16_tflops"],
+                 bf16_tflops_sustained=m.get("bf16_tflops_sustained", m["bf16_tflops"]), source="measured")
+    return p
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the oracle's restatement of the reference NumPy path on the host cores
+# ------------------------------------------------------------------------------------------------------------------
+def cpu_dense_layer_sample(seed=0, M=QWEN["M"]):
+    """One Qwen3-1.7B-shaped layer (4 GEMM groups) at M tokens through the oracle: act-quant (float32 recipe), INT32
+    GEMM via float64 BLAS, scaling epilogue.  Weights are random INT8 operands in the quantizer's range (packing is
+    a load-time step and is not part of the per-step path).  Returns (seconds, ops)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import scmx_oracle as O
+    rng = np.random.default_rng(seed)
+    ws = {g: (rng.integers(-96, 97, nk).astype(np.int8), np.full(nk[0], 2.0 ** -9, np.float32)) for g, nk in QWEN["groups"].items()}
+    xs_in = {g: O.bf16_round(rng.standard_normal((M, nk[1])).astype(np.float32)) for g, nk in QWEN["groups"].items()}
+    res = O.bf16_round(rng.standard_normal((M, 2048)).astype(np.float32))
+    t0 = time.perf_counter()
+    for g, (wq, wsc) in ws.items():
+        xq, xs = O.act_quant(xs_in[g])
+        acc = O.gemm_i32(xq, wq)
+        if g == "gu":
+            O.epilogue(acc, xs, wsc, 3)
+        elif g == "qkv":
+            O.epilogue(acc, xs, wsc, 1)
+        else:
+            O.epilogue(acc, xs, wsc, 2, res)
+    dt = time.perf_counter() - t0
+    return dt, qwen_ops(M, 1)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count()
+    times = []
+    for i in range(args.warmup + args.steps):
+        dt, ops = cpu_dense_layer_sample(seed=i)
+        if i >= args.warmup:
+            times.append(dt)
+    t = float(np.mean(times))
+    val = ops / t / 1e12
+    line = dict(impl="reference", metric="w4a8_gemm_tops", value=val, unit="TOPS", n_gpus=args.gpus, steps=args.steps,
+                warmup=args.warmup, ms_per_step=t * 1e3, higher_is_better=True, scaling="strong", vs_baseline=None,
+                dtype="int8", data="synthetic",
+                config=dict(workload="qwen3-1.7b-shaped dense prefill, M=2048, SC-MXFP4 W4A8", sample="1 of 28 layers per step"),
+                cpu_baseline=dict(value=val, unit="TOPS", cores=cores, kind="port",
+                                  sample="one layer (4 GEMM groups) at M=2048 per step: act-quant + f64-BLAS INT32 GEMM + epilogue"),
+                e2e=dict(value=val, unit="TOPS", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------------------------
+class DenseModel:
+    """Packed weights of the Qwen3-1.7B-shaped stack (this rank's column shard) and the per-layer W4A8 chain."""
+
+    def __init__(self, pkg, torch, layers, M, shard=(0, 1), seed=0):
+        self.pkg, self.torch, self.M = pkg, torch, M
+        F, S = pkg.sc_format, pkg.sc_kernels
+        rank, world = shard
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        self.layers = []
+        for li in range(layers):
+            lw = {}
+            for name, (n, k) in QWEN["groups"].items():
+                w = torch.randn((n, k), generator=g, device="cuda", dtype=torch.float32) * 0.02
+                if name == "gu":     # gate rows then up rows -> interleaved 4-row groups for the SwiGLU epilogue
+                    w = w[torch.from_numpy(S.interleave_gate_up(n // 2)).cuda()]
+                if world > 1:        # tensor parallel: this rank's block of output columns (weight rows)
+                    w = w[rank * n // world:(rank + 1) * n // world].contiguous()
+                codes, bc, ws, _, _ = F.quantize_device(w.contiguous(), want_qw=False)
+                lw[name] = (codes, bc, ws, w.shape[0], k)
+            self.layers.append(lw)
+        self.nw = torch.ones(2048, dtype=torch.bfloat16, device="cuda")
+        self.launches_per_layer = 12
+
+    def packed_bytes(self):
+        return sum(c.numel() * 4 + b.numel() + s.numel() * 4 for lw in self.layers for (c, b, s, _, _) in lw.values())
+
+    def gemm(self, lw, name, xq, xs, epi, res=None, events=None):
+        S = self.pkg.sc_kernels
+        codes, bc, ws, n, k = lw[name]
+        wq = S.unpack_i8(codes, bc, n, k)
+        if events is not None:
+            e0, e1 = self.torch.cuda.Event(enable_timing=True), self.torch.cuda.Event(enable_timing=True)
+            e0.record()
+        y = S.mm_epi(xq, wq, xs, ws, epi, res=res)
+        if events is not None:
+            e1.record()
+            events.append((e0, e1, 2 * xq.shape[0] * n * k))
+        return y
+
+    def step(self, h, o, events=None):
+        """h [M, 2048] bf16 residual stream, o [M, 2048] bf16 stand-in for the attention output (attention itself is
+        outside the W4A8 path).  Returns the final residual stream."""
+        S = self.pkg.sc_kernels
+        M = self.M
+        for lw in self.layers:
+            xq, xs = S.rmsnorm_quant(h, self.nw, 1e-6, M)
+            self.gemm(lw, "qkv", xq, xs, 1, events=events)
+            oq, os_ = S.act_quant(o, M)
+            h = self.gemm(lw, "o", oq, os_, 2, res=h, events=events)
+            xq, xs = S.rmsnorm_quant(h, self.nw, 1e-6, M)
+            act = self.gemm(lw, "gu", xq, xs, 3, events=events)
+            aq, as_ = S.act_quant(act, M)
+            h = self.gemm(lw, "down", aq, as_, 2, res=h, events=events)
+        return h
+
+
+def bench_decode(pkg, torch, model, reps=3):
+    """Batch-1 decode GEMVs over every packed weight set of the stack (nothing L2-resident across a pass)."""
+    G = pkg.sc_decode
+    xq = {k: torch.randint(-127, 128, (k,), dtype=torch.int8, device="cuda") for k in (2048, 6144)}
+    xs = torch.full((1,), 0.01, device="cuda")
+    res = torch.zeros(2048, dtype=torch.bfloat16, device="cuda")
+
+    def one_pass():
+        for lw in model.layers:
+            for name, epi in (("qkv", 1), ("o", 2), ("gu", 3), ("down", 2)):
+                codes, bc, ws, n, k = lw[name]
+                G.gemv(xq[k], codes, bc, xs, ws, n, epi, res=res if epi == 2 else None)
+    one_pass()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    try:
+        with torch.cuda.graph(g):
+            one_pass()
+        run = g.replay
+    except Exception:
+        run = one_pass
+    for _ in range(2):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    nbytes = sum(gemv_bytes(n, k) for lw in model.layers for (_, _, _, n, k) in lw.values())
+    return dict(ms_per_step=ms, gemv_per_step=4 * len(model.layers), bytes_per_step=nbytes, gbs=nbytes / ms / 1e6,
+                us_per_gemv=ms * 1e3 / (4 * len(model.layers)))
+
+
+class MoeLayer:
+    """One OLMoE-shaped MoE half-block: 64 experts, gate|up [2048, 2048] (interleaved) and down [2048, 1024] each."""
+
+    def __init__(self, pkg, torch, cfg=OLMOE, distinct=4, seed=0):
+        F, S = pkg.sc_format, pkg.sc_kernels
+        self.pkg, self.torch, self.cfg = pkg, torch, cfg
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        D, Fd, E = cfg["D"], cfg["F"], cfg["E"]
+        perm = torch.from_numpy(S.interleave_gate_up(Fd)).cuda()
+
+        def pack(n, k, p=None):
+            cs, bs, ss = [], [], []
+            for e in range(E):
+                w = torch.randn((n, k), generator=g, device="cuda") * 0.02
+                if p is not None:
+                    w = w[p]
+                c, b, s, _, _ = F.quantize_device(w.contiguous(), want_qw=False)
+                cs.append(c); bs.append(b); ss.append(s)
+            return torch.stack(cs), torch.stack(bs), torch.stack(ss)
+        self.gu = pack(2 * Fd, D, perm)
+        self.dn = pack(D, Fd)
+        self.nw = torch.ones(D, dtype=torch.bfloat16, device="cuda")
+
+    def step(self, h, logits):
+        S, M_ = self.pkg.sc_kernels, self.pkg.sc_moe
+        c = self.cfg
+        L, E, k, D, Fd = c["tokens"], c["E"], c["topk"], c["D"], c["F"]
+        R = L * k
+        xq, xs = S.rmsnorm_quant(h, self.nw, 1e-5, L)
+        inds, scores = M_.router_topk(logits, k)
+        pos, tok, es, off, ts, mt = M_.route_sort(inds, E, 128)
+        xq_s, xs_s = M_.gather_rows(xq, xs, tok, R)
+        act = M_.moe_mm(xq_s, R, *self.gu, off, ts, mt, 2 * Fd, 3, xs_s)
+        xq2, xs2 = S.act_quant(act, R + 128)
+        yd = M_.moe_mm(xq2, R, *self.dn, off, ts, mt, D, 1, xs2)
+        hout, _, _ = M_.moe_combine(yd, pos, scores, h, self.nw, 1e-5, L)
+        return hout
+
+
+def bench_moe(pkg, torch, reps=5):
+    c = OLMOE
+    layer = MoeLayer(pkg, torch)
+    g = torch.Generator(device="cuda").manual_seed(1)
+    h = torch.randn((c["tokens"], c["D"]), generator=g, device="cuda").to(torch.bfloat16)
+    logits = torch.randn((c["tokens"], c["E"]), generator=g, device="cuda")
+    for _ in range(3):
+        layer.step(h, logits)
+    torch.cuda.synchronize()
+    pkg._lib.check_status()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        layer.step(h, logits)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    ops = 2 * c["tokens"] * c["topk"] * 3 * c["F"] * c["D"]
+    return dict(ms_per_half_block=ms, tokens_per_s_one_layer=c["tokens"] / ms * 1e3,
+                tokens_per_s_16_layers=c["tokens"] / (ms * c["layers"]) * 1e3, tops=ops / ms / 1e9)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    pkg = importlib.import_module("mxfp4-int8-m5_b200")
+    pk = peaks()
+    M, layers = QWEN["M"], QWEN["layers"]
+    model = DenseModel(pkg, torch, layers, M, shard=(rank, world))
+    g = torch.Generator(device="cuda").manual_seed(123 + rank)
+    h0 = torch.randn((M, 2048), generator=g, device="cuda").to(torch.bfloat16)
+    o0 = torch.randn((M, 2048), generator=g, device="cuda").to(torch.bfloat16)
+    tp = None
+    if world > 1:
+        par = importlib.import_module("mxfp4-int8-m5_b200.parallel")
+        tp = par.TensorParallelDense(pkg, model, dist)
+
+    def step(h, o, events=None):
+        return tp.step(h, o) if tp is not None else model.step(h, o, events)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- warm-up (eager), then capture the step in a CUDA graph: 336 launches per step are launch-bound from Python
+    out = step(h0, o0)
+    torch.cuda.synchronize()
+    pkg._lib.check_status()
+    graph = None
+    if world == 1 and not args.no_graph:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = step(h0, o0)
+        except Exception as e:   # noqa: BLE001
+            print(f"# CUDA graph capture unavailable ({e}); timing eager launches", file=sys.stderr)
+            graph = None
+    run = graph.replay if graph is not None else (lambda: step(h0, o0))
+    for _ in range(max(args.warmup, 3)):
+        run()
+    barrier()
+    # ---- timed: K steps, CUDA events on the launching stream, max over ranks.  The 717.9 MB of packed weights and the
+    # INT8 scratch exceed L2 (126 MB), so every step streams its weights from HBM (no explicit flush needed).
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as cs:
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            run()
+        e1.record()
+        barrier()
+    clocks = cs.summary()
+    ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    pkg._lib.check_status()
+    ops = qwen_ops()
+    value = ops / ms / 1e9
+
+    # ---- e2e: host buffers in, host result out, through the public API
+    hp, op_, outp = h0.cpu().pin_memory(), o0.cpu().pin_memory(), torch.empty_like(h0, device="cpu").pin_memory()
+
+    def e2e_step():
+        h0.copy_(hp, non_blocking=True)          # the step's inputs come from pinned host memory ...
+        o0.copy_(op_, non_blocking=True)
+        if graph is not None:
+            graph.replay()
+            outp.copy_(out, non_blocking=True)   # ... and its result goes back to the host
+        else:
+            outp.copy_(step(h0, o0), non_blocking=True)
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms_e2e], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_e2e = float(t.item())
+    e2e = dict(value=ops / ms_e2e / 1e9, unit="TOPS", h2d_bytes_per_step=hp.numel() * 2 + op_.numel() * 2,
+               d2h_bytes_per_step=outp.numel() * 2, ms_per_step=ms_e2e)
+
+    line = dict(metric="w4a8_gemm_tops", value=value, unit="TOPS", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
+                ms_per_step=ms, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="int8", data="synthetic",
+                config=dict(workload="qwen3-1.7b-shaped dense prefill: 28 layers x (qkv, o, gate|up, down), M=2048 tokens, "
+                                     "SC-MXFP4 W4A8, random-init N(0,0.02) weights",
+                            parallelism="single GPU" if world == 1 else f"tp{world} (output columns)",
+                            l2="inputs larger than L2: 718 MB of packed weights per step", cuda_graph=graph is not None),
+                clocks=clocks, e2e=e2e, gpu_launches=model.launches_per_layer * layers * args.steps)
+
+    if rank == 0 and world == 1:
+        # ---- roofline of the dominant kernel (the tcgen05 GEMM), timed live with CUDA events around each launch
+        ev = []
+        model.step(h0, o0, events=ev)
+        model.step(h0, o0, events=(ev := []))
+        torch.cuda.synchronize()
+        gemm_ms = sum(a.elapsed_time(b) for a, b, _ in ev)
+        gemm_ops = sum(o for _, _, o in ev)
+        peak = 2 * pk["bf16_tflops_sustained"]
+        ach = gemm_ops / gemm_ms / 1e9
+        line["roofline"] = dict(kernel="gemm_i8_kernel (tcgen05 kind::i8)", bound="tensor", achieved=ach, peak=peak, unit="TOP/s",
+                                frac=ach / peak, traffic=None, launches=len(ev), avg_launch_us=gemm_ms * 1e3 / len(ev),
+                                peak_note=f"2 x bf16_tflops_sustained of {pk['source']} peaks (INT8 dense rate = 2 x bf16); "
+                                          f"nominal 4500: frac_nominal={ach / 4500:.3f}")
+        line["decode"] = bench_decode(pkg, torch, model)
+        line["decode"]["hbm_frac"] = line["decode"]["gbs"] / pk["hbm_gbs"]
+        del model.layers[4:]
+        torch.cuda.empty_cache()
+        try:
+            line["moe"] = bench_moe(pkg, torch)
+        except Exception as e:   # noqa: BLE001
+            line["moe"] = dict(error=str(e))
+        pkg._lib.check_status()
+        dt, cops = cpu_dense_layer_sample()
+        line["cpu_baseline"] = dict(value=cops / dt / 1e12, unit="TOPS", cores=os.cpu_count(), kind="port",
+                                    sample="1 of 28 layers at M=2048: act-quant + f64-BLAS INT32 GEMM + epilogue (NumPy oracle)")
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
