@@ -53,7 +53,7 @@ class ClockSampler:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms",
-                                          "100", "-i", str(self.idx)], stdout=open(self.path, "w"),
+                                          "20", "-i", str(self.idx)], stdout=open(self.path, "w"),
                                          stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
@@ -437,6 +437,37 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_case(args):
+    """Small single-kernel cases for profiler captures (a few launches, a few hundred MB at most)."""
+    import torch
+    torch.cuda.set_device(0)
+    pkg = importlib.import_module("mxfp4-int8-m5_b200")
+    S, G, F = pkg.sc_kernels, pkg.sc_decode, pkg.sc_format
+    g = torch.Generator(device="cuda").manual_seed(0)
+    if args.case == "gemm":       # the gate|up GEMM of one layer: 2048 x 12288 x 2048, SwiGLU epilogue
+        xq = torch.randint(-127, 128, (2048, 2048), dtype=torch.int8, device="cuda", generator=g)
+        wq = torch.randint(-96, 97, (12288, 2048), dtype=torch.int8, device="cuda", generator=g)
+        xs = torch.full((2048,), 1e-2, device="cuda")
+        ws = torch.full((12288,), 2.0 ** -9, device="cuda")
+        for _ in range(4):
+            S.mm_epi(xq, wq, xs, ws, 3)
+    elif args.case == "gemv":     # 12 distinct gate|up weight sets (154 MB > L2), one GEMV each, two passes
+        sets = []
+        for _ in range(12):
+            w = torch.randn((12288, 2048), generator=g, device="cuda") * 0.02
+            sets.append(F.quantize_device(w, want_qw=False)[:3])
+        xq = torch.randint(-127, 128, (2048,), dtype=torch.int8, device="cuda", generator=g)
+        xs = torch.full((1,), 1e-2, device="cuda")
+        for _ in range(2):
+            for c, b, w_ in sets:
+                G.gemv(xq, c, b, xs, w_, 12288, 3)
+    else:
+        bench_moe(pkg, torch, reps=1)
+    torch.cuda.synchronize()
+    pkg._lib.check_status()
+    print(json.dumps(dict(case=args.case, ok=True)))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -444,8 +475,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--case", choices=["gemm", "gemv", "moe"], help="run one small kernel case (for profiler captures) and exit")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -58,13 +58,13 @@ __device__ __forceinline__ float rbf(float x) { return bf16_to_f32(f32_to_bf16(x
 
 // SiLU(g) * u with every step rounded to bf16: e = T(exp|g|), y = T(1/T(1+e)), sig = g<0 ? y : T(1-y),
 // silu = T(g*sig), out = T(silu*u).  Same step order as e2e/sc_kernels.py:319-328.
-__device__ __forceinline__ float swiglu_bf16(float g, float u) {
+__device__ __forceinline__ float silu_bf16(float g) {
     const float e = rbf(expf(fabsf(g)));
     const float y = rbf(__fdiv_rn(1.0f, rbf(__fadd_rn(1.0f, e))));
     const float sig = (g < 0.0f) ? y : rbf(__fsub_rn(1.0f, y));
-    const float silu = rbf(__fmul_rn(g, sig));
-    return rbf(__fmul_rn(silu, u));
+    return rbf(__fmul_rn(g, sig));
 }
+__device__ __forceinline__ float swiglu_bf16(float g, float u) { return rbf(__fmul_rn(silu_bf16(g), u)); }
 
 // y = T((float(acc) * xs) * ws), the scaling epilogue order of e2e/sc_kernels.py:101.
 __device__ __forceinline__ float scale_acc(int acc, float xs, float ws) {

@@ -2,13 +2,14 @@
 // tensor memory, operands staged in shared memory by TMA, and the scaling epilogue fused.  One kernel serves the
 // dense GEMM (xq [M,K] . wq [N,K]^T) and the grouped mixture-of-experts GEMM (row segments per expert).
 //
-// Persistent, warp-specialised CTA (one per SM, 192 threads):
+// Persistent, warp-specialised CTA (one per SM, 320 threads):
 //   warp 0      TMA producer: for every K block of 128 bytes loads a 128 x 128 tile of A and a BN x 128 tile of B into
 //               one of STAGES shared-memory stages (128-byte swizzle), completing on the stage's "full" mbarrier.
 //   warp 1      MMA issuer: one elected thread issues 4 tcgen05.mma (M128 x N BN x K32) per stage into one of two
 //               TMEM accumulators (BN columns each), tcgen05.commit frees the stage ("empty" mbarrier) and, after the
 //               last K block, publishes the accumulator ("tmem_full").  Also owns TMEM allocation.
-//   warps 2..5  epilogue: each warp reads its 32 TMEM lanes with tcgen05.ld (32 columns at a time), applies
+//   warps 2..9  epilogue: each warp reads its 32 TMEM lanes x half of the tile's columns with tcgen05.ld (32 columns at a
+//               time, the next load in flight while the current chunk is processed), applies
 //               T((float(acc) * xscale[m]) * wscale[n]) (+ residual, or SwiGLU on interleaved gate/up columns) and
 //               stores; then releases the accumulator ("tmem_empty") so the next tile's MMAs overlap this epilogue.
 //
@@ -24,6 +25,9 @@ constexpr int BM = 128;          // rows of A per tile = TMEM lanes
 constexpr int BK = 128;          // K bytes per stage = one 128-byte swizzle row
 constexpr int UMMA_K = 32;       // K per tcgen05.mma kind::i8
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // 2 s
+constexpr int EPI_WARPS = 8;
+constexpr int EPI_THREADS = 32 * EPI_WARPS;
+constexpr int CTA_THREADS = 64 + EPI_THREADS;   // TMA warp + MMA warp + epilogue warps
 
 struct GemmArgs {
     int M, N, K;                 // dense: rows of xq; grouped: total sorted rows R
@@ -37,6 +41,7 @@ struct GemmArgs {
     int E;
     int e_begin, e_end;          // grouped: experts handled by this launch; B rows are relative to e_begin
     int32_t* status;
+    const uint16_t* silu_lut;    // 65536-entry bf16 table of silu(g) indexed by the bf16 bits of g (EPI 3)
 };
 
 // ---- PTX wrappers ----------------------------------------------------------------------------------------------------
@@ -79,8 +84,8 @@ __device__ __forceinline__ int mbar_wait(uint32_t bar, uint32_t parity, volatile
         if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; return 1; }
     }
 }
-// Barrier among the 128 epilogue threads only (named barrier 1).
-__device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// Barrier among the epilogue threads only (named barrier 1).
+__device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory"); }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
     asm volatile(
@@ -189,6 +194,70 @@ __device__ __forceinline__ Tile get_tile(const GemmArgs& a, int t, int tiles_m, 
     return tl;
 }
 
+// ---- epilogue of 32 consecutive columns of one row ----------------------------------------------------------------------
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+__device__ __forceinline__ float bf16_lo(uint32_t p) { return __uint_as_float(p << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t p) { return __uint_as_float(p & 0xFFFF0000u); }
+__device__ __forceinline__ float scale2(uint32_t acc, float xs, float w) { return __fmul_rn(__fmul_rn((float)(int)acc, xs), w); }
+
+// r: 32 INT32 accumulators of columns n .. n+31 of row `row`; ws: the 32 staged weight scales.
+// EPI 1: T((float(acc)*xs)*ws); EPI 2: T(res + T(...)); EPI 3: per 4 columns [g0,g1,u0,u1] -> T(silu(T(g)) * T(u)) x 2, where
+// silu(g) = T(g * sigmoid_T(g)) is read from a 65536-entry table indexed by the bf16 bits of g (built once per device by
+// evaluating the step-by-step bf16 formula for every gate value, so the table holds exactly the bits the formula gives).
+__device__ __forceinline__ void epilogue_chunk(const GemmArgs& a, const uint32_t (&r)[32], const float* ws, float xs, int row,
+                                               int n, bool row_ok) {
+    if (!row_ok || n >= a.N) return;
+    if (a.epi == 0) {
+        uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<int32_t*>(a.out) + (size_t)row * a.N + n);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+    } else if (a.epi == 3) {
+        uint32_t pk[8];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            const float4 w4 = *reinterpret_cast<const float4*>(ws + 4 * g);
+            const uint32_t gg = pack_bf16x2(scale2(r[4 * g], xs, w4.x), scale2(r[4 * g + 1], xs, w4.y));
+            const uint32_t uu = pack_bf16x2(scale2(r[4 * g + 2], xs, w4.z), scale2(r[4 * g + 3], xs, w4.w));
+            const float s0 = __uint_as_float((uint32_t)__ldg(a.silu_lut + (gg & 0xFFFFu)) << 16);
+            const float s1 = __uint_as_float((uint32_t)__ldg(a.silu_lut + (gg >> 16)) << 16);
+            pk[g] = pack_bf16x2(__fmul_rn(s0, bf16_lo(uu)), __fmul_rn(s1, bf16_hi(uu)));
+        }
+        uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(a.out) + (size_t)row * (a.N / 2) + n / 2);
+        o[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        o[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+    } else {
+        uint32_t pk[16];
+        if (a.epi == 2) {
+            const uint4* rp = reinterpret_cast<const uint4*>(a.res + (size_t)row * a.N + n);
+            uint32_t rr[16];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint4 v = rp[j];
+                rr[4 * j] = v.x; rr[4 * j + 1] = v.y; rr[4 * j + 2] = v.z; rr[4 * j + 3] = v.w;
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const float2 w2 = *reinterpret_cast<const float2*>(ws + 2 * j);
+                const uint32_t y = pack_bf16x2(scale2(r[2 * j], xs, w2.x), scale2(r[2 * j + 1], xs, w2.y));
+                pk[j] = pack_bf16x2(__fadd_rn(bf16_lo(rr[j]), bf16_lo(y)), __fadd_rn(bf16_hi(rr[j]), bf16_hi(y)));
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const float2 w2 = *reinterpret_cast<const float2*>(ws + 2 * j);
+                pk[j] = pack_bf16x2(scale2(r[2 * j], xs, w2.x), scale2(r[2 * j + 1], xs, w2.y));
+            }
+        }
+        uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(a.out) + (size_t)row * a.N + n);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+    }
+}
+
 // ---- the kernel -----------------------------------------------------------------------------------------------------------
 template <int BN, int STAGES>
 struct Smem {
@@ -202,7 +271,7 @@ struct Smem {
 };
 
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(192, 1) gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA,
+__global__ void __launch_bounds__(CTA_THREADS, 1) gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA,
                                                           const __grid_constant__ CUtensorMap tmB, const GemmArgs a) {
     using L = Smem<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
@@ -224,7 +293,7 @@ __global__ void __launch_bounds__(192, 1) gemm_i8_kernel(const __grid_constant__
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar_tfull + 8 * i, 1);
-            mbar_init(bar_tempty + 8 * i, 4);      // one arrival per epilogue warp
+            mbar_init(bar_tempty + 8 * i, EPI_WARPS);      // one arrival per epilogue warp
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -290,72 +359,40 @@ __global__ void __launch_bounds__(192, 1) gemm_i8_kernel(const __grid_constant__
             }
         }
     } else {
-        // ------------------------------------------------ epilogue warps 2..5; TMEM lane quarter = warp % 4
+        // ------------------------------------------------ epilogue warps 2..9: TMEM lane quarter = warp % 4 (the quarter
+        // a warp may read), column half = (warp - 2) / 4.  Two warps per scheduler hide each other's latencies.
         const int q = warp & 3;
-        const int et = threadIdx.x - 64;          // 0..127 among the epilogue threads
+        const int chalf = (warp - 2) >> 2;
+        const int et = threadIdx.x - 64;          // 0..255 among the epilogue threads
+        constexpr int CHUNKS = BN / 64;           // 32-column chunks per warp
         uint32_t acc = 0, acc_phase = 0;
         for (int t = blockIdx.x; t < total && fail == 0; t += gridDim.x) {
             const Tile tl = get_tile<BN>(a, t, tiles_m, slot0);
             float* ws = ws_stage + acc * BN;
             if (a.epi != 0) {
-                for (int i = et; i < BN; i += 128) ws[i] = (tl.n0 + i < a.N) ? a.wscale[tl.wrow + i] : 0.0f;
+                for (int i = et; i < BN; i += EPI_THREADS) ws[i] = (tl.n0 + i < a.N) ? a.wscale[tl.wrow + i] : 0.0f;
             }
             if (int w = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) fail = w == 1 ? 4 : -1;
-            // the 128 epilogue threads agree on giving up (and see the staged scales) before anyone touches TMEM
+            // the epilogue threads agree on giving up (and see the staged scales) before anyone touches TMEM
             epilogue_bar();
             if (*abort_flag) { if (!fail) fail = -1; break; }
             tc_fence_after();
             const int row = tl.row0 + 32 * q + lane;
             const bool row_ok = row < tl.row_end;
             const float xs = (a.epi != 0 && row_ok) ? a.xscale[row] : 0.0f;
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + acc * BN + c * 32 + ((uint32_t)(32 * q) << 16), r);
+            const uint32_t taddr = tmem_base + acc * BN + chalf * (BN / 2) + ((uint32_t)(32 * q) << 16);
+            uint32_t r0[32], r1[32];
+            tmem_ld32(taddr, r0);
+            tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < CHUNKS; c += 2) {
+                // the next chunk's TMEM load is in flight while this chunk is converted and stored
+                tmem_ld32(taddr + (c + 1) * 32, r1);
+                epilogue_chunk(a, r0, ws + chalf * (BN / 2) + c * 32, xs, row, tl.n0 + chalf * (BN / 2) + c * 32, row_ok);
                 tmem_ld_wait();
-                const int n = tl.n0 + c * 32;
-                if (!row_ok || n >= a.N) continue;
-                if (a.epi == 0) {
-                    uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<int32_t*>(a.out) + (size_t)row * a.N + n);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) o[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-                } else if (a.epi == 3) {
-                    uint32_t pk[8];
-#pragma unroll
-                    for (int g = 0; g < 8; ++g) {
-                        const float4 w4 = *reinterpret_cast<const float4*>(ws + c * 32 + 4 * g);
-                        const float g0 = scale_acc((int)r[4 * g], xs, w4.x), g1 = scale_acc((int)r[4 * g + 1], xs, w4.y);
-                        const float u0 = scale_acc((int)r[4 * g + 2], xs, w4.z), u1 = scale_acc((int)r[4 * g + 3], xs, w4.w);
-                        pk[g] = f32_to_bf16(swiglu_bf16(g0, u0)) | ((uint32_t)f32_to_bf16(swiglu_bf16(g1, u1)) << 16);
-                    }
-                    uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(a.out) + (size_t)row * (a.N / 2) + n / 2);
-                    o[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                    o[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-                } else {
-                    uint32_t pk[16];
-                    uint32_t rr[16];
-                    if (a.epi == 2) {
-                        const uint4* rp = reinterpret_cast<const uint4*>(a.res + (size_t)row * a.N + n);
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const uint4 v = rp[j];
-                            rr[4 * j] = v.x; rr[4 * j + 1] = v.y; rr[4 * j + 2] = v.z; rr[4 * j + 3] = v.w;
-                        }
-                    }
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const float2 w2 = *reinterpret_cast<const float2*>(ws + c * 32 + 2 * j);
-                        float y0 = scale_acc((int)r[2 * j], xs, w2.x), y1 = scale_acc((int)r[2 * j + 1], xs, w2.y);
-                        if (a.epi == 2) {
-                            y0 = __fadd_rn(__uint_as_float(rr[j] << 16), y0);
-                            y1 = __fadd_rn(__uint_as_float(rr[j] & 0xFFFF0000u), y1);
-                        }
-                        pk[j] = f32_to_bf16(y0) | ((uint32_t)f32_to_bf16(y1) << 16);
-                    }
-                    uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(a.out) + (size_t)row * a.N + n);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) o[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
-                }
+                if (c + 2 < CHUNKS) tmem_ld32(taddr + (c + 2) * 32, r0);
+                epilogue_chunk(a, r1, ws + chalf * (BN / 2) + (c + 1) * 32, xs, row, tl.n0 + chalf * (BN / 2) + (c + 1) * 32, row_ok);
+                if (c + 2 < CHUNKS) tmem_ld_wait();
             }
             tc_fence_before();
             __syncwarp();
@@ -365,7 +402,6 @@ __global__ void __launch_bounds__(192, 1) gemm_i8_kernel(const __grid_constant__
         }
     }
 
-    // ---- shutdown: record a failed wait, let in-flight copies land, free TMEM
     // status[0]: 1 producer waited for a free stage, 2 MMA waited for a free accumulator, 3 MMA waited for operands,
     // 4 epilogue waited for an accumulator; status[1] CTA, status[2] thread.  Secondary give-ups (fail < 0) are not recorded.
     if (fail > 0) {
@@ -386,6 +422,39 @@ __global__ void __launch_bounds__(192, 1) gemm_i8_kernel(const __grid_constant__
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+
+// ---- SiLU table for the SwiGLU epilogue ----------------------------------------------------------------------------------
+// silu(g) = T(g * sigmoid_T(g)) depends on the bf16 gate alone, so the epilogue reads it from a table with one entry per bf16
+// bit pattern.  The table is filled on the device by the same step-by-step bf16 formula the row kernels use.
+__device__ __align__(256) uint16_t g_silu_lut[65536];
+
+__global__ void silu_lut_init_kernel() {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < 65536u) g_silu_lut[i] = f32_to_bf16(silu_bf16(bf16_to_f32((uint16_t)i)));
+}
+
+// Device address of the table for the current device; built on the first call per device (stream-ordered on `st`, followed
+// by one synchronisation of that stream so that later calls on other streams see it).
+static int silu_lut_ptr(cudaStream_t st, const uint16_t** out) {
+    static const uint16_t* ptrs[64] = {};
+    int dev = 0;
+    SCMX_CUDA_OK(cudaGetDevice(&dev));
+    SCMX_REQUIRE(dev >= 0 && dev < 64, SCMX_ELIMIT, "device ordinal %d out of range", dev);
+    if (!ptrs[dev]) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        SCMX_CUDA_OK(cudaStreamIsCapturing(st, &cap));
+        SCMX_REQUIRE(cap == cudaStreamCaptureStatusNone, SCMX_EINVAL,
+                     "the first SwiGLU-epilogue GEMM on a device builds a table: call it once outside stream capture");
+        void* p = nullptr;
+        SCMX_CUDA_OK(cudaGetSymbolAddress(&p, g_silu_lut));
+        silu_lut_init_kernel<<<256, 256, 0, st>>>();
+        SCMX_LAUNCH_OK("silu_lut_init_kernel");
+        SCMX_CUDA_OK(cudaStreamSynchronize(st));
+        ptrs[dev] = static_cast<const uint16_t*>(p);
+    }
+    *out = ptrs[dev];
+    return SCMX_OK;
+}
 
 // ---- host side ------------------------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -441,13 +510,17 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
         SCMX_CUDA_OK(cudaFuncSetAttribute(gemm_i8_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
         configured = true;
     }
-    gemm_i8_kernel<BN, STAGES><<<grid, 192, L::TOTAL, st>>>(tmA, tmB, a);
+    gemm_i8_kernel<BN, STAGES><<<grid, CTA_THREADS, L::TOTAL, st>>>(tmA, tmB, a);
     SCMX_LAUNCH_OK("gemm_i8_kernel");
     return SCMX_OK;
 }
 
 static int run_gemm(const int8_t* xq, int64_t a_rows, const int8_t* wq, int64_t b_rows, GemmArgs& a, cudaStream_t st) {
     int bn = g_bn_override ? g_bn_override : (a.N >= 256 ? 256 : 128);
+    if (a.epi == 3) {
+        int rc3 = silu_lut_ptr(st, &a.silu_lut);
+        if (rc3) return rc3;
+    }
     CUtensorMap tmA, tmB;
     int rc = make_map(&tmA, xq, a_rows, a.K, BM);
     if (rc) return rc;
