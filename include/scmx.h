@@ -132,6 +132,20 @@ int scmx_moe_mm(const int8_t* xq, int64_t R, const uint32_t* codes, const uint8_
                 const float* xscale, void* out, int tm, int experts_per_pass, int8_t* scratch, int64_t scratch_bytes,
                 int32_t* status, void* stream);
 
+/* scmx_moe_mm without a scratch argument; it has no counterpart in the reference (whose arrays are allocated by MLX).
+ * For hosts that cannot hand the library device memory at call time: a serving process that gave all of HBM to its own
+ * pool at start-up (a cudaMalloc there would fail, or stall the device mid-request), or a foreign-language runtime bound
+ * to this C ABI that owns no device allocator.  The decoded-INT8 staging area is a fixed 16 MiB array inside the library
+ * (two 8 MiB halves), held by every GPU that loads the library until the process exits.  The call allocates nothing.
+ * Limit: one decoded expert matrix must fit one half, N * K <= 8 MiB (8388608); larger shapes return SCMX_ELIMIT.
+ * The first call on a device looks up the array's device address (and, for epi 3, builds the SiLU table and
+ * synchronises the stream once): make that first call before any stream capture.  All calls share the one array:
+ * every byte read from it is rewritten by the same call first, so contents left by an earlier call are never used,
+ * but two calls whose kernels overlap on the GPU (different streams, or different threads on the same device) race. */
+int scmx_moe_mm_static(const int8_t* xq, int64_t R, const uint32_t* codes, const uint8_t* bcodes, const float* wscale,
+                       const int32_t* off, const int32_t* tstart, int E, int64_t N, int64_t K, const scmx_format* fmt,
+                       int epi, const float* xscale, void* out, int tm, int32_t* status, void* stream);
+
 /* Weighted sequential-bf16 sum of the topk expert rows + residual (+ next RMSNorm + INT8 when quant != 0).
  * Replaces fused_olmoe.moe_combine (e2e/fused_olmoe.py:45-97).  y bf16 [R,K], pos int32 [M*topk], scores bf16
  * [M,topk], res bf16 [Mp,K] -> h bf16 [Mp,K], xq int8 [Mp,K], xs f32 [Mp]. */

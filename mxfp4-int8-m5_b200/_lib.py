@@ -44,6 +44,8 @@ SIGNATURES = {
     "scmx_moe_mm_i8": [c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_int, c_vp, c_vp, c_int, c_vp, c_vp],
     "scmx_moe_mm": [c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, _FMT_P, c_int, c_vp, c_vp, c_int,
                     c_int, c_vp, c_i64, c_vp, c_vp],
+    "scmx_moe_mm_static": [c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, _FMT_P, c_int, c_vp, c_vp, c_int,
+                           c_vp, c_vp],
     "scmx_moe_combine": [c_vp, c_vp, c_vp, c_vp, c_vp, c_float, c_i64, c_i64, c_i64, c_int, c_int, c_vp, c_vp, c_vp,
                          c_vp],
     "scmx_gemv": [c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, _FMT_P, c_int, c_vp, c_vp, c_int, c_int, c_int, c_vp,

@@ -626,3 +626,76 @@ extern "C" int scmx_moe_mm(const int8_t* xq, int64_t R, const uint32_t* codes, c
     }
     return SCMX_OK;
 }
+
+// ---- grouped GEMM from packed weights with the scratch held inside the library ------------------------------------------
+// Some hosts of this library cannot give it scratch memory: a serving process that hands all of HBM to its own
+// KV-cache / activation pool at start-up has nothing left to cudaMalloc from later (and cudaMalloc would stall the device
+// in the middle of a request), and a runtime that binds the C ABI from another language often has no device allocator
+// at all.  For them the decoded-INT8 staging area of the grouped GEMM lives in this fixed array: two halves of 8 MiB,
+// resident on every GPU that loads the library until the process exits.
+namespace scmx {
+constexpr int64_t MOE_STATIC_HALF_BYTES = 8ll << 20;
+static __device__ __align__(256) int8_t g_moe_static_scratch[2 * MOE_STATIC_HALF_BYTES];
+
+// The array's name is only a host-side handle; kernels need its device address, looked up once per device with that
+// device current.
+static int moe_static_scratch_ptr(int8_t** out) {
+    static int8_t* ptrs[64] = {};
+    int dev = 0;
+    SCMX_CUDA_OK(cudaGetDevice(&dev));
+    SCMX_REQUIRE(dev >= 0 && dev < 64, SCMX_ELIMIT, "device ordinal %d out of range", dev);
+    if (!ptrs[dev]) {
+        int8_t* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress((void**)&p, g_moe_static_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            set_error("cudaGetSymbolAddress(g_moe_static_scratch) failed on device %d: %s", dev, cudaGetErrorString(e));
+            return SCMX_ECUDA;
+        }
+        ptrs[dev] = p;
+    }
+    *out = ptrs[dev];
+    return SCMX_OK;
+}
+}  // namespace scmx
+
+extern "C" int scmx_moe_mm_static(const int8_t* xq, int64_t R, const uint32_t* codes, const uint8_t* bcodes,
+                                  const float* wscale, const int32_t* off, const int32_t* tstart, int E, int64_t N, int64_t K,
+                                  const scmx_format* fmt, int epi, const float* xscale, void* out, int tm, int32_t* status,
+                                  void* stream) {
+    int rc = check_common("moe_mm_static", N, K, epi, xscale, wscale, out, status);
+    if (rc) return rc;
+    DevFormat f;
+    rc = make_dev_format(fmt, &f);
+    if (rc) return rc;
+    SCMX_REQUIRE(epi != 2, SCMX_EINVAL, "moe_mm_static: epi must be 0, 1 or 3");
+    SCMX_REQUIRE(tm == BM, SCMX_EINVAL, "moe_mm_static: tm=%d, the kernel's M tile is %d (pass tm=%d to route_sort)", tm, BM, BM);
+    SCMX_REQUIRE(E >= 1 && E <= 65536 && R >= 0 && R < (1ll << 30) && off && tstart, SCMX_EINVAL,
+                 "moe_mm_static: bad E / R / offsets");
+    SCMX_REQUIRE(N * K <= MOE_STATIC_HALF_BYTES, SCMX_ELIMIT,
+                 "moe_mm_static: one decoded expert matrix is N*K = %lld bytes, more than the %lld bytes of one half of the "
+                 "built-in scratch; use scmx_moe_mm with caller-provided scratch",
+                 (long long)(N * K), (long long)MOE_STATIC_HALF_BYTES);
+    if (R == 0) return SCMX_OK;
+    int8_t* scratch = nullptr;
+    rc = moe_static_scratch_ptr(&scratch);
+    if (rc) return rc;
+    const int epp = (int)(MOE_STATIC_HALF_BYTES / (N * K));      // experts decoded per pass (>= 1)
+    const int64_t half = MOE_STATIC_HALF_BYTES;
+    const int64_t wpe = N * K / 8;
+    const int64_t bpe = N * (K / (f.block * f.blocks_per_byte));
+    int pass = 0;
+    for (int e0 = 0; e0 < E; e0 += epp, ++pass) {
+        const int e1 = e0 + epp < E ? e0 + epp : E;
+        int8_t* buf = scratch + (pass & 1) * half;
+        // every byte the GEMM reads from `buf` is rewritten here first, so nothing left by an earlier call is ever used
+        rc = scmx_unpack_i8(codes + e0 * wpe, bcodes + e0 * bpe, (int64_t)(e1 - e0) * N, K, fmt, buf, stream);
+        if (rc) return rc;
+        GemmArgs a = {};
+        a.M = (int)R; a.N = (int)N; a.K = (int)K; a.epi = epi; a.xscale = xscale; a.wscale = wscale; a.out = out;
+        a.off = off; a.tstart = tstart; a.E = E; a.e_begin = e0; a.e_end = e1; a.status = status;
+        rc = run_gemm(xq, R, buf, (int64_t)(e1 - e0) * N, a, (cudaStream_t)stream);
+        if (rc) return rc;
+    }
+    return SCMX_OK;
+}
+
