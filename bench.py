@@ -150,60 +150,26 @@ def run_reference(args):
 # ------------------------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------------------------
-class DenseModel:
-    """Packed weights of the Qwen3-1.7B-shaped stack (this rank's column shard) and the per-layer W4A8 chain."""
-
-    def __init__(self, pkg, torch, layers, M, shard=(0, 1), seed=0):
-        self.pkg, self.torch, self.M = pkg, torch, M
-        F, S = pkg.sc_format, pkg.sc_kernels
-        rank, world = shard
-        g = torch.Generator(device="cuda").manual_seed(seed)
-        self.layers = []
-        for li in range(layers):
-            lw = {}
-            for name, (n, k) in QWEN["groups"].items():
-                w = torch.randn((n, k), generator=g, device="cuda", dtype=torch.float32) * 0.02
-                if name == "gu":     # gate rows then up rows -> interleaved 4-row groups for the SwiGLU epilogue
-                    w = w[torch.from_numpy(S.interleave_gate_up(n // 2)).cuda()]
-                if world > 1:        # tensor parallel: this rank's block of output columns (weight rows)
-                    w = w[rank * n // world:(rank + 1) * n // world].contiguous()
-                codes, bc, ws, _, _ = F.quantize_device(w.contiguous(), want_qw=False)
-                lw[name] = (codes, bc, ws, w.shape[0], k)
-            self.layers.append(lw)
-        self.nw = torch.ones(2048, dtype=torch.bfloat16, device="cuda")
-        self.launches_per_layer = 12
-
-    def packed_bytes(self):
-        return sum(c.numel() * 4 + b.numel() + s.numel() * 4 for lw in self.layers for (c, b, s, _, _) in lw.values())
-
-    def gemm(self, lw, name, xq, xs, epi, res=None, events=None):
-        S = self.pkg.sc_kernels
-        codes, bc, ws, n, k = lw[name]
-        wq = S.unpack_i8(codes, bc, n, k)
-        if events is not None:
-            e0, e1 = self.torch.cuda.Event(enable_timing=True), self.torch.cuda.Event(enable_timing=True)
-            e0.record()
-        y = S.mm_epi(xq, wq, xs, ws, epi, res=res)
-        if events is not None:
-            e1.record()
-            events.append((e0, e1, 2 * xq.shape[0] * n * k))
-        return y
-
-    def step(self, h, o, events=None):
-        """h [M, 2048] bf16 residual stream, o [M, 2048] bf16 stand-in for the attention output (attention itself is
-        outside the W4A8 path).  Returns the final residual stream."""
-        S = self.pkg.sc_kernels
-        M = self.M
-        for lw in self.layers:
-            xq, xs = S.rmsnorm_quant(h, self.nw, 1e-6, M)
-            self.gemm(lw, "qkv", xq, xs, 1, events=events)
-            oq, os_ = S.act_quant(o, M)
-            h = self.gemm(lw, "o", oq, os_, 2, res=h, events=events)
-            xq, xs = S.rmsnorm_quant(h, self.nw, 1e-6, M)
-            act = self.gemm(lw, "gu", xq, xs, 3, events=events)
-            aq, as_ = S.act_quant(act, M)
-            h = self.gemm(lw, "down", aq, as_, 2, res=h, events=events)
-        return h
+def build_dense_layers(pkg, torch, layers, shard=(0, 1), seed=0):
+    """Random-init N(0, 0.02) weights of the Qwen3-1.7B-shaped stack, SC-MXFP4-packed on the GPU; with world > 1 only this
+    rank's block of output columns (weight rows) is packed.  Every rank draws the same full matrices (same seed)."""
+    F, S, P = pkg.sc_format, pkg.sc_kernels, pkg.parallel
+    rank, world = shard
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    out = []
+    for _ in range(layers):
+        lw = {}
+        for name, (n, k) in QWEN["groups"].items():
+            w = torch.randn((n, k), generator=g, device="cuda", dtype=torch.float32) * 0.02
+            if name == "gu":     # gate rows then up rows -> interleaved 4-row groups for the SwiGLU epilogue
+                w = w[torch.from_numpy(S.interleave_gate_up(n // 2)).cuda()]
+            if world > 1:
+                r0, r1 = P.shard_rows(n, rank, world, 4)
+                w = w[r0:r1]
+            codes, bc, ws, _, _ = F.quantize_device(w.contiguous(), want_qw=False)
+            lw[name] = (codes, bc, ws, w.shape[0], k)
+        out.append(lw)
+    return out
 
 
 def bench_decode(pkg, torch, model, reps=3):
@@ -242,55 +208,46 @@ def bench_decode(pkg, torch, model, reps=3):
                 us_per_gemv=ms * 1e3 / (4 * len(model.layers)))
 
 
-class MoeLayer:
-    """One OLMoE-shaped MoE half-block: 64 experts, gate|up [2048, 2048] (interleaved) and down [2048, 1024] each."""
+def build_moe_block(pkg, torch, cfg=OLMOE, shard=(0, 1), seed=0, two_pass=False):
+    """One OLMoE-shaped MoE half-block: E experts, gate|up [2F, D] (rows interleaved) and down [D, F] each, N(0, 0.02),
+    packed on the GPU.  With world > 1 only this rank's experts are built (all ranks use the same per-expert seeds)."""
+    F, S = pkg.sc_format, pkg.sc_kernels
+    rank, world = shard
+    D, Fd, E = cfg["D"], cfg["F"], cfg["E"]
+    perm = torch.from_numpy(S.interleave_gate_up(Fd)).cuda()
+    e0, e1 = rank * E // world, (rank + 1) * E // world
 
-    def __init__(self, pkg, torch, cfg=OLMOE, distinct=4, seed=0):
-        F, S = pkg.sc_format, pkg.sc_kernels
-        self.pkg, self.torch, self.cfg = pkg, torch, cfg
-        g = torch.Generator(device="cuda").manual_seed(seed)
-        D, Fd, E = cfg["D"], cfg["F"], cfg["E"]
-        perm = torch.from_numpy(S.interleave_gate_up(Fd)).cuda()
-
-        def pack(n, k, p=None):
-            cs, bs, ss = [], [], []
-            for e in range(E):
-                w = torch.randn((n, k), generator=g, device="cuda") * 0.02
-                if p is not None:
-                    w = w[p]
-                c, b, s, _, _ = F.quantize_device(w.contiguous(), want_qw=False)
-                cs.append(c); bs.append(b); ss.append(s)
-            return torch.stack(cs), torch.stack(bs), torch.stack(ss)
-        self.gu = pack(2 * Fd, D, perm)
-        self.dn = pack(D, Fd)
-        self.nw = torch.ones(D, dtype=torch.bfloat16, device="cuda")
-
-    def step(self, h, logits):
-        S, M_ = self.pkg.sc_kernels, self.pkg.sc_moe
-        c = self.cfg
-        L, E, k, D, Fd = c["tokens"], c["E"], c["topk"], c["D"], c["F"]
-        R = L * k
-        xq, xs = S.rmsnorm_quant(h, self.nw, 1e-5, L)
-        inds, scores = M_.router_topk(logits, k)
-        pos, tok, es, off, ts, mt = M_.route_sort(inds, E, 128)
-        xq_s, xs_s = M_.gather_rows(xq, xs, tok, R)
-        act = M_.moe_mm(xq_s, R, *self.gu, off, ts, mt, 2 * Fd, 3, xs_s)
-        xq2, xs2 = S.act_quant(act, R + 128)
-        yd = M_.moe_mm(xq2, R, *self.dn, off, ts, mt, D, 1, xs2)
-        hout, _, _ = M_.moe_combine(yd, pos, scores, h, self.nw, 1e-5, L)
-        return hout
+    def pack(n, k, tag, p=None):
+        cs, bs, ss = [], [], []
+        for e in range(e0, e1):
+            g = torch.Generator(device="cuda").manual_seed(seed * 100003 + tag * 1009 + e)
+            w = torch.randn((n, k), generator=g, device="cuda") * 0.02
+            if p is not None:
+                w = w[p]
+            c, b, s_, _, _ = F.quantize_device(w.contiguous(), want_qw=False)
+            cs.append(c); bs.append(b); ss.append(s_)
+        return torch.stack(cs), torch.stack(bs), torch.stack(ss)
+    return pkg.fused_moe.MoeBlock(pack(2 * Fd, D, 1, perm), pack(D, Fd, 2), e1 - e0, cfg["topk"], D, Fd, two_pass=two_pass)
 
 
-def bench_moe(pkg, torch, reps=5):
+def bench_moe(pkg, torch, dist=None, reps=5):
+    """OLMoE-shaped MoE half-block at 4096 tokens: quant -> route -> (dispatch) -> two grouped GEMMs -> (return) -> combine.
+    With a process group: experts sharded by rank, tokens split by rank, NCCL all-to-all for dispatch and return."""
     c = OLMOE
-    layer = MoeLayer(pkg, torch)
+    world = dist.get_world_size() if dist is not None else 1
+    rank = dist.get_rank() if dist is not None else 0
+    blk = build_moe_block(pkg, torch, shard=(rank, world))
+    layer = pkg.parallel.ExpertParallelMoe(pkg, blk, c["E"], c["topk"]) if world > 1 else blk
+    Lr = c["tokens"] // world
     g = torch.Generator(device="cuda").manual_seed(1)
-    h = torch.randn((c["tokens"], c["D"]), generator=g, device="cuda").to(torch.bfloat16)
-    logits = torch.randn((c["tokens"], c["E"]), generator=g, device="cuda")
+    h = torch.randn((c["tokens"], c["D"]), generator=g, device="cuda").to(torch.bfloat16)[rank * Lr:(rank + 1) * Lr].contiguous()
+    logits = torch.randn((c["tokens"], c["E"]), generator=g, device="cuda")[rank * Lr:(rank + 1) * Lr].contiguous()
     for _ in range(3):
         layer.step(h, logits)
     torch.cuda.synchronize()
     pkg._lib.check_status()
+    if dist is not None:
+        dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(reps):
@@ -298,9 +255,61 @@ def bench_moe(pkg, torch, reps=5):
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / reps
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
     ops = 2 * c["tokens"] * c["topk"] * 3 * c["F"] * c["D"]
     return dict(ms_per_half_block=ms, tokens_per_s_one_layer=c["tokens"] / ms * 1e3,
-                tokens_per_s_16_layers=c["tokens"] / (ms * c["layers"]) * 1e3, tops=ops / ms / 1e9)
+                tokens_per_s_16_layers=c["tokens"] / (ms * c["layers"]) * 1e3, tops=ops / ms / 1e9,
+                parallelism="single GPU" if world == 1 else f"ep{world}: {c['E'] // world} experts and {Lr} tokens per GPU, NCCL all-to-all")
+
+
+def gemm_only_roofline(pkg, torch, stack, pk, reps=3):
+    """Average duration of the tcgen05 GEMM launches of one step, timed alone: every packed matrix is decoded to INT8
+    beforehand (1.4 GB, far beyond L2), then the 112 GEMMs (with their real epilogues) are replayed back to back from a
+    CUDA graph with events around the replay."""
+    S = pkg.sc_kernels
+    M = stack.M
+    g = torch.Generator(device="cuda").manual_seed(7)
+    wq = [{name: S.unpack_i8(c, b, n, k) for name, (c, b, _, n, k) in lw.items()} for lw in stack.layers]
+    xq = {k: torch.randint(-127, 128, (M, k), dtype=torch.int8, device="cuda", generator=g) for k in (2048, 6144)}
+    xs = torch.full((M,), 1e-2, device="cuda")
+    res = torch.zeros((M, 2048), dtype=torch.bfloat16, device="cuda")
+
+    def all_gemms():
+        for lw, lq in zip(stack.layers, wq):
+            for name, epi in (("qkv", 1), ("o", 2), ("gu", 3), ("down", 2)):
+                _, _, ws, n, k = lw[name]
+                S.mm_epi(xq[k], lq[name], xs, ws, epi, res=res if epi == 2 else None)
+    all_gemms()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        all_gemms()
+    for _ in range(2):
+        graph.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    n_launch = 4 * len(stack.layers)
+    ops = qwen_ops(M, len(stack.layers))
+    peak = 2 * pk["bf16_tflops_sustained"]
+    ach = ops / ms / 1e9
+    return dict(kernel="gemm_i8_kernel (tcgen05 kind::i8)", bound="tensor", achieved=ach, peak=peak, unit="TOP/s", frac=ach / peak,
+                traffic=GEMM_TRAFFIC_BYTES, launches=n_launch, avg_launch_us=ms * 1e3 / n_launch,
+                algorithmic_ops_per_launch=ops / n_launch,
+                peak_note=f"2 x bf16_tflops_sustained of {pk['source']} peaks (MEASURED_PEAKS.json has no INT8 figure; the INT8 dense "
+                          f"rate is twice bf16); of nominal 4500 TOP/s: {ach / 4500:.3f}",
+                traffic_note="dram read+write of the gate|up launch from profiles/gemm_i8_kernel_gateup_2048x12288x2048.md; "
+                             "algorithmic operand bytes of that launch are 29.4 MB")
+
+
+GEMM_TRAFFIC_BYTES = 29.5e6 + 0.12e6
 
 
 def run_ours(args):
@@ -315,43 +324,45 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     pkg = importlib.import_module("mxfp4-int8-m5_b200")
     pk = peaks()
-    M, layers = QWEN["M"], QWEN["layers"]
-    model = DenseModel(pkg, torch, layers, M, shard=(rank, world))
-    g = torch.Generator(device="cuda").manual_seed(123 + rank)
-    h0 = torch.randn((M, 2048), generator=g, device="cuda").to(torch.bfloat16)
-    o0 = torch.randn((M, 2048), generator=g, device="cuda").to(torch.bfloat16)
-    tp = None
-    if world > 1:
-        par = importlib.import_module("mxfp4-int8-m5_b200.parallel")
-        tp = par.TensorParallelDense(pkg, model, dist)
-
-    def step(h, o, events=None):
-        return tp.step(h, o) if tp is not None else model.step(h, o, events)
+    M, layers, hidden = QWEN["M"], QWEN["layers"], 2048
+    lw = build_dense_layers(pkg, torch, layers, shard=(rank, world))
+    g = torch.Generator(device="cuda").manual_seed(123)
+    h0 = torch.randn((M, hidden), generator=g, device="cuda").to(torch.bfloat16)
+    o0 = torch.randn((M, hidden), generator=g, device="cuda").to(torch.bfloat16)
+    if world == 1:
+        stack = pkg.fused_dense.DenseStack(lw, M, hidden, overlap=not args.no_overlap)
+        hin, oin = h0, o0
+    else:      # residual stream in segment layout [G, M, hidden/G]; this rank's columns of the attention output
+        stack = pkg.parallel.TensorParallelDense(pkg, lw, M, hidden)
+        w = hidden // world
+        hin = h0.view(M, world, w).permute(1, 0, 2).contiguous()
+        oin = o0[:, rank * w:(rank + 1) * w].contiguous()
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- warm-up (eager), then capture the step in a CUDA graph: 336 launches per step are launch-bound from Python
-    out = step(h0, o0)
+    # ---- warm-up (eager), then capture the step in a CUDA graph: ~340 launches per step are launch-bound from Python
+    out = stack.step(hin, oin)
     torch.cuda.synchronize()
     pkg._lib.check_status()
     graph = None
-    if world == 1 and not args.no_graph:
+    if not args.no_graph:
         try:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                out = step(h0, o0)
+                out = stack.step(hin, oin)
         except Exception as e:   # noqa: BLE001
-            print(f"# CUDA graph capture unavailable ({e}); timing eager launches", file=sys.stderr)
+            print(f"# CUDA graph capture unavailable ({type(e).__name__}: {e}); timing eager launches", file=sys.stderr)
             graph = None
-    run = graph.replay if graph is not None else (lambda: step(h0, o0))
+            torch.cuda.synchronize()
+    run = graph.replay if graph is not None else (lambda: stack.step(hin, oin))
     for _ in range(max(args.warmup, 3)):
         run()
     barrier()
-    # ---- timed: K steps, CUDA events on the launching stream, max over ranks.  The 717.9 MB of packed weights and the
-    # INT8 scratch exceed L2 (126 MB), so every step streams its weights from HBM (no explicit flush needed).
+    # ---- timed: K steps, CUDA events on the launching stream, max over ranks.  The 718 MB of packed weights exceed L2
+    # (126 MB), so every step streams its weights from HBM (no explicit flush needed).
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as cs:
         barrier()
@@ -361,26 +372,30 @@ def run_ours(args):
         e1.record()
         barrier()
     clocks = cs.summary()
-    ms = e0.elapsed_time(e1) / args.steps
-    if world > 1:
-        t = torch.tensor([ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+
+    def max_ms(ms):
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return ms
+    ms = max_ms(e0.elapsed_time(e1) / args.steps)
     pkg._lib.check_status()
     ops = qwen_ops()
     value = ops / ms / 1e9
 
-    # ---- e2e: host buffers in, host result out, through the public API
-    hp, op_, outp = h0.cpu().pin_memory(), o0.cpu().pin_memory(), torch.empty_like(h0, device="cpu").pin_memory()
+    # ---- e2e: the step's inputs come from pinned host memory and its result goes back to the host, every step
+    hp, op_ = hin.cpu().pin_memory(), oin.cpu().pin_memory()
+    outp = torch.empty_like(out, device="cpu").pin_memory()
 
     def e2e_step():
-        h0.copy_(hp, non_blocking=True)          # the step's inputs come from pinned host memory ...
-        o0.copy_(op_, non_blocking=True)
+        hin.copy_(hp, non_blocking=True)
+        oin.copy_(op_, non_blocking=True)
         if graph is not None:
             graph.replay()
-            outp.copy_(out, non_blocking=True)   # ... and its result goes back to the host
+            outp.copy_(out, non_blocking=True)
         else:
-            outp.copy_(step(h0, o0), non_blocking=True)
+            outp.copy_(stack.step(hin, oin), non_blocking=True)
     for _ in range(2):
         e2e_step()
     barrier()
@@ -389,11 +404,7 @@ def run_ours(args):
         e2e_step()
     e1.record()
     barrier()
-    ms_e2e = e0.elapsed_time(e1) / args.steps
-    if world > 1:
-        t = torch.tensor([ms_e2e], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_e2e = float(t.item())
+    ms_e2e = max_ms(e0.elapsed_time(e1) / args.steps)
     e2e = dict(value=ops / ms_e2e / 1e9, unit="TOPS", h2d_bytes_per_step=hp.numel() * 2 + op_.numel() * 2,
                d2h_bytes_per_step=outp.numel() * 2, ms_per_step=ms_e2e)
 
@@ -401,33 +412,21 @@ def run_ours(args):
                 ms_per_step=ms, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="int8", data="synthetic",
                 config=dict(workload="qwen3-1.7b-shaped dense prefill: 28 layers x (qkv, o, gate|up, down), M=2048 tokens, "
                                      "SC-MXFP4 W4A8, random-init N(0,0.02) weights",
-                            parallelism="single GPU" if world == 1 else f"tp{world} (output columns)",
+                            parallelism="single GPU" if world == 1 else f"tp{world}: weights sharded by output column, "
+                                        "4 all-gathers per layer",
                             l2="inputs larger than L2: 718 MB of packed weights per step", cuda_graph=graph is not None),
-                clocks=clocks, e2e=e2e, gpu_launches=model.launches_per_layer * layers * args.steps)
-
-    if rank == 0 and world == 1:
-        # ---- roofline of the dominant kernel (the tcgen05 GEMM), timed live with CUDA events around each launch
-        ev = []
-        model.step(h0, o0, events=ev)
-        model.step(h0, o0, events=(ev := []))
-        torch.cuda.synchronize()
-        gemm_ms = sum(a.elapsed_time(b) for a, b, _ in ev)
-        gemm_ops = sum(o for _, _, o in ev)
-        peak = 2 * pk["bf16_tflops_sustained"]
-        ach = gemm_ops / gemm_ms / 1e9
-        line["roofline"] = dict(kernel="gemm_i8_kernel (tcgen05 kind::i8)", bound="tensor", achieved=ach, peak=peak, unit="TOP/s",
-                                frac=ach / peak, traffic=None, launches=len(ev), avg_launch_us=gemm_ms * 1e3 / len(ev),
-                                peak_note=f"2 x bf16_tflops_sustained of {pk['source']} peaks (INT8 dense rate = 2 x bf16); "
-                                          f"nominal 4500: frac_nominal={ach / 4500:.3f}")
-        line["decode"] = bench_decode(pkg, torch, model)
+                clocks=clocks, e2e=e2e, gpu_launches=stack.launches_per_layer * layers * args.steps)
+    if world == 1:
+        line["roofline"] = gemm_only_roofline(pkg, torch, stack, pk)
+        line["decode"] = bench_decode(pkg, torch, stack)
         line["decode"]["hbm_frac"] = line["decode"]["gbs"] / pk["hbm_gbs"]
-        del model.layers[4:]
-        torch.cuda.empty_cache()
-        try:
-            line["moe"] = bench_moe(pkg, torch)
-        except Exception as e:   # noqa: BLE001
-            line["moe"] = dict(error=str(e))
-        pkg._lib.check_status()
+    del stack, lw, graph
+    torch.cuda.empty_cache()
+    try:
+        line["moe"] = bench_moe(pkg, torch, dist if world > 1 else None)
+    except Exception as e:   # noqa: BLE001
+        line["moe"] = dict(error=f"{type(e).__name__}: {e}")
+    if rank == 0 and world == 1:
         dt, cops = cpu_dense_layer_sample()
         line["cpu_baseline"] = dict(value=cops / dt / 1e12, unit="TOPS", cores=os.cpu_count(), kind="port",
                                     sample="1 of 28 layers at M=2048: act-quant + f64-BLAS INT32 GEMM + epilogue (NumPy oracle)")
@@ -462,7 +461,7 @@ def run_case(args):
             for c, b, w_ in sets:
                 G.gemv(xq, c, b, xs, w_, 12288, 3)
     else:
-        bench_moe(pkg, torch, reps=1)
+        bench_moe(pkg, torch, None, reps=1)
     torch.cuda.synchronize()
     pkg._lib.check_status()
     print(json.dumps(dict(case=args.case, ok=True)))
@@ -475,6 +474,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-overlap", action="store_true", help="decode weights on the main stream instead of a side stream")
     ap.add_argument("--case", choices=["gemm", "gemv", "moe"], help="run one small kernel case (for profiler captures) and exit")
     args = ap.parse_args()
     if args.case:

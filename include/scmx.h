@@ -69,6 +69,15 @@ int scmx_act_quant(const uint16_t* x, int64_t M, int64_t K, int64_t Mp, int8_t* 
 int scmx_rmsnorm_quant(const uint16_t* x, const uint16_t* nw, float eps, int64_t M, int64_t K, int64_t Mp,
                        int8_t* xq, float* xs, uint16_t* xn, void* stream);
 
+/* act_quant / rmsnorm_quant on rows stored as `nseg` column segments: element (m, s*w + j), w = K/nseg, lives at
+ * x[s*seg_stride + m*w + j] (each segment a row-major [M, w] matrix, `seg_stride` elements apart) — the layout an
+ * all-gather of column-sharded GEMM outputs leaves behind, consumed without a transposing copy.  The reference is
+ * single-device and has no counterpart; the arithmetic is that of e2e/sc_kernels.py:200-229 / :123-174.  K <= 8192. */
+int scmx_act_quant_seg(const uint16_t* x, int64_t M, int64_t K, int64_t Mp, int nseg, int64_t seg_stride, int8_t* xq,
+                       float* xs, void* stream);
+int scmx_rmsnorm_quant_seg(const uint16_t* x, const uint16_t* nw, float eps, int64_t M, int64_t K, int64_t Mp, int nseg,
+                           int64_t seg_stride, int8_t* xq, float* xs, uint16_t* xn, void* stream);
+
 /* h = res + T(acc * xscale[m] * wscale[n]) from INT32 accumulators [Mp,N].
  * Replaces sc_kernels.res_epilogue (e2e/sc_kernels.py:191-197,547-551). */
 int scmx_res_epilogue(const int32_t* acc, const float* xscale, const float* wscale, const uint16_t* res, int64_t Mp,

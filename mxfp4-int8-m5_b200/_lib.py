@@ -33,6 +33,8 @@ SIGNATURES = {
     "scmx_unpack_i8": [c_vp, c_vp, c_i64, c_i64, _FMT_P, c_vp, c_vp],
     "scmx_act_quant": [c_vp, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp],
     "scmx_rmsnorm_quant": [c_vp, c_vp, c_float, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp],
+    "scmx_act_quant_seg": [c_vp, c_i64, c_i64, c_i64, c_int, c_i64, c_vp, c_vp, c_vp],
+    "scmx_rmsnorm_quant_seg": [c_vp, c_vp, c_float, c_i64, c_i64, c_i64, c_int, c_i64, c_vp, c_vp, c_vp, c_vp],
     "scmx_res_epilogue": [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp],
     "scmx_swiglu_quant": [c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp],
     "scmx_swiglu": [c_vp, c_vp, c_i64, c_vp, c_vp],

@@ -147,6 +147,211 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(const uint16_t* __re
     if (threadIdx.x == 0) xs[row] = s;
 }
 
+// Input rows may be stored in column segments (the layout an all-gather of column shards produces): element
+// (m, s * w + j) lives at x[s * seg_stride + m * w + j].  One segment of width K is the ordinary row-major matrix.
+struct RowSegs {
+    int w8;              // 16-byte vectors per segment row
+    int64_t stride8;     // distance between segments in 16-byte vectors
+    __device__ __forceinline__ int64_t index(int64_t row, int v) const {
+        return (int64_t)(v / w8) * stride8 + row * w8 + (v % w8);
+    }
+};
+
+// ---- warp-per-row variants (K <= 256 * MAXV): the whole row lives in registers, reductions are shuffles only -------------
+__device__ __forceinline__ void unpack8(const uint4& r, float v[8]) {
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        v[2 * j] = __uint_as_float(w[j] << 16);
+        v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+    }
+}
+__device__ __forceinline__ uint2 pack8_i8(const int q[8]) {
+    uint2 o;
+    o.x = (q[0] & 0xFF) | ((q[1] & 0xFF) << 8) | ((q[2] & 0xFF) << 16) | ((uint32_t)(q[3] & 0xFF) << 24);
+    o.y = (q[4] & 0xFF) | ((q[5] & 0xFF) << 8) | ((q[6] & 0xFF) << 16) | ((uint32_t)(q[7] & 0xFF) << 24);
+    return o;
+}
+
+template <int MAXV, bool NORM>
+__global__ void __launch_bounds__(256) row_quant_warp_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ nw,
+                                                             float eps, int64_t M, int64_t Mp, int K, RowSegs sg,
+                                                             int8_t* __restrict__ xq, float* __restrict__ xs,
+                                                             uint16_t* __restrict__ xn) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= Mp) return;
+    const int nv = K / 8;                      // 16-byte vectors per row
+    uint2* qrow = reinterpret_cast<uint2*>(xq + row * K);
+    if (row >= M) {                            // padded rows: zero codes, zero scale
+#pragma unroll
+        for (int i = 0; i < MAXV; ++i) {
+            const int v = i * 32 + lane;
+            if (v < nv) {
+                qrow[v] = make_uint2(0, 0);
+                if (NORM && xn) reinterpret_cast<uint4*>(xn + row * K)[v] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        if (lane == 0) xs[row] = 0.0f;
+        return;
+    }
+    const uint4* x4 = reinterpret_cast<const uint4*>(x);
+    uint4 raw[MAXV];
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+        const int v = i * 32 + lane;
+        raw[i] = v < nv ? x4[sg.index(row, v)] : make_uint4(0, 0, 0, 0);
+    }
+    float inv = 1.0f;
+    if (NORM) {
+        double ss = 0.0;
+#pragma unroll
+        for (int i = 0; i < MAXV; ++i) {
+            float f[8];
+            unpack8(raw[i], f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss += (double)f[j] * (double)f[j];
+        }
+        ss = warp_sum(ss);
+        inv = rms_inverse(ss, K, eps);
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+        const int v = i * 32 + lane;
+        float f[8];
+        unpack8(raw[i], f);
+        if (NORM && v < nv) {
+            float w[8];
+            unpack8(reinterpret_cast<const uint4*>(nw)[v], w);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = rbf(__fmul_rn(w[j], rbf(__fmul_rn(f[j], inv))));
+            uint4 o;
+            o.x = f32_to_bf16(f[0]) | ((uint32_t)f32_to_bf16(f[1]) << 16);
+            o.y = f32_to_bf16(f[2]) | ((uint32_t)f32_to_bf16(f[3]) << 16);
+            o.z = f32_to_bf16(f[4]) | ((uint32_t)f32_to_bf16(f[5]) << 16);
+            o.w = f32_to_bf16(f[6]) | ((uint32_t)f32_to_bf16(f[7]) << 16);
+            raw[i] = o;                        // keep the normalized row (bf16) for the quantization pass
+            if (xn) reinterpret_cast<uint4*>(xn + row * K)[v] = o;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+    }
+    amax = warp_max(amax);
+    float s, qi;
+    quant_scale(amax, s, qi);
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+        const int v = i * 32 + lane;
+        if (v < nv) {
+            float f[8];
+            int q[8];
+            unpack8(raw[i], f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) q[j] = quant_code(f[j], qi);
+            qrow[v] = pack8_i8(q);
+        }
+    }
+    if (lane == 0) xs[row] = s;
+}
+
+// CTA-per-row variant for wider rows (K <= 2048 * MAXV): each thread keeps MAXV 16-byte vectors of the row in registers.
+template <int MAXV, bool NORM>
+__global__ void __launch_bounds__(256) row_quant_block_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ nw,
+                                                              float eps, int64_t M, int K, RowSegs sg, int8_t* __restrict__ xq,
+                                                              float* __restrict__ xs, uint16_t* __restrict__ xn) {
+    __shared__ float red[33];
+    __shared__ double dred[33];
+    const int64_t row = blockIdx.x;
+    const int nv = K / 8;
+    uint2* qrow = reinterpret_cast<uint2*>(xq + row * K);
+    if (row >= M) {
+#pragma unroll
+        for (int i = 0; i < MAXV; ++i) {
+            const int v = i * 256 + threadIdx.x;
+            if (v < nv) {
+                qrow[v] = make_uint2(0, 0);
+                if (NORM && xn) reinterpret_cast<uint4*>(xn + row * K)[v] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        if (threadIdx.x == 0) xs[row] = 0.0f;
+        return;
+    }
+    const uint4* x4 = reinterpret_cast<const uint4*>(x);
+    uint4 raw[MAXV];
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+        const int v = i * 256 + threadIdx.x;
+        raw[i] = v < nv ? x4[sg.index(row, v)] : make_uint4(0, 0, 0, 0);
+    }
+    float inv = 1.0f;
+    if (NORM) {
+        double ss = 0.0;
+#pragma unroll
+        for (int i = 0; i < MAXV; ++i) {
+            float f[8];
+            unpack8(raw[i], f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss += (double)f[j] * (double)f[j];
+        }
+        ss = block_sum(ss, dred);
+        inv = rms_inverse(ss, K, eps);
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+        const int v = i * 256 + threadIdx.x;
+        float f[8];
+        unpack8(raw[i], f);
+        if (NORM && v < nv) {
+            float w[8];
+            unpack8(reinterpret_cast<const uint4*>(nw)[v], w);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = rbf(__fmul_rn(w[j], rbf(__fmul_rn(f[j], inv))));
+            uint4 o;
+            o.x = f32_to_bf16(f[0]) | ((uint32_t)f32_to_bf16(f[1]) << 16);
+            o.y = f32_to_bf16(f[2]) | ((uint32_t)f32_to_bf16(f[3]) << 16);
+            o.z = f32_to_bf16(f[4]) | ((uint32_t)f32_to_bf16(f[5]) << 16);
+            o.w = f32_to_bf16(f[6]) | ((uint32_t)f32_to_bf16(f[7]) << 16);
+            raw[i] = o;
+            if (xn) reinterpret_cast<uint4*>(xn + row * K)[v] = o;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+    }
+    amax = block_max(amax, red);
+    float s, qi;
+    quant_scale(amax, s, qi);
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+        const int v = i * 256 + threadIdx.x;
+        if (v < nv) {
+            float f[8];
+            int q[8];
+            unpack8(raw[i], f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) q[j] = quant_code(f[j], qi);
+            qrow[v] = pack8_i8(q);
+        }
+    }
+    if (threadIdx.x == 0) xs[row] = s;
+}
+
+template <bool NORM>
+static bool launch_row_quant_warp(const uint16_t* x, const uint16_t* nw, float eps, int64_t M, int64_t Mp, int64_t K,
+                                  int nseg, int64_t seg_stride, int8_t* xq, float* xs, uint16_t* xn, cudaStream_t st) {
+    const unsigned grid = (unsigned)((Mp + 7) / 8);
+    RowSegs sg;
+    sg.w8 = (int)(K / nseg / 8);
+    sg.stride8 = seg_stride / 8;
+    if (K <= 256 * 4) row_quant_warp_kernel<4, NORM><<<grid, 256, 0, st>>>(x, nw, eps, M, Mp, (int)K, sg, xq, xs, xn);
+    else if (K <= 256 * 8) row_quant_warp_kernel<8, NORM><<<grid, 256, 0, st>>>(x, nw, eps, M, Mp, (int)K, sg, xq, xs, xn);
+    else if (K <= 256 * 16) row_quant_warp_kernel<16, NORM><<<grid, 256, 0, st>>>(x, nw, eps, M, Mp, (int)K, sg, xq, xs, xn);
+    else if (K <= 2048 * 4) row_quant_block_kernel<4, NORM><<<(unsigned)Mp, 256, 0, st>>>(x, nw, eps, M, (int)K, sg, xq, xs, xn);
+    else return false;
+    return true;
+}
+
 // ---- residual epilogue on INT32 accumulators ---------------------------------------------------------------------
 __global__ void __launch_bounds__(256) res_epilogue_kernel(const int32_t* __restrict__ acc, const float* __restrict__ xscale,
                                                            const float* __restrict__ wscale,
@@ -329,7 +534,8 @@ extern "C" int scmx_act_quant(const uint16_t* x, int64_t M, int64_t K, int64_t M
                  (long long)K);
     SCMX_REQUIRE(aligned16(x) && aligned16(xq) && K % 8 == 0, SCMX_EINVAL, "act_quant: x and xq must be 16-byte aligned");
     if (Mp == 0) return SCMX_OK;
-    act_quant_kernel<<<(unsigned)Mp, 256, 0, (cudaStream_t)stream>>>(x, M, (int)K, xq, xs);
+    if (!launch_row_quant_warp<false>(x, nullptr, 0.0f, M, Mp, K, 1, 0, xq, xs, nullptr, (cudaStream_t)stream))
+        act_quant_kernel<<<(unsigned)Mp, 256, 0, (cudaStream_t)stream>>>(x, M, (int)K, xq, xs);
     SCMX_LAUNCH_OK("act_quant_kernel");
     return SCMX_OK;
 }
@@ -342,7 +548,8 @@ extern "C" int scmx_rmsnorm_quant(const uint16_t* x, const uint16_t* nw, float e
     SCMX_REQUIRE(aligned16(x) && aligned16(nw) && aligned16(xq) && (!xn || aligned16(xn)), SCMX_EINVAL,
                  "rmsnorm_quant: buffers must be 16-byte aligned");
     if (Mp == 0) return SCMX_OK;
-    rmsnorm_quant_kernel<<<(unsigned)Mp, 256, 0, (cudaStream_t)stream>>>(x, nw, eps, M, (int)K, xq, xs, xn);
+    if (!launch_row_quant_warp<true>(x, nw, eps, M, Mp, K, 1, 0, xq, xs, xn, (cudaStream_t)stream))
+        rmsnorm_quant_kernel<<<(unsigned)Mp, 256, 0, (cudaStream_t)stream>>>(x, nw, eps, M, (int)K, xq, xs, xn);
     SCMX_LAUNCH_OK("rmsnorm_quant_kernel");
     return SCMX_OK;
 }
@@ -403,3 +610,38 @@ extern "C" int scmx_gather_rows(const int8_t* xq, const float* xs, const int32_t
     SCMX_LAUNCH_OK("gather_rows_kernel");
     return SCMX_OK;
 }
+
+// Segmented-row variants: x holds nseg column segments of width K / nseg, `seg_stride` elements apart (each segment a
+// row-major [M, K / nseg] matrix).  Outputs are ordinary row-major [Mp, K].
+static int check_seg(const char* who, int64_t M, int64_t K, int64_t Mp, int nseg, int64_t seg_stride) {
+    SCMX_REQUIRE(M >= 0 && Mp >= M && K > 0 && nseg >= 1 && K % (8 * nseg) == 0 && K <= 8192, SCMX_EINVAL,
+                 "%s: need M <= Mp, K %% (8 * nseg) == 0 and K <= 8192 (M=%lld Mp=%lld K=%lld nseg=%d)", who, (long long)M,
+                 (long long)Mp, (long long)K, nseg);
+    SCMX_REQUIRE(seg_stride % 8 == 0 && (nseg == 1 || seg_stride >= M * (K / nseg)), SCMX_EINVAL,
+                 "%s: seg_stride=%lld must be a multiple of 8 and at least M * K / nseg", who, (long long)seg_stride);
+    return SCMX_OK;
+}
+
+extern "C" int scmx_act_quant_seg(const uint16_t* x, int64_t M, int64_t K, int64_t Mp, int nseg, int64_t seg_stride, int8_t* xq,
+                                  float* xs, void* stream) {
+    int rc = check_seg("act_quant_seg", M, K, Mp, nseg, seg_stride);
+    if (rc) return rc;
+    SCMX_REQUIRE(aligned16(x) && aligned16(xq), SCMX_EINVAL, "act_quant_seg: x and xq must be 16-byte aligned");
+    if (Mp == 0) return SCMX_OK;
+    launch_row_quant_warp<false>(x, nullptr, 0.0f, M, Mp, K, nseg, seg_stride, xq, xs, nullptr, (cudaStream_t)stream);
+    SCMX_LAUNCH_OK("row_quant kernel");
+    return SCMX_OK;
+}
+
+extern "C" int scmx_rmsnorm_quant_seg(const uint16_t* x, const uint16_t* nw, float eps, int64_t M, int64_t K, int64_t Mp,
+                                      int nseg, int64_t seg_stride, int8_t* xq, float* xs, uint16_t* xn, void* stream) {
+    int rc = check_seg("rmsnorm_quant_seg", M, K, Mp, nseg, seg_stride);
+    if (rc) return rc;
+    SCMX_REQUIRE(aligned16(x) && aligned16(nw) && aligned16(xq) && (!xn || aligned16(xn)), SCMX_EINVAL,
+                 "rmsnorm_quant_seg: buffers must be 16-byte aligned");
+    if (Mp == 0) return SCMX_OK;
+    launch_row_quant_warp<true>(x, nw, eps, M, Mp, K, nseg, seg_stride, xq, xs, xn, (cudaStream_t)stream);
+    SCMX_LAUNCH_OK("row_quant kernel");
+    return SCMX_OK;
+}
+

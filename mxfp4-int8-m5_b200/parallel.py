@@ -1,0 +1,145 @@
+"""Multi-GPU forms of the W4A8 path: one process per GPU, torch.distributed (NCCL over NVLink) for the exchanges.
+
+  * Dense layers shard by OUTPUT COLUMN (weight rows).  The format is per output row, so a row slice of codes / bcodes /
+    wscale is an exact shard and every rank's INT32 accumulators equal the corresponding columns of the single-GPU GEMM.
+    Column shards of a GEMM output are all-gathered into the segment layout [G, M, N/G] and consumed in place by the
+    segmented row kernels (act_quant_seg / rmsnorm_quant_seg): no transposing copies, and the residual slice of rank g
+    is the contiguous segment g.
+  * MoE layers shard by EXPERT, tokens by rank.  Rows are counting-sorted by global expert id (= by destination rank),
+    exchanged with all-to-all (INT8 rows + f32 scales out, bf16 rows back), regrouped by local expert on the receiver,
+    and returned to the sender in its original sorted order, where moe_combine finishes the block.
+
+The reference is single-device (one Apple GPU, no collectives); the exactness argument for row sharding is the one it
+uses for row concatenation (e2e/fused_qwen3.py:36,44-46) and for order independence of the sorted rows
+(e2e/sc_moe.py:110-113).  The bookkeeping in this file is device-agnostic so that it also runs on CPU tensors with the
+gloo backend.
+"""
+import torch
+import torch.distributed as dist
+
+
+# ---- host-side bookkeeping (no kernels) ---------------------------------------------------------------------------
+def shard_rows(N, rank, world, multiple=1):
+    """[r0, r1) of an N-row weight for `rank`; shards are equal and a multiple of `multiple` rows."""
+    assert N % (world * multiple) == 0, f"N={N} is not divisible into {world} shards of a multiple of {multiple} rows"
+    per = N // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_packed(codes, bcodes, wscale, N, K, rank, world, multiple=1):
+    """Row shard of a packed matrix (codes [N*K/8], bcodes [N, ...], wscale [N]) -> (codes, bcodes, wscale, N_local, K)."""
+    r0, r1 = shard_rows(N, rank, world, multiple)
+    c = codes.reshape(N, K // 8)[r0:r1].reshape(-1).contiguous()
+    return c, bcodes[r0:r1].contiguous(), wscale[r0:r1].contiguous(), r1 - r0, K
+
+
+def expert_owner_splits(cnt, world):
+    """cnt int [E] rows per global expert (experts are owned in contiguous blocks of E/world) -> rows per destination rank."""
+    return cnt.reshape(world, -1).sum(1)
+
+
+def exchange_counts(cnt, world, group=None):
+    """Every rank sends the counts of the experts owned by rank d to rank d; returns int64 [world, E/world], row s = what
+    rank s will send here."""
+    send = cnt.reshape(world, -1).to(torch.int64).contiguous()
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    return recv
+
+
+def exchange_rows(rows, send_splits, recv_splits, group=None, out=None):
+    """Variable all-to-all of the leading dimension: rows[sum(send_splits), ...] -> [sum(recv_splits), ...]."""
+    n = int(sum(recv_splits))
+    if out is None:
+        out = torch.empty((n,) + tuple(rows.shape[1:]), dtype=rows.dtype, device=rows.device)
+    dist.all_to_all_single(out[:n], rows, output_split_sizes=list(recv_splits), input_split_sizes=list(send_splits), group=group)
+    return out
+
+
+def local_expert_ids(recv_cnt):
+    """recv_cnt int64 [world, El] -> local expert id of every received row (rows arrive source-major, expert-minor)."""
+    world, El = recv_cnt.shape
+    ids = torch.arange(El, device=recv_cnt.device, dtype=torch.int32).repeat(world)
+    return torch.repeat_interleave(ids, recv_cnt.reshape(-1), output_size=int(recv_cnt.sum()))
+
+
+# ---- tensor-parallel dense stack ----------------------------------------------------------------------------------------
+class TensorParallelDense:
+    """Column-sharded dense decoder stack (see fused_dense.DenseStack for the chain)."""
+
+    def __init__(self, pkg, layers_local, M, hidden, group=None, eps=1e-6):
+        """layers_local: this rank's row shards {group: (codes, bcodes, wscale, N_local, K)} (shard_packed)."""
+        self.S, self.layers, self.M, self.hidden, self.eps, self.group = pkg.sc_kernels, layers_local, M, hidden, eps, group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        dev = layers_local[0]["qkv"][0].device
+        self.nw = torch.ones(hidden, dtype=torch.bfloat16, device=dev)
+        self.launches_per_layer = 12
+
+    def gather(self, local):
+        """[M, w] column shard -> [G, M, w] segment layout on every rank."""
+        out = torch.empty((self.world,) + tuple(local.shape), dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(out.view(-1, local.shape[1]), local.contiguous(), group=self.group)
+        return out
+
+    def _gemm(self, lw, name, xq, xs, epi, res=None):
+        codes, bc, ws, n, k = lw[name]
+        return self.S.mm_epi(xq, self.S.unpack_i8(codes, bc, n, k), xs, ws, epi, res=res)
+
+    def step(self, h_seg, o_local):
+        """h_seg bf16 [G, M, hidden/G]: residual stream in segment layout; o_local bf16 [M, hidden/G]: this rank's columns
+        of the attention output.  Returns the new residual stream, again in segment layout (identical on every rank)."""
+        S, M, r = self.S, self.M, self.rank
+        for lw in self.layers:
+            xq, xs = S.rmsnorm_quant_seg(h_seg, self.nw, self.eps, M)
+            self._gemm(lw, "qkv", xq, xs, 1)                       # this rank's heads; attention is outside the path
+            oq, os_ = S.act_quant_seg(self.gather(o_local), M)
+            h_seg = self.gather(self._gemm(lw, "o", oq, os_, 2, res=h_seg[r]))
+            xq, xs = S.rmsnorm_quant_seg(h_seg, self.nw, self.eps, M)
+            act = self._gemm(lw, "gu", xq, xs, 3)                  # [M, F/G]
+            aq, as_ = S.act_quant_seg(self.gather(act), M)
+            h_seg = self.gather(self._gemm(lw, "down", aq, as_, 2, res=h_seg[r]))
+        return h_seg
+
+
+# ---- expert-parallel MoE half-block -----------------------------------------------------------------------------------------
+class ExpertParallelMoe:
+    """MoE half-block with experts [rank*E/G, (rank+1)*E/G) on this rank and L/G tokens per rank."""
+
+    def __init__(self, pkg, block_local, n_experts, topk, group=None):
+        """block_local: fused_moe.MoeBlock built from this rank's E/G experts."""
+        self.pkg, self.block, self.E, self.k, self.group = pkg, block_local, n_experts, topk, group
+        self.world = dist.get_world_size(group)
+        assert n_experts % self.world == 0 and block_local.E == n_experts // self.world
+
+    def step(self, h, logits):
+        """h bf16 [Lr, D] local tokens, logits f32 [Lr, E] over ALL experts -> new residual rows bf16 [Lr, D]."""
+        S, M_, L_ = self.pkg.sc_kernels, self.pkg.sc_moe, self.pkg._lib
+        blk, G, k = self.block, self.world, self.k
+        Lr, D = h.shape
+        R = Lr * k
+        xq, xs = S.rmsnorm_quant(h, blk.nw, blk.eps, Lr)
+        inds, scores = M_.router_topk(logits, k)
+        pos, tok, _, off, _, _ = M_.route_sort(inds, self.E, M_.TM)      # sorted by global expert = by destination rank
+        xq_s, xs_s = M_.gather_rows(xq, xs, tok, R)
+        cnt = off[1:] - off[:-1]
+        recv_cnt = exchange_counts(cnt, G, self.group)
+        splits = torch.stack([expert_owner_splits(cnt.to(torch.int64), G), recv_cnt.sum(1)]).cpu()   # the one host sync
+        send_splits, recv_splits = splits[0].tolist(), splits[1].tolist()
+        Rr = int(sum(recv_splits))
+        rx_q = torch.empty((Rr + M_.TM, D), dtype=torch.int8, device=h.device)
+        exchange_rows(xq_s[:R], send_splits, recv_splits, self.group, out=rx_q)
+        rx_s = exchange_rows(xs_s, send_splits, recv_splits, self.group)
+        # regroup the received rows by local expert
+        le = local_expert_ids(recv_cnt)
+        pos2, tok2, _, off2, ts2, mt2 = M_.route_sort(le.view(Rr, 1), blk.E, M_.TM)
+        xq_r, xs_r = M_.gather_rows(rx_q, rx_s, tok2, Rr)
+        y_sorted = blk.experts(xq_r, xs_r, Rr, off2, ts2, mt2)             # bf16 [Rr, D]
+        # back to arrival order (row i of the receive buffer is sorted row pos2[i]), then back to the senders
+        y_rx = torch.empty((Rr, D), dtype=torch.bfloat16, device=h.device)
+        if Rr:
+            L_.call("scmx_gather_rows", L_.ptr(y_sorted.view(torch.int8)), None, L_.ptr(pos2), Rr, 0, 2 * D,
+                    L_.ptr(y_rx.view(torch.int8)), None, L_.stream())
+        y_back = exchange_rows(y_rx, recv_splits, send_splits, self.group)
+        hout, _, _ = M_.moe_combine(y_back, pos, scores, h, blk.nw, blk.eps, Lr, quant=False)
+        return hout

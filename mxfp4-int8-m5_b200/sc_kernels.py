@@ -30,10 +30,11 @@ def _bf16(x):
     return x
 
 
-def unpack_i8(codes, bcodes, N, K, deps=()):
-    """Packed codes + block codes -> INT8 operand [N, K]."""
-    _lib.require_cuda(codes, bcodes)
-    wq = torch.empty((N, K), dtype=torch.int8, device=codes.device)
+def unpack_i8(codes, bcodes, N, K, deps=(), out=None):
+    """Packed codes + block codes -> INT8 operand [N, K] (written into `out` when given)."""
+    _lib.require_cuda(codes, bcodes, out)
+    wq = out if out is not None else torch.empty((N, K), dtype=torch.int8, device=codes.device)
+    assert wq.dtype == torch.int8 and wq.numel() >= N * K
     _lib.call("scmx_unpack_i8", _lib.ptr(codes), _lib.ptr(bcodes), N, K, F.DEFAULT.c_struct(), _lib.ptr(wq), _lib.stream())
     return wq
 
@@ -46,6 +47,30 @@ def act_quant(x, Mp=None, nt=256, deps=()):
     xq = torch.empty((Mp, K), dtype=torch.int8, device=x.device)
     xs = torch.empty(Mp, dtype=torch.float32, device=x.device)
     _lib.call("scmx_act_quant", _lib.ptr(x), M, K, Mp, _lib.ptr(xq), _lib.ptr(xs), _lib.stream())
+    return xq, xs
+
+
+def act_quant_seg(xseg, Mp=None):
+    """act_quant of rows stored as column segments: xseg bf16 [G, M, w] holds the [M, G*w] matrix whose columns
+    g*w .. (g+1)*w are xseg[g] (what an all-gather of column shards produces)."""
+    _lib.require_cuda(xseg)
+    G, M, w = _bf16(xseg).shape
+    Mp = Mp or pad_rows(M)
+    xq = torch.empty((Mp, G * w), dtype=torch.int8, device=xseg.device)
+    xs = torch.empty(Mp, dtype=torch.float32, device=xseg.device)
+    _lib.call("scmx_act_quant_seg", _lib.ptr(xseg), M, G * w, Mp, G, M * w, _lib.ptr(xq), _lib.ptr(xs), _lib.stream())
+    return xq, xs
+
+
+def rmsnorm_quant_seg(xseg, w, eps, Mp=None):
+    """rmsnorm_quant of rows stored as column segments (see act_quant_seg)."""
+    _lib.require_cuda(xseg, w)
+    G, M, ws = _bf16(xseg).shape
+    Mp = Mp or pad_rows(M)
+    xq = torch.empty((Mp, G * ws), dtype=torch.int8, device=xseg.device)
+    xs = torch.empty(Mp, dtype=torch.float32, device=xseg.device)
+    _lib.call("scmx_rmsnorm_quant_seg", _lib.ptr(xseg), _lib.ptr(w), _eps(eps), M, G * ws, Mp, G, M * ws, _lib.ptr(xq),
+              _lib.ptr(xs), None, _lib.stream())
     return xq, xs
 
 
