@@ -348,7 +348,8 @@ def run_ours(args):
     torch.cuda.synchronize()
     pkg._lib.check_status()
     graph = None
-    if not args.no_graph:
+    # (multi-rank steps contain NCCL collectives and are timed as eager launches)
+    if not args.no_graph and world == 1:
         try:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):

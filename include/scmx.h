@@ -106,6 +106,11 @@ int scmx_mm_i8(const int8_t* xq, const int8_t* wq, int64_t M, int64_t N, int64_t
  * module-level tile constants TM, TN, NSG, GROUP_M (e2e/sc_kernels.py:25) and the `tile=` arguments. */
 int scmx_set_gemm_tile(int bn);
 
+/* Process-wide switches with no counterpart in the reference: programmatic dependent launch for the kernels of the chains
+ * (default on) and the streaming (bulk-copy, persistent) form of the dense GEMV (default on).  For A/B measurements. */
+int scmx_set_pdl(int enable);
+int scmx_set_gemv_stream(int enable);
+
 /* ---- grouped MoE GEMM ------------------------------------------------------------------------------------------- */
 
 /* Counting sort of M*topk assignments by expert with segment offsets and M-tile starts.

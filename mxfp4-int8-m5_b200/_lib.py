@@ -40,6 +40,8 @@ SIGNATURES = {
     "scmx_swiglu": [c_vp, c_vp, c_i64, c_vp, c_vp],
     "scmx_mm_i8": [c_vp, c_vp, c_i64, c_i64, c_i64, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp],
     "scmx_set_gemm_tile": [c_int],
+    "scmx_set_pdl": [c_int],
+    "scmx_set_gemv_stream": [c_int],
     "scmx_route_sort": [c_vp, c_i64, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp],
     "scmx_router_topk": [c_vp, c_i64, c_int, c_int, c_vp, c_vp, c_vp, c_vp],
     "scmx_gather_rows": [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp],

@@ -6,6 +6,7 @@
 namespace scmx {
 
 static thread_local char g_err[512] = "no error";
+int g_use_pdl = 1;
 
 void set_error(const char* fmt, ...) {
     va_list ap;
@@ -50,3 +51,7 @@ int make_dev_format(const scmx_format* fmt, DevFormat* out) {
 
 extern "C" const char* scmx_last_error_string(void) { return scmx::g_err; }
 extern "C" int scmx_abi_version(void) { return 1; }
+extern "C" int scmx_set_pdl(int enable) {
+    scmx::g_use_pdl = enable ? 1 : 0;
+    return SCMX_OK;
+}

@@ -10,6 +10,40 @@ namespace scmx {
 
 void set_error(const char* fmt, ...);
 
+// ---- programmatic dependent launch ----------------------------------------------------------------------------------------
+// Kernels of the chains are launched with programmatic stream serialization: a kernel may become resident while its
+// predecessor drains, runs its set-up, and blocks in pdl_wait() until the predecessor has completed and flushed.  Every
+// kernel performs all its reads of activations and all its writes after pdl_wait(), so by induction along the stream
+// nothing earlier is still running when a kernel touches memory.
+extern int g_use_pdl;
+
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_use_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+#define SCMX_PDL_OK(name, expr)                                                              \
+    do {                                                                                      \
+        cudaError_t e__ = (expr);                                                             \
+        if (e__ != cudaSuccess) {                                                             \
+            ::scmx::set_error("launch of %s failed: %s", name, cudaGetErrorString(e__));      \
+            return SCMX_ECUDA;                                                                \
+        }                                                                                     \
+    } while (0)
+
 #define SCMX_REQUIRE(cond, code, ...)                 \
     do {                                              \
         if (!(cond)) {                                \

@@ -18,13 +18,13 @@
 // out the kernel records where in `status`, lets in-flight copies land, frees its TMEM and returns.
 #include <cuda.h>
 #include "scmx_common.cuh"
+#include "scmx_ptx.cuh"
 
 namespace scmx {
 
 constexpr int BM = 128;          // rows of A per tile = TMEM lanes
 constexpr int BK = 128;          // K bytes per stage = one 128-byte swizzle row
 constexpr int UMMA_K = 32;       // K per tcgen05.mma kind::i8
-constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // 2 s
 constexpr int EPI_WARPS = 8;
 constexpr int EPI_THREADS = 32 * EPI_WARPS;
 constexpr int CTA_THREADS = 64 + EPI_THREADS;   // TMA warp + MMA warp + epilogue warps
@@ -44,46 +44,6 @@ struct GemmArgs {
     const uint16_t* silu_lut;    // 65536-entry bf16 table of silu(g) indexed by the bf16 bits of g (EPI 3)
 };
 
-// ---- PTX wrappers ----------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok;
-}
-__device__ __forceinline__ uint64_t globaltimer_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-// Bounded wait: 0 = barrier phase completed, 1 = the time limit ran out, 2 = another role of this CTA gave up first.
-__device__ __forceinline__ int mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_try_wait(bar, parity)) return 0;
-    const uint64_t t0 = globaltimer_ns();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 64; ++i)
-            if (mbar_try_wait(bar, parity)) return 0;
-        if (*abort_flag) return 2;
-        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; return 1; }
-    }
-}
 // Barrier among the epilogue threads only (named barrier 1).
 __device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory"); }
 
@@ -303,10 +263,14 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_i8_kernel(const __grid_co
         tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
         tmem_relinquish();
     }
+    pdl_launch_dependents();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // everything above (barrier init, TMEM allocation) overlapped the previous kernel's tail; operands, scales and
+    // tile tables written by earlier kernels are only touched from here on
+    pdl_wait();
 
     int tiles_m, slot0;
     const int total = num_tiles<BN>(a, tiles_m, slot0);
@@ -510,7 +474,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
         SCMX_CUDA_OK(cudaFuncSetAttribute(gemm_i8_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
         configured = true;
     }
-    gemm_i8_kernel<BN, STAGES><<<grid, CTA_THREADS, L::TOTAL, st>>>(tmA, tmB, a);
+    launch_pdl(gemm_i8_kernel<BN, STAGES>, dim3(grid), dim3(CTA_THREADS), (size_t)L::TOTAL, st, tmA, tmB, a);
     SCMX_LAUNCH_OK("gemm_i8_kernel");
     return SCMX_OK;
 }

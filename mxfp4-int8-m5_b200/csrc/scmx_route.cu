@@ -14,6 +14,8 @@ __global__ void __launch_bounds__(1024) route_sort_kernel(const int32_t* __restr
                                                           int32_t* __restrict__ tstart) {
     __shared__ unsigned cnt[1024];
     __shared__ unsigned cur[1024];
+    pdl_launch_dependents();
+    pdl_wait();
     const int tid = threadIdx.x, nt = blockDim.x;
     for (int e = tid; e < E; e += nt) cnt[e] = 0;
     __syncthreads();
@@ -62,6 +64,8 @@ __global__ void __launch_bounds__(1024) route_sort_kernel(const int32_t* __restr
 __global__ void __launch_bounds__(256) router_topk_kernel(const float* __restrict__ logits, int64_t M, int E, int topk,
                                                           int32_t* __restrict__ inds, uint16_t* __restrict__ scores,
                                                           float* __restrict__ scores_f32) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (t >= M) return;
@@ -124,7 +128,7 @@ extern "C" int scmx_route_sort(const int32_t* inds, int64_t M, int topk, int E, 
     SCMX_REQUIRE(M >= 0 && topk >= 1 && tm >= 1, SCMX_EINVAL, "route_sort: need M >= 0, topk >= 1, tm >= 1");
     SCMX_REQUIRE(E >= 1 && E <= 1024, SCMX_ELIMIT, "route_sort: E=%d outside 1..1024", E);
     SCMX_REQUIRE(M * topk < (1ll << 30), SCMX_ELIMIT, "route_sort: M*topk too large");
-    route_sort_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(inds, (int)(M * topk), topk, E, tm, pos, tok, esorted, off, tstart);
+    launch_pdl(route_sort_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, inds, (int)(M * topk), topk, E, tm, pos, tok, esorted, off, tstart);
     SCMX_LAUNCH_OK("route_sort_kernel");
     return SCMX_OK;
 }
@@ -134,7 +138,7 @@ extern "C" int scmx_router_topk(const float* logits, int64_t M, int E, int topk,
     SCMX_REQUIRE(M >= 0 && E >= 1 && E <= 1024 && topk >= 1 && topk <= E, SCMX_EINVAL,
                  "router_topk: need 1 <= topk <= E <= 1024 (E=%d topk=%d)", E, topk);
     if (M == 0) return SCMX_OK;
-    router_topk_kernel<<<(unsigned)((M + 7) / 8), 256, 0, (cudaStream_t)stream>>>(logits, M, E, topk, inds, scores, scores_f32);
+    launch_pdl(router_topk_kernel, dim3((unsigned)((M + 7) / 8)), dim3(256), 0, (cudaStream_t)stream, logits, M, E, topk, inds, scores, scores_f32);
     SCMX_LAUNCH_OK("router_topk_kernel");
     return SCMX_OK;
 }

@@ -9,6 +9,8 @@ namespace scmx {
 __global__ void __launch_bounds__(256) unpack_kernel(const uint4* __restrict__ codes, const uint8_t* __restrict__ bcodes,
                                                      int64_t n_vec, int vec_per_row, int bc_row_bytes, DevFormat f,
                                                      uint4* __restrict__ wq) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_vec) return;
     const int64_t n = i / vec_per_row;
@@ -56,6 +58,8 @@ __device__ __forceinline__ void store8_bf16(uint16_t* p, const float v[8]) {
 // ---- act_quant -------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) act_quant_kernel(const uint16_t* __restrict__ x, int64_t M, int K,
                                                         int8_t* __restrict__ xq, float* __restrict__ xs) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float red[33];
     const int64_t row = blockIdx.x;
     int8_t* qrow = xq + row * K;
@@ -98,6 +102,8 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(const uint16_t* __re
                                                             const uint16_t* __restrict__ nw, float eps, int64_t M, int K,
                                                             int8_t* __restrict__ xq, float* __restrict__ xs,
                                                             uint16_t* __restrict__ xn) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float red[33];
     __shared__ double dred[33];
     const int64_t row = blockIdx.x;
@@ -178,6 +184,8 @@ __global__ void __launch_bounds__(256) row_quant_warp_kernel(const uint16_t* __r
                                                              float eps, int64_t M, int64_t Mp, int K, RowSegs sg,
                                                              int8_t* __restrict__ xq, float* __restrict__ xs,
                                                              uint16_t* __restrict__ xn) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= Mp) return;
@@ -260,6 +268,8 @@ template <int MAXV, bool NORM>
 __global__ void __launch_bounds__(256) row_quant_block_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ nw,
                                                               float eps, int64_t M, int K, RowSegs sg, int8_t* __restrict__ xq,
                                                               float* __restrict__ xs, uint16_t* __restrict__ xn) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float red[33];
     __shared__ double dred[33];
     const int64_t row = blockIdx.x;
@@ -344,10 +354,10 @@ static bool launch_row_quant_warp(const uint16_t* x, const uint16_t* nw, float e
     RowSegs sg;
     sg.w8 = (int)(K / nseg / 8);
     sg.stride8 = seg_stride / 8;
-    if (K <= 256 * 4) row_quant_warp_kernel<4, NORM><<<grid, 256, 0, st>>>(x, nw, eps, M, Mp, (int)K, sg, xq, xs, xn);
-    else if (K <= 256 * 8) row_quant_warp_kernel<8, NORM><<<grid, 256, 0, st>>>(x, nw, eps, M, Mp, (int)K, sg, xq, xs, xn);
-    else if (K <= 256 * 16) row_quant_warp_kernel<16, NORM><<<grid, 256, 0, st>>>(x, nw, eps, M, Mp, (int)K, sg, xq, xs, xn);
-    else if (K <= 2048 * 4) row_quant_block_kernel<4, NORM><<<(unsigned)Mp, 256, 0, st>>>(x, nw, eps, M, (int)K, sg, xq, xs, xn);
+    if (K <= 256 * 4) launch_pdl(row_quant_warp_kernel<4, NORM>, dim3(grid), dim3(256), 0, st, x, nw, eps, M, Mp, (int)K, sg, xq, xs, xn);
+    else if (K <= 256 * 8) launch_pdl(row_quant_warp_kernel<8, NORM>, dim3(grid), dim3(256), 0, st, x, nw, eps, M, Mp, (int)K, sg, xq, xs, xn);
+    else if (K <= 256 * 16) launch_pdl(row_quant_warp_kernel<16, NORM>, dim3(grid), dim3(256), 0, st, x, nw, eps, M, Mp, (int)K, sg, xq, xs, xn);
+    else if (K <= 2048 * 4) launch_pdl(row_quant_block_kernel<4, NORM>, dim3((unsigned)Mp), dim3(256), 0, st, x, nw, eps, M, (int)K, sg, xq, xs, xn);
     else return false;
     return true;
 }
@@ -357,6 +367,8 @@ __global__ void __launch_bounds__(256) res_epilogue_kernel(const int32_t* __rest
                                                            const float* __restrict__ wscale,
                                                            const uint16_t* __restrict__ res, int64_t total4, int N,
                                                            uint16_t* __restrict__ h) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total4) return;
     const int64_t e = i * 4;
@@ -380,6 +392,8 @@ __global__ void __launch_bounds__(256) res_epilogue_kernel(const int32_t* __rest
 __global__ void __launch_bounds__(256) swiglu_quant_kernel(const int32_t* __restrict__ acc, const float* __restrict__ xscale,
                                                            const float* __restrict__ wscale, int F, int8_t* __restrict__ xq,
                                                            float* __restrict__ xs) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float red[33];
     const int64_t row = blockIdx.x;
     const int32_t* ar = acc + row * 2 * (int64_t)F;
@@ -415,6 +429,8 @@ __global__ void __launch_bounds__(256) swiglu_quant_kernel(const int32_t* __rest
 
 __global__ void swiglu_kernel(const uint16_t* __restrict__ g, const uint16_t* __restrict__ u, int64_t n,
                               uint16_t* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = f32_to_bf16(swiglu_bf16(bf16_to_f32(g[i]), bf16_to_f32(u[i])));
 }
@@ -428,6 +444,8 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t* __rest
                                                           float eps, int64_t M, int K, int topk, int quant,
                                                           uint16_t* __restrict__ h, int8_t* __restrict__ xq,
                                                           float* __restrict__ xs) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float red[33];
     __shared__ double dred[33];
     __shared__ int s_pos[TOPK_MAX];
@@ -494,6 +512,8 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t* __rest
 __global__ void __launch_bounds__(128) gather_rows_kernel(const int8_t* __restrict__ xq, const float* __restrict__ xs,
                                                           const int32_t* __restrict__ tok, int64_t rows_s, int K,
                                                           int8_t* __restrict__ dq, float* __restrict__ ds) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int64_t p = blockIdx.x;
     const int t = tok[p];
     const uint4* src = reinterpret_cast<const uint4*>(xq + (int64_t)t * K);
@@ -522,7 +542,7 @@ extern "C" int scmx_unpack_i8(const uint32_t* codes, const uint8_t* bcodes, int6
     if (N == 0) return SCMX_OK;
     const int64_t n_vec = N * K / 32;
     const int bc_row = (int)(K / (f.block * f.blocks_per_byte));
-    unpack_kernel<<<(unsigned)((n_vec + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+    launch_pdl(unpack_kernel, dim3((unsigned)((n_vec + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, 
         reinterpret_cast<const uint4*>(codes), bcodes, n_vec, (int)(K / 32), bc_row, f, reinterpret_cast<uint4*>(wq));
     SCMX_LAUNCH_OK("unpack_kernel");
     return SCMX_OK;
@@ -535,7 +555,7 @@ extern "C" int scmx_act_quant(const uint16_t* x, int64_t M, int64_t K, int64_t M
     SCMX_REQUIRE(aligned16(x) && aligned16(xq) && K % 8 == 0, SCMX_EINVAL, "act_quant: x and xq must be 16-byte aligned");
     if (Mp == 0) return SCMX_OK;
     if (!launch_row_quant_warp<false>(x, nullptr, 0.0f, M, Mp, K, 1, 0, xq, xs, nullptr, (cudaStream_t)stream))
-        act_quant_kernel<<<(unsigned)Mp, 256, 0, (cudaStream_t)stream>>>(x, M, (int)K, xq, xs);
+        launch_pdl(act_quant_kernel, dim3((unsigned)Mp), dim3(256), 0, (cudaStream_t)stream, x, M, (int)K, xq, xs);
     SCMX_LAUNCH_OK("act_quant_kernel");
     return SCMX_OK;
 }
@@ -549,7 +569,7 @@ extern "C" int scmx_rmsnorm_quant(const uint16_t* x, const uint16_t* nw, float e
                  "rmsnorm_quant: buffers must be 16-byte aligned");
     if (Mp == 0) return SCMX_OK;
     if (!launch_row_quant_warp<true>(x, nw, eps, M, Mp, K, 1, 0, xq, xs, xn, (cudaStream_t)stream))
-        rmsnorm_quant_kernel<<<(unsigned)Mp, 256, 0, (cudaStream_t)stream>>>(x, nw, eps, M, (int)K, xq, xs, xn);
+        launch_pdl(rmsnorm_quant_kernel, dim3((unsigned)Mp), dim3(256), 0, (cudaStream_t)stream, x, nw, eps, M, (int)K, xq, xs, xn);
     SCMX_LAUNCH_OK("rmsnorm_quant_kernel");
     return SCMX_OK;
 }
@@ -561,7 +581,7 @@ extern "C" int scmx_res_epilogue(const int32_t* acc, const float* xscale, const 
                  "res_epilogue: buffers must be 16-byte aligned");
     const int64_t total4 = Mp * N / 4;
     if (total4 == 0) return SCMX_OK;
-    res_epilogue_kernel<<<(unsigned)((total4 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(acc, xscale, wscale, res,
+    launch_pdl(res_epilogue_kernel, dim3((unsigned)((total4 + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, acc, xscale, wscale, res,
                                                                                             total4, (int)N, h);
     SCMX_LAUNCH_OK("res_epilogue_kernel");
     return SCMX_OK;
@@ -573,7 +593,7 @@ extern "C" int scmx_swiglu_quant(const int32_t* acc, const float* xscale, const 
     SCMX_REQUIRE(aligned16(acc) && aligned16(wscale) && aligned16(xq), SCMX_EINVAL,
                  "swiglu_quant: buffers must be 16-byte aligned");
     if (Mp == 0) return SCMX_OK;
-    swiglu_quant_kernel<<<(unsigned)Mp, 256, 0, (cudaStream_t)stream>>>(acc, xscale, wscale, (int)F, xq, xs);
+    launch_pdl(swiglu_quant_kernel, dim3((unsigned)Mp), dim3(256), 0, (cudaStream_t)stream, acc, xscale, wscale, (int)F, xq, xs);
     SCMX_LAUNCH_OK("swiglu_quant_kernel");
     return SCMX_OK;
 }
@@ -581,7 +601,7 @@ extern "C" int scmx_swiglu_quant(const int32_t* acc, const float* xscale, const 
 extern "C" int scmx_swiglu(const uint16_t* g, const uint16_t* u, int64_t n, uint16_t* out, void* stream) {
     SCMX_REQUIRE(n >= 0, SCMX_EINVAL, "swiglu: negative length");
     if (n == 0) return SCMX_OK;
-    swiglu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(g, u, n, out);
+    launch_pdl(swiglu_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, g, u, n, out);
     SCMX_LAUNCH_OK("swiglu_kernel");
     return SCMX_OK;
 }
@@ -594,7 +614,7 @@ extern "C" int scmx_moe_combine(const uint16_t* y, const int32_t* pos, const uin
     SCMX_REQUIRE(aligned16(y) && aligned16(res) && aligned16(h) && (!quant || (aligned16(xq) && aligned16(nw))),
                  SCMX_EINVAL, "moe_combine: buffers must be 16-byte aligned");
     if (Mp == 0) return SCMX_OK;
-    moe_combine_kernel<32><<<(unsigned)Mp, 256, 0, (cudaStream_t)stream>>>(y, pos, scores, res, nw, eps, M, (int)K, topk,
+    launch_pdl(moe_combine_kernel<32>, dim3((unsigned)Mp), dim3(256), 0, (cudaStream_t)stream, y, pos, scores, res, nw, eps, M, (int)K, topk,
                                                                              quant, h, xq, xs);
     SCMX_LAUNCH_OK("moe_combine_kernel");
     return SCMX_OK;
@@ -606,7 +626,7 @@ extern "C" int scmx_gather_rows(const int8_t* xq, const float* xs, const int32_t
                  "gather_rows: need rows_s <= rows_q and K %% 16 == 0");
     SCMX_REQUIRE(aligned16(xq) && aligned16(dst_q), SCMX_EINVAL, "gather_rows: buffers must be 16-byte aligned");
     if (rows_q == 0) return SCMX_OK;
-    gather_rows_kernel<<<(unsigned)rows_q, 128, 0, (cudaStream_t)stream>>>(xq, xs, tok, rows_s, (int)K, dst_q, dst_s);
+    launch_pdl(gather_rows_kernel, dim3((unsigned)rows_q), dim3(128), 0, (cudaStream_t)stream, xq, xs, tok, rows_s, (int)K, dst_q, dst_s);
     SCMX_LAUNCH_OK("gather_rows_kernel");
     return SCMX_OK;
 }
