@@ -204,8 +204,35 @@ def bench_decode(pkg, torch, model, reps=3):
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / reps
     nbytes = sum(gemv_bytes(n, k) for lw in model.layers for (_, _, _, n, k) in lw.values())
-    return dict(ms_per_step=ms, gemv_per_step=4 * len(model.layers), bytes_per_step=nbytes, gbs=nbytes / ms / 1e6,
-                us_per_gemv=ms * 1e3 / (4 * len(model.layers)))
+    out = dict(ms_per_step=ms, gemv_per_step=4 * len(model.layers), bytes_per_step=nbytes, gbs=nbytes / ms / 1e6,
+               us_per_gemv=ms * 1e3 / (4 * len(model.layers)))
+    # the GEMV kernel on a matrix large enough that launch latency does not matter: LM-head shaped, 151936 x 2048
+    # (vocabulary of the model family), 160 MB of packed weights per launch, three distinct launches per pass
+    F = pkg.sc_format
+    N, K = 151936, 2048
+    g = torch.Generator(device="cuda").manual_seed(5)
+    big = []
+    for _ in range(3):
+        w = torch.randn((N, K), generator=g, device="cuda") * 0.02
+        big.append(F.quantize_device(w, want_qw=False)[:3])
+        del w
+
+    def big_pass():
+        for c, b, w_ in big:
+            G.gemv(xq[K], c, b, xs, w_, N, 1)
+    for _ in range(2):
+        big_pass()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        big_pass()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) / reps / len(big) * 1e3
+    out["kernel_roofline"] = dict(kernel="gemv_stream_kernel", workload="151936 x 2048 SC-MXFP4 GEMV", bound="hbm",
+                                  algorithmic_bytes_per_launch=gemv_bytes(N, K), us_per_launch=us,
+                                  achieved=gemv_bytes(N, K) / us / 1e3, unit="GB/s")
+    return out
 
 
 def build_moe_block(pkg, torch, cfg=OLMOE, shard=(0, 1), seed=0, two_pass=False):
@@ -323,6 +350,8 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     pkg = importlib.import_module("mxfp4-int8-m5_b200")
+    if args.no_pdl:
+        pkg._lib.call("scmx_set_pdl", 0)
     pk = peaks()
     M, layers, hidden = QWEN["M"], QWEN["layers"], 2048
     lw = build_dense_layers(pkg, torch, layers, shard=(rank, world))
@@ -417,10 +446,16 @@ def run_ours(args):
                                         "4 all-gathers per layer",
                             l2="inputs larger than L2: 718 MB of packed weights per step", cuda_graph=graph is not None),
                 clocks=clocks, e2e=e2e, gpu_launches=stack.launches_per_layer * layers * args.steps)
+    if args.dense_only:
+        if rank == 0:
+            print(json.dumps(line))
+        return
     if world == 1:
         line["roofline"] = gemm_only_roofline(pkg, torch, stack, pk)
         line["decode"] = bench_decode(pkg, torch, stack)
         line["decode"]["hbm_frac"] = line["decode"]["gbs"] / pk["hbm_gbs"]
+        kr = line["decode"]["kernel_roofline"]
+        kr.update(peak=pk["hbm_gbs"], frac=kr["achieved"] / pk["hbm_gbs"])
     del stack, lw, graph
     torch.cuda.empty_cache()
     try:
@@ -461,6 +496,14 @@ def run_case(args):
         for _ in range(2):
             for c, b, w_ in sets:
                 G.gemv(xq, c, b, xs, w_, 12288, 3)
+    elif args.case == "gemvbig":  # one LM-head-shaped GEMV, 151936 x 2048 (160 MB of packed weights), three launches
+        w = torch.randn((151936, 2048), generator=g, device="cuda") * 0.02
+        c, b, w_, _, _ = F.quantize_device(w, want_qw=False)
+        del w
+        xq = torch.randint(-127, 128, (2048,), dtype=torch.int8, device="cuda", generator=g)
+        xs = torch.full((1,), 1e-2, device="cuda")
+        for _ in range(3):
+            G.gemv(xq, c, b, xs, w_, 151936, 1)
     else:
         bench_moe(pkg, torch, None, reps=1)
     torch.cuda.synchronize()
@@ -476,7 +519,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-overlap", action="store_true", help="decode weights on the main stream instead of a side stream")
-    ap.add_argument("--case", choices=["gemm", "gemv", "moe"], help="run one small kernel case (for profiler captures) and exit")
+    ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic stream serialization")
+    ap.add_argument("--dense-only", action="store_true", help="skip the roofline / decode / MoE / CPU sections")
+    ap.add_argument("--case", choices=["gemm", "gemv", "gemvbig", "moe"], help="run one small kernel case (for profiler captures) and exit")
     args = ap.parse_args()
     if args.case:
         run_case(args)

@@ -44,6 +44,16 @@ int make_dev_format(const scmx_format* fmt, DevFormat* out) {
     out->block = fmt->block;
     out->bc_bits = fmt->bc_bits;
     out->blocks_per_byte = 8 / fmt->bc_bits;
+    out->block_shift = -1;
+    for (int sft = 3; sft < 20; ++sft)
+        if (fmt->block == (1 << sft)) out->block_shift = sft;
+    out->pb_shift = fmt->bc_bits == 1 ? 3 : fmt->bc_bits == 2 ? 2 : fmt->bc_bits == 4 ? 1 : 0;
+    out->pb_mask = out->blocks_per_byte - 1;
+    out->bc_shift = fmt->bc_bits == 1 ? 0 : fmt->bc_bits == 2 ? 1 : fmt->bc_bits == 4 ? 2 : 3;
+    out->bc_mask = (1u << fmt->bc_bits) - 1u;
+    out->pow2 = 1;
+    for (int i = 0; i < fmt->n_mult; ++i)
+        if (fmt->mult[i] != (1 << i)) out->pow2 = 0;
     return SCMX_OK;
 }
 

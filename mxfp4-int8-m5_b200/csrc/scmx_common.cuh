@@ -78,6 +78,11 @@ struct DevFormat {
     int block;                   // weights per block code
     int bc_bits;
     int blocks_per_byte;         // 8 / bc_bits
+    int pow2;                    // 1 when mult[i] == 1 << i for every used i (the multiplier is a shift)
+    int block_shift;             // log2(block) when block is a power of two, else -1 (divisions are used instead)
+    int pb_shift, pb_mask;       // log2(blocks_per_byte), blocks_per_byte - 1
+    int bc_shift;                // log2(bc_bits)
+    uint32_t bc_mask;            // (1 << bc_bits) - 1
 };
 
 int make_dev_format(const scmx_format* fmt, DevFormat* out);
@@ -162,6 +167,17 @@ __device__ __forceinline__ int quant_code(float v, float qi) {
     return (int)fminf(fmaxf(r, -127.0f), 127.0f);
 }
 
+// Four quantization codes packed into a word: byte j = int8(rint(v[j] * qi)).  rint is taken by adding 1.5 * 2^23, whose
+// float spacing is exactly 1 (round-half-even), and the low byte of the sum's bit pattern is the two's-complement code;
+// |v * qi| <= 127 by construction of qi, so no clamp is needed.  The product and the sum are rounded separately.
+__device__ __forceinline__ uint32_t quant4(float v0, float v1, float v2, float v3, float qi) {
+    const uint32_t b0 = __float_as_uint(__fadd_rn(__fmul_rn(v0, qi), 12582912.0f));
+    const uint32_t b1 = __float_as_uint(__fadd_rn(__fmul_rn(v1, qi), 12582912.0f));
+    const uint32_t b2 = __float_as_uint(__fadd_rn(__fmul_rn(v2, qi), 12582912.0f));
+    const uint32_t b3 = __float_as_uint(__fadd_rn(__fmul_rn(v3, qi), 12582912.0f));
+    return (b0 & 0xFFu) | ((b1 & 0xFFu) << 8) | ((b2 & 0xFFu) << 16) | (b3 << 24);
+}
+
 // Decode one 32-bit word of 8 packed codes to two words of 4 INT8 each, given per-block byte LUTs
 // (positive magnitudes already multiplied by the block multiplier, and their negations).
 __device__ __forceinline__ void decode_word(uint32_t w, uint32_t plo, uint32_t phi, uint32_t nlo, uint32_t nhi,
@@ -193,6 +209,12 @@ __device__ __forceinline__ uint32_t fmt_mult(const DevFormat& f, uint32_t bc) {
 
 __device__ __forceinline__ uint32_t block_code(const uint8_t* row_bc, int blk, int bc_bits, int per_byte) {
     return (row_bc[blk / per_byte] >> (bc_bits * (blk % per_byte))) & ((1u << bc_bits) - 1u);
+}
+// Index of the block that holds element k of a row (shift when the block size is a power of two).
+__device__ __forceinline__ int block_of(const DevFormat& f, int k) { return f.block_shift >= 0 ? (k >> f.block_shift) : (k / f.block); }
+// Bit offset of block `blk` inside its byte, and the byte index: shifts only (bc_bits and codes per byte are powers of two).
+__device__ __forceinline__ uint32_t block_code_fast(const DevFormat& f, const uint8_t* row_bc, int blk) {
+    return (row_bc[blk >> f.pb_shift] >> ((blk & f.pb_mask) << f.bc_shift)) & f.bc_mask;
 }
 
 }  // namespace scmx

@@ -235,7 +235,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_i8_kernel(const __grid_co
                                                           const __grid_constant__ CUtensorMap tmB, const GemmArgs a) {
     using L = Smem<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);  // stays a shared-space pointer
     const uint32_t sbase = smem_u32(smem);
     const uint32_t bar_full = sbase + L::BAR_OFF, bar_empty = bar_full + 8 * STAGES;
     const uint32_t bar_tfull = bar_empty + 8 * STAGES, bar_tempty = bar_tfull + 16;

@@ -37,8 +37,43 @@ __device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
     return v;
 }
 
-// per-byte negation of four INT8 in -127..127
-__device__ __forceinline__ uint32_t neg4(uint32_t x) { return __vneg4(x); }
+// Per-byte two's-complement negation of four INT8 without carries between bytes:
+// -b = ~b + 1; the low seven bits of ~b plus one never overflow the byte, and the top bit is folded in with an XOR.
+__device__ __forceinline__ uint32_t neg4(uint32_t x) {
+    const uint32_t nx = ~x;
+    return ((nx & 0x7F7F7F7Fu) + 0x01010101u) ^ (nx & 0x80808080u);
+}
+
+// prmt.b32 in its default mode: selector nibble bits 0-2 pick one of the eight source bytes (every selector built below
+// has bit 3 of each nibble clear, so no sanitising AND is needed).
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+__device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+// sum over the 8 codes of word w of (+-x) * magnitude: 11 instructions
+__device__ __forceinline__ int word_dot(uint32_t w, uint32_t x0, uint32_t xn0, uint32_t x1, uint32_t xn1, uint32_t mlo, uint32_t mhi,
+                                        int acc) {
+    const uint32_t sel = w & 0x77777777u;
+    const uint32_t ssel = ((w >> 1) & 0x44444444u) | 0x32103210u;
+    acc = dp4a_ss(prmt(x0, xn0, ssel), prmt(mlo, mhi, sel), acc);
+    return dp4a_ss(prmt(x1, xn1, ssel >> 16), prmt(mlo, mhi, sel >> 16), acc);
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds8(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
 
 template <int STEPS, bool B32>
 __global__ void __launch_bounds__(256) gemv_kernel(const GemvArgs a) {
@@ -74,13 +109,12 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvArgs a) {
                 w[s][r] = ldg_stream(reinterpret_cast<const uint4*>(codes + (size_t)(n0 + r) * wpr + k0 / 8));
                 const uint8_t* rb = bcodes + (size_t)(n0 + r) * a.bc_row_bytes;
                 if (B32) {
-                    const int blk = k0 / a.f.block;
-                    bc[s][r] = rb[blk / a.f.blocks_per_byte];
+                    bc[s][r] = rb[block_of(a.f, k0) >> a.f.pb_shift];
                 } else {
                     // the lane's 32 codes span 32/block blocks whose codes fit one aligned 32-bit field
-                    const int bit0 = (k0 / a.f.block) * a.f.bc_bits;
+                    const int bit0 = (k0 >> a.f.block_shift) << a.f.bc_shift;
                     uint32_t v = 0;
-                    const int nbytes = (32 / a.f.block * a.f.bc_bits + 7) / 8;
+                    const int nbytes = (((32 >> a.f.block_shift) << a.f.bc_shift) + 7) / 8;
                     for (int i = 0; i < nbytes; ++i) v |= (uint32_t)rb[bit0 / 8 + i] << (8 * i);
                     bc[s][r] = v >> (bit0 % 8);
                 }
@@ -104,8 +138,8 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvArgs a) {
         for (int r = 0; r < 4; ++r) {
             const uint32_t ww[4] = {w[s][r].x, w[s][r].y, w[s][r].z, w[s][r].w};
             if (B32) {
-                const int blk = k0s[s] / a.f.block;
-                const uint32_t code = (bc[s][r] >> (a.f.bc_bits * (blk % a.f.blocks_per_byte))) & ((1u << a.f.bc_bits) - 1u);
+                const int blk = block_of(a.f, k0s[s]);
+                const uint32_t code = (bc[s][r] >> ((blk & a.f.pb_mask) << a.f.bc_shift)) & a.f.bc_mask;
                 int bs = 0;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -115,12 +149,12 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvArgs a) {
                     bs = __dp4a((int)__byte_perm(x[2 * j + 1], xn[2 * j + 1], ssel >> 16),
                                 (int)__byte_perm(a.f.mag_lo, a.f.mag_hi, sel >> 16), bs);
                 }
-                tot[r] += bs * (int)fmt_mult(a.f, code);
+                tot[r] += a.f.pow2 ? (bs << code) : bs * (int)fmt_mult(a.f, code);
             } else {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const int bi = (8 * j) / a.f.block;   // block index inside the lane's 32 codes
-                    const uint32_t code = (bc[s][r] >> (a.f.bc_bits * bi)) & ((1u << a.f.bc_bits) - 1u);
+                    const int bi = (8 * j) >> a.f.block_shift;   // block index inside the lane's 32 codes
+                    const uint32_t code = (bc[s][r] >> (bi << a.f.bc_shift)) & a.f.bc_mask;
                     const uint32_t sel = ww[j] & 0x77777777u;
                     const uint32_t ssel = ((ww[j] >> 1) & 0x44444444u) | 0x32103210u;
                     int bs = __dp4a((int)__byte_perm(x[2 * j], xn[2 * j], ssel), (int)__byte_perm(a.f.mag_lo, a.f.mag_hi, sel), 0);
@@ -174,22 +208,24 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvArgs a) {
 }
 
 // ---- streaming variant for dense GEMVs ------------------------------------------------------------------------------------
-// A persistent CTA (one per SM, 288 threads) walks over tiles of TR consecutive weight rows.  The rows of a tile are
+// A persistent CTA (one per SM, 544 threads) walks over tiles of TR consecutive weight rows.  The rows of a tile are
 // contiguous in the packed layout, so one thread streams each tile into a shared-memory ring with two untiled bulk copies
-// (codes, block codes) that complete on an mbarrier; eight consumer warps expand and accumulate from shared memory
+// (codes, block codes) that complete on an mbarrier; sixteen consumer warps expand and accumulate from shared memory
 // (warp = 4 rows x one K split) and release the stage through a second mbarrier.  Copies run STAGES tiles ahead of the
 // arithmetic, and since weights do not depend on the previous kernel they start before griddepcontrol.wait: with one CTA
 // of < 112 KB per SM the next GEMV of a chain is already resident and filling its ring while this one finishes.
-constexpr int SG_STAGE_BYTES = 32768;      // packed codes per stage
-constexpr int SG_BC_BYTES = 1024;          // block codes per stage
+constexpr int SG_STAGE_BYTES = 65536;      // packed codes per stage
+constexpr int SG_BC_BYTES = 2048;          // block codes per stage
 constexpr int SG_X_BYTES = 8192;           // INT8 activations (K <= 8192)
 constexpr int SG_STAGES = 3;
-constexpr int SG_THREADS = 288;            // 8 consumer warps + 1 producer warp
+constexpr int SG_NW = 16;                  // consumer warps
+constexpr int SG_THREADS = 32 * (SG_NW + 1);   // consumer warps + 1 producer warp
 
 struct StreamArgs {
     GemvArgs g;
-    int tr;            // rows per tile (4, 8, 16 or 32)
+    int tr;            // rows per tile (4, 8, 16, 32 or 64)
     int n_tiles;
+    int mode;          // 0 normal; 1 = measurement aid: stream the tiles but skip the arithmetic
     int32_t* status;
 };
 
@@ -197,30 +233,30 @@ template <bool B32>
 __global__ void __launch_bounds__(SG_THREADS, 1) gemv_stream_kernel(const StreamArgs sa) {
     extern __shared__ uint8_t smem_raw[];
     const GemvArgs& a = sa.g;
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127);
-    // layout: [STAGES][codes 32 KB][bcodes 1 KB] | x (K bytes) | split-K sums [4][8][4] | split-K counters [4][8] |
+    uint8_t* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);     // stays a shared-space pointer
+    // layout: [STAGES][codes 64 KB][bcodes 2 KB] | x (K bytes) | split-K sums [4][16][4] | split-K counters [4][16] |
     //         barriers | abort flag
     uint8_t* s_x = smem + SG_STAGES * (SG_STAGE_BYTES + SG_BC_BYTES);
     int* s_part = reinterpret_cast<int*>(s_x + SG_X_BYTES);
-    int* s_cnt = s_part + 128;
-    const uint32_t bar_full = smem_u32(s_cnt + 32), bar_empty = bar_full + 8 * SG_STAGES;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(s_cnt + 32 + 4 * SG_STAGES);
+    int* s_cnt = s_part + 256;
+    const uint32_t bar_full = smem_u32(s_cnt + 64), bar_empty = bar_full + 8 * SG_STAGES;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(s_cnt + 64 + 4 * SG_STAGES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int K = a.K, row_bytes = K / 2, bc_row = a.bc_row_bytes;
     if (threadIdx.x == 0) {
         for (int s = 0; s < SG_STAGES; ++s) {
             mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, 8);
+            mbar_init(bar_empty + 8 * s, SG_NW);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (threadIdx.x < 160) s_part[threadIdx.x] = 0;      // split-K sums and counters
+    if (threadIdx.x < 320) s_part[threadIdx.x] = 0;      // split-K sums and counters
     pdl_launch_dependents();
     __syncthreads();
     int fail = 0;
-    if (warp == 8) {
+    if (warp == SG_NW) {
         // ---- producer: weights only, so it does not wait for the previous kernel
         if (lane == 0) {
             int stage = 0;
@@ -240,61 +276,80 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv_stream_kernel(const Stream
     } else {
         // ---- consumers: activations come from the previous kernel
         pdl_wait();
-        for (int i = threadIdx.x; i < K / 16; i += 256)
+        for (int i = threadIdx.x; i < K / 16; i += 32 * SG_NW)
             reinterpret_cast<uint4*>(s_x)[i] = reinterpret_cast<const uint4*>(a.xq)[i];
-        asm volatile("bar.sync 1, 256;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * SG_NW) : "memory");
         const int rg = sa.tr / 4;                 // row groups per tile
-        const int sk = 8 / rg;                    // K splits per row group
+        const int sk = SG_NW / rg;                // K splits per row group
         const int rgi = warp % rg, ks = warp / rg;
         const int kbeg = ks * (K / sk), kend = kbeg + K / sk;
         const float xs = a.epi != 0 ? a.xscale[0] : 0.0f;
+        const uint32_t mlo = a.f.mag_lo, mhi = a.f.mag_hi;
+        // A lane visits the same K offsets in every tile.  When its K range is at most two steps of 1024 codes the
+        // activations (and their negations) for those offsets stay in registers for the whole kernel.
+        const bool xcache = (kend - kbeg) <= 2048;
+        uint32_t xr[2][8], xnr[2][8];
+#pragma unroll
+        for (int sidx = 0; sidx < 2; ++sidx) {
+            const int k0 = kbeg + lane * 32 + sidx * 1024;
+            const bool ok = xcache && k0 < kend;
+            const uint4 xa = ok ? *reinterpret_cast<const uint4*>(s_x + k0) : make_uint4(0, 0, 0, 0);
+            const uint4 xb = ok ? *reinterpret_cast<const uint4*>(s_x + k0 + 16) : make_uint4(0, 0, 0, 0);
+            const uint32_t xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { xr[sidx][j] = xv[j]; xnr[sidx][j] = neg4(xv[j]); }
+        }
         int stage = 0, it = 0;
         uint32_t phase = 0;
         for (int t = blockIdx.x; t < sa.n_tiles; t += gridDim.x) {
             if (int w = mbar_wait(bar_full + 8 * stage, phase, abort_flag)) { fail = w == 1 ? 2 : -1; }
             if (fail) break;
             const uint8_t* st = smem + stage * (SG_STAGE_BYTES + SG_BC_BYTES);
+            const uint32_t st_s = smem_u32(st);
             const int r0 = t * sa.tr + 4 * rgi;      // first of this warp's 4 rows
             const bool rows_ok = r0 < a.N;
             int tot[4] = {0, 0, 0, 0};
             if (rows_ok) {
-                for (int k0 = kbeg + lane * 32; k0 < kend; k0 += 1024) {
-                    const uint4 xa = *reinterpret_cast<const uint4*>(s_x + k0);
-                    const uint4 xb = *reinterpret_cast<const uint4*>(s_x + k0 + 16);
-                    const uint32_t x[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-                    uint32_t xn[8];
+#pragma unroll 2
+                for (int sidx = 0; sidx < 32; ++sidx) {
+                    const int k0 = kbeg + lane * 32 + sidx * 1024;
+                    if (k0 >= kend) break;
+                    uint32_t x[8], xn[8];
+                    if (xcache) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) xn[j] = neg4(x[j]);
+                        for (int j = 0; j < 8; ++j) { x[j] = xr[sidx & 1][j]; xn[j] = xnr[sidx & 1][j]; }
+                    } else {
+                        const uint4 xa = *reinterpret_cast<const uint4*>(s_x + k0);
+                        const uint4 xb = *reinterpret_cast<const uint4*>(s_x + k0 + 16);
+                        const uint32_t xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) { x[j] = xv[j]; xn[j] = neg4(xv[j]); }
+                    }
 #pragma unroll
                     for (int r = 0; r < 4; ++r) {
-                        const uint8_t* rowp = st + (size_t)(4 * rgi + r) * row_bytes;
-                        const uint4 wv = *reinterpret_cast<const uint4*>(rowp + k0 / 2);
+                        const uint32_t row_s = st_s + (uint32_t)(4 * rgi + r) * (uint32_t)row_bytes;
+                        const uint4 wv = lds128(row_s + (uint32_t)(k0 >> 1));
                         const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+                        if (sa.mode == 1) { tot[r] += (int)(ww[0] ^ ww[1] ^ ww[2] ^ ww[3] ^ x[r]); continue; }
+                        const uint32_t rb_s = st_s + SG_STAGE_BYTES + (uint32_t)(4 * rgi + r) * (uint32_t)bc_row;
                         const uint8_t* rb = st + SG_STAGE_BYTES + (size_t)(4 * rgi + r) * bc_row;
                         if (B32) {
-                            const int blk = k0 / a.f.block;
-                            const uint32_t code = (rb[blk / a.f.blocks_per_byte] >> (a.f.bc_bits * (blk % a.f.blocks_per_byte))) &
-                                                  ((1u << a.f.bc_bits) - 1u);
+                            const int blk = block_of(a.f, k0);
+                            const uint32_t code = (lds8(rb_s + (uint32_t)(blk >> a.f.pb_shift)) >> ((blk & a.f.pb_mask) << a.f.bc_shift)) & a.f.bc_mask;
                             int bs = 0;
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const uint32_t sel = ww[j] & 0x77777777u;
-                                const uint32_t ssel = ((ww[j] >> 1) & 0x44444444u) | 0x32103210u;
-                                bs = __dp4a((int)__byte_perm(x[2 * j], xn[2 * j], ssel), (int)__byte_perm(a.f.mag_lo, a.f.mag_hi, sel), bs);
-                                bs = __dp4a((int)__byte_perm(x[2 * j + 1], xn[2 * j + 1], ssel >> 16),
-                                            (int)__byte_perm(a.f.mag_lo, a.f.mag_hi, sel >> 16), bs);
-                            }
-                            tot[r] += bs * (int)fmt_mult(a.f, code);
+                            for (int j = 0; j < 4; ++j) bs = word_dot(ww[j], x[2 * j], xn[2 * j], x[2 * j + 1], xn[2 * j + 1], mlo, mhi, bs);
+                            tot[r] += a.f.pow2 ? (bs << code) : bs * (int)fmt_mult(a.f, code);
                         } else {
-                            const int bit0 = (k0 / a.f.block) * a.f.bc_bits;
-                            const int nbytes = (32 / a.f.block * a.f.bc_bits + 7) / 8;
+                            const int bit0 = (k0 >> a.f.block_shift) << a.f.bc_shift;
+                            const int nbytes = (((32 >> a.f.block_shift) << a.f.bc_shift) + 7) / 8;
                             uint32_t bcv = 0;
                             for (int i = 0; i < nbytes; ++i) bcv |= (uint32_t)rb[bit0 / 8 + i] << (8 * i);
                             bcv >>= (bit0 % 8);
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
-                                const int bi = (8 * j) / a.f.block;
-                                const uint32_t code = (bcv >> (a.f.bc_bits * bi)) & ((1u << a.f.bc_bits) - 1u);
+                                const int bi = (8 * j) >> a.f.block_shift;
+                                const uint32_t code = (bcv >> (bi << a.f.bc_shift)) & a.f.bc_mask;
                                 const uint32_t sel = ww[j] & 0x77777777u;
                                 const uint32_t ssel = ((ww[j] >> 1) & 0x44444444u) | 0x32103210u;
                                 int bs = __dp4a((int)__byte_perm(x[2 * j], xn[2 * j], ssel), (int)__byte_perm(a.f.mag_lo, a.f.mag_hi, sel), 0);
@@ -314,17 +369,17 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv_stream_kernel(const Stream
             bool writer = lane == 0;
             if (sk > 1 && lane == 0) {
                 // add the K splits of a row group (exact integers) without a barrier: the last split to arrive finishes
-                int* accp = s_part + ((it & 3) * 8 + rgi) * 4;
+                int* accp = s_part + ((it & 3) * 16 + rgi) * 4;
 #pragma unroll
                 for (int r = 0; r < 4; ++r) atomicAdd(accp + r, tot[r]);
                 __threadfence_block();
-                const int c = atomicAdd(s_cnt + (it & 3) * 8 + rgi, 1);
+                const int c = atomicAdd(s_cnt + (it & 3) * 16 + rgi, 1);
                 writer = c == sk - 1;
                 if (writer) {
                     __threadfence_block();
 #pragma unroll
                     for (int r = 0; r < 4; ++r) tot[r] = atomicExch(accp + r, 0);
-                    atomicExch(s_cnt + (it & 3) * 8 + rgi, 0);
+                    atomicExch(s_cnt + (it & 3) * 16 + rgi, 0);
                 }
             }
             ++it;
@@ -385,7 +440,7 @@ using namespace scmx;
 
 static int g_gemv_stream = 1;
 extern "C" int scmx_set_gemv_stream(int enable) {
-    g_gemv_stream = enable ? 1 : 0;
+    g_gemv_stream = enable;
     return SCMX_OK;
 }
 
@@ -416,16 +471,18 @@ extern "C" int scmx_gemv(const int8_t* xq, const float* xscale, const uint32_t* 
     a.out = out; a.N = (int)N; a.K = (int)K; a.epi = epi; a.n_routed = n_routed; a.shared = shared; a.xstride = xstride;
     a.bc_row_bytes = (int)(K / (a.f.block * a.f.blocks_per_byte));
     // ---- streaming kernel for dense GEMVs whose tiles satisfy the bulk-copy alignment rules
-    if (!eidx && K <= SG_X_BYTES && K % 32 == 0 && (a.bc_row_bytes % 4) == 0 && (reinterpret_cast<uintptr_t>(bcodes) & 15) == 0 &&
+    // (matrices under 16 MB finish within a few microseconds either way and start faster with the register kernel below)
+    if (!eidx && (g_gemv_stream == 2 || g_gemv_stream == 3 || N * K / 2 >= (16ll << 20)) && K <= SG_X_BYTES && K % 32 == 0 && (a.bc_row_bytes % 4) == 0 && (reinterpret_cast<uintptr_t>(bcodes) & 15) == 0 &&
         g_gemv_stream) {
-        int tr = 32;
-        while (tr > 4 && ((int64_t)tr * (K / 2) > SG_STAGE_BYTES || (N + tr - 1) / tr < 148)) tr >>= 1;
-        if ((int64_t)tr * (K / 2) <= SG_STAGE_BYTES && (int64_t)tr * a.bc_row_bytes <= SG_BC_BYTES && (K / (8 / (tr / 4))) % 32 == 0) {
+        int tr = 64;
+        while (tr > 4 && ((int64_t)tr * (K / 2) > SG_STAGE_BYTES || (N + tr - 1) / tr < 96)) tr >>= 1;
+        if ((int64_t)tr * (K / 2) <= SG_STAGE_BYTES && (int64_t)tr * a.bc_row_bytes <= SG_BC_BYTES && (K / (SG_NW / (tr / 4))) % 32 == 0) {
             StreamArgs sa;
             sa.g = a;
             sa.tr = tr;
             sa.n_tiles = (int)((N + tr - 1) / tr);
             sa.status = nullptr;
+            sa.mode = g_gemv_stream == 2 ? 1 : 0;
             static int n_sm = 0;
             if (!n_sm) {
                 int dev = 0;
@@ -433,7 +490,7 @@ extern "C" int scmx_gemv(const int8_t* xq, const float* xscale, const uint32_t* 
                 cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
             }
             const int grid = sa.n_tiles < n_sm ? sa.n_tiles : n_sm;
-            const size_t smem = SG_STAGES * (SG_STAGE_BYTES + SG_BC_BYTES) + SG_X_BYTES + 640 + 8 * 2 * SG_STAGES + 16 + 128;
+            const size_t smem = SG_STAGES * (SG_STAGE_BYTES + SG_BC_BYTES) + SG_X_BYTES + 1280 + 8 * 2 * SG_STAGES + 16 + 128;
             const bool b32s = a.f.block % 32 == 0;
             static bool configured = false;
             if (!configured) {

@@ -5,24 +5,24 @@
 
 namespace scmx {
 
-// ---- unpack: thread = one uint4 of codes (32 weights) ------------------------------------------------------------
+// ---- unpack: thread = one uint4 of codes (32 weights); block = 64 vectors x 4 rows, no index divisions ---------------------
 __global__ void __launch_bounds__(256) unpack_kernel(const uint4* __restrict__ codes, const uint8_t* __restrict__ bcodes,
-                                                     int64_t n_vec, int vec_per_row, int bc_row_bytes, DevFormat f,
+                                                     int64_t N, int vec_per_row, int bc_row_bytes, DevFormat f,
                                                      uint4* __restrict__ wq) {
     pdl_launch_dependents();
     pdl_wait();
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n_vec) return;
-    const int64_t n = i / vec_per_row;
-    const int k0 = (int)(i % vec_per_row) * 32;
+    const int64_t n = (int64_t)blockIdx.x * 4 + threadIdx.y;
+    const int v = blockIdx.y * 64 + threadIdx.x;
+    if (n >= N || v >= vec_per_row) return;
+    const int64_t i = n * vec_per_row + v;
+    const int k0 = v * 32;
     const uint4 c = codes[i];
     const uint32_t w[4] = {c.x, c.y, c.z, c.w};
     const uint8_t* bc = bcodes + n * bc_row_bytes;
     uint32_t o[8];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-        const int blk = (k0 + 8 * j) / f.block;
-        const uint32_t m = fmt_mult(f, block_code(bc, blk, f.bc_bits, f.blocks_per_byte));
+        const uint32_t m = fmt_mult(f, block_code_fast(f, bc, block_of(f, k0 + 8 * j)));
         const uint32_t plo = lut_scale(f.mag_lo, m), phi = lut_scale(f.mag_hi, m);
         decode_word(w[j], plo, phi, lut_negate(plo), lut_negate(phi), o[2 * j], o[2 * j + 1]);
     }
@@ -158,7 +158,9 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(const uint16_t* __re
 struct RowSegs {
     int w8;              // 16-byte vectors per segment row
     int64_t stride8;     // distance between segments in 16-byte vectors
+    // position of 16-byte vector v of row `row`; ordinary matrices (one segment) need no division
     __device__ __forceinline__ int64_t index(int64_t row, int v) const {
+        if (stride8 == 0) return row * w8 + v;
         return (int64_t)(v / w8) * stride8 + row * w8 + (v % w8);
     }
 };
@@ -253,11 +255,8 @@ __global__ void __launch_bounds__(256) row_quant_warp_kernel(const uint16_t* __r
         const int v = i * 32 + lane;
         if (v < nv) {
             float f[8];
-            int q[8];
             unpack8(raw[i], f);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) q[j] = quant_code(f[j], qi);
-            qrow[v] = pack8_i8(q);
+            qrow[v] = make_uint2(quant4(f[0], f[1], f[2], f[3], qi), quant4(f[4], f[5], f[6], f[7], qi));
         }
     }
     if (lane == 0) xs[row] = s;
@@ -337,11 +336,8 @@ __global__ void __launch_bounds__(256) row_quant_block_kernel(const uint16_t* __
         const int v = i * 256 + threadIdx.x;
         if (v < nv) {
             float f[8];
-            int q[8];
             unpack8(raw[i], f);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) q[j] = quant_code(f[j], qi);
-            qrow[v] = pack8_i8(q);
+            qrow[v] = make_uint2(quant4(f[0], f[1], f[2], f[3], qi), quant4(f[4], f[5], f[6], f[7], qi));
         }
     }
     if (threadIdx.x == 0) xs[row] = s;
@@ -540,10 +536,12 @@ extern "C" int scmx_unpack_i8(const uint32_t* codes, const uint8_t* bcodes, int6
                  "unpack_i8: block=%d must divide or be a multiple of 32", f.block);
     SCMX_REQUIRE(aligned16(codes) && aligned16(wq), SCMX_EINVAL, "unpack_i8: codes and wq must be 16-byte aligned");
     if (N == 0) return SCMX_OK;
-    const int64_t n_vec = N * K / 32;
+    const int vec_per_row = (int)(K / 32);
     const int bc_row = (int)(K / (f.block * f.blocks_per_byte));
-    launch_pdl(unpack_kernel, dim3((unsigned)((n_vec + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, 
-        reinterpret_cast<const uint4*>(codes), bcodes, n_vec, (int)(K / 32), bc_row, f, reinterpret_cast<uint4*>(wq));
+    SCMX_REQUIRE((vec_per_row + 63) / 64 <= 65535, SCMX_ELIMIT, "unpack_i8: K too large");
+    launch_pdl(unpack_kernel, dim3((unsigned)((N + 3) / 4), (unsigned)((vec_per_row + 63) / 64)), dim3(64, 4), 0,
+               (cudaStream_t)stream, reinterpret_cast<const uint4*>(codes), bcodes, N, vec_per_row, bc_row, f,
+               reinterpret_cast<uint4*>(wq));
     SCMX_LAUNCH_OK("unpack_kernel");
     return SCMX_OK;
 }
