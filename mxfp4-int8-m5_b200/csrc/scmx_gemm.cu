@@ -499,6 +499,28 @@ static int run_gemm(const int8_t* xq, int64_t a_rows, const int8_t* wq, int64_t 
     return launch_gemm<128, 6>(tmA, tmB, a, grid, st);
 }
 
+// A per-device side stream and the events that order it against the caller's stream (created on first use; event waits and
+// records are legal during stream capture, where they become graph dependencies).
+struct SideStream {
+    cudaStream_t side;
+    cudaEvent_t fork, decoded[2], gemm_done[2];
+};
+static int side_stream(SideStream** out) {
+    static SideStream ctx[64];
+    static bool ready[64] = {};
+    int dev = 0;
+    SCMX_CUDA_OK(cudaGetDevice(&dev));
+    SCMX_REQUIRE(dev >= 0 && dev < 64, SCMX_ELIMIT, "device ordinal %d out of range", dev);
+    if (!ready[dev]) {
+        SCMX_CUDA_OK(cudaStreamCreateWithFlags(&ctx[dev].side, cudaStreamNonBlocking));
+        cudaEvent_t* ev[5] = {&ctx[dev].fork, &ctx[dev].decoded[0], &ctx[dev].decoded[1], &ctx[dev].gemm_done[0], &ctx[dev].gemm_done[1]};
+        for (int i = 0; i < 5; ++i) SCMX_CUDA_OK(cudaEventCreateWithFlags(ev[i], cudaEventDisableTiming));
+        ready[dev] = true;
+    }
+    *out = &ctx[dev];
+    return SCMX_OK;
+}
+
 static int check_common(const char* who, int64_t N, int64_t K, int epi, const float* xscale, const float* wscale,
                         const void* out, const int32_t* status) {
     SCMX_REQUIRE(N > 0 && N % 32 == 0 && N < (1ll << 30), SCMX_EINVAL, "%s: N=%lld must be a positive multiple of 32", who,
@@ -576,17 +598,39 @@ extern "C" int scmx_moe_mm(const int8_t* xq, int64_t R, const uint32_t* codes, c
     if (R == 0) return SCMX_OK;
     const int64_t wpe = N * K / 8;                              // code words per expert
     const int64_t bpe = N * (K / (f.block * f.blocks_per_byte));  // block-code bytes per expert
-    int pass = 0;
-    for (int e0 = 0; e0 < E; e0 += experts_per_pass, ++pass) {
+    cudaStream_t main_s = (cudaStream_t)stream;
+    SideStream* sd = nullptr;
+    rc = side_stream(&sd);
+    if (rc) return rc;
+    const int passes = (E + experts_per_pass - 1) / experts_per_pass;
+    // The decode of pass p+1 runs on a side stream while the GEMM of pass p runs on the caller's stream; two scratch
+    // halves alternate, so the decode of pass p+1 also waits for the GEMM of pass p-1 (the last reader of its half).
+    auto decode = [&](int p, cudaStream_t st) -> int {
+        const int e0 = p * experts_per_pass;
         const int e1 = e0 + experts_per_pass < E ? e0 + experts_per_pass : E;
-        int8_t* buf = scratch + (pass & 1) * half;
-        rc = scmx_unpack_i8(codes + e0 * wpe, bcodes + e0 * bpe, (int64_t)(e1 - e0) * N, K, fmt, buf, stream);
-        if (rc) return rc;
+        return scmx_unpack_i8(codes + e0 * wpe, bcodes + e0 * bpe, (int64_t)(e1 - e0) * N, K, fmt, scratch + (p & 1) * half, st);
+    };
+    SCMX_CUDA_OK(cudaEventRecord(sd->fork, main_s));
+    SCMX_CUDA_OK(cudaStreamWaitEvent(sd->side, sd->fork, 0));
+    rc = decode(0, sd->side);
+    if (rc) return rc;
+    SCMX_CUDA_OK(cudaEventRecord(sd->decoded[0], sd->side));
+    for (int p = 0; p < passes; ++p) {
+        if (p + 1 < passes) {
+            if (p >= 1) SCMX_CUDA_OK(cudaStreamWaitEvent(sd->side, sd->gemm_done[(p - 1) & 1], 0));
+            rc = decode(p + 1, sd->side);
+            if (rc) return rc;
+            SCMX_CUDA_OK(cudaEventRecord(sd->decoded[(p + 1) & 1], sd->side));
+        }
+        SCMX_CUDA_OK(cudaStreamWaitEvent(main_s, sd->decoded[p & 1], 0));
+        const int e0 = p * experts_per_pass;
+        const int e1 = e0 + experts_per_pass < E ? e0 + experts_per_pass : E;
         GemmArgs a = {};
         a.M = (int)R; a.N = (int)N; a.K = (int)K; a.epi = epi; a.xscale = xscale; a.wscale = wscale; a.out = out;
         a.off = off; a.tstart = tstart; a.E = E; a.e_begin = e0; a.e_end = e1; a.status = status;
-        rc = run_gemm(xq, R, buf, (int64_t)(e1 - e0) * N, a, (cudaStream_t)stream);
+        rc = run_gemm(xq, R, scratch + (p & 1) * half, (int64_t)(e1 - e0) * N, a, main_s);
         if (rc) return rc;
+        SCMX_CUDA_OK(cudaEventRecord(sd->gemm_done[p & 1], main_s));
     }
     return SCMX_OK;
 }
