@@ -264,8 +264,18 @@ def bench_moe(pkg, torch, dist=None, reps=5):
     world = dist.get_world_size() if dist is not None else 1
     rank = dist.get_rank() if dist is not None else 0
     blk = build_moe_block(pkg, torch, shard=(rank, world))
-    layer = pkg.parallel.ExpertParallelMoe(pkg, blk, c["E"], c["topk"]) if world > 1 else blk
     Lr = c["tokens"] // world
+    exchange = "none"
+    if world > 1:
+        try:
+            layer = pkg.parallel.PeerExpertParallelMoe(pkg, blk, c["E"], c["topk"], Lr)
+            exchange = "dispatch/return kernels over NVLink peer memory, CUDA graph"
+        except Exception as e:   # noqa: BLE001
+            print(f"# peer-memory path unavailable ({type(e).__name__}: {e}); using NCCL all-to-all, eager launches", file=sys.stderr)
+            layer = pkg.parallel.ExpertParallelMoe(pkg, blk, c["E"], c["topk"])
+            exchange = "NCCL all-to-all, eager launches"
+    else:
+        layer = blk
     g = torch.Generator(device="cuda").manual_seed(1)
     h = torch.randn((c["tokens"], c["D"]), generator=g, device="cuda").to(torch.bfloat16)[rank * Lr:(rank + 1) * Lr].contiguous()
     logits = torch.randn((c["tokens"], c["E"]), generator=g, device="cuda")[rank * Lr:(rank + 1) * Lr].contiguous()
@@ -273,12 +283,25 @@ def bench_moe(pkg, torch, dist=None, reps=5):
         layer.step(h, logits)
     torch.cuda.synchronize()
     pkg._lib.check_status()
+    run = lambda: layer.step(h, logits)   # noqa: E731
+    if world == 1 or exchange.startswith("dispatch"):
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                layer.step(h, logits)
+            run = graph.replay
+        except Exception as e:   # noqa: BLE001
+            print(f"# MoE graph capture unavailable ({type(e).__name__}: {e})", file=sys.stderr)
+            torch.cuda.synchronize()
+    for _ in range(2):
+        run()
+    torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(reps):
-        layer.step(h, logits)
+        run()
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / reps
@@ -289,7 +312,7 @@ def bench_moe(pkg, torch, dist=None, reps=5):
     ops = 2 * c["tokens"] * c["topk"] * 3 * c["F"] * c["D"]
     return dict(ms_per_half_block=ms, tokens_per_s_one_layer=c["tokens"] / ms * 1e3,
                 tokens_per_s_16_layers=c["tokens"] / (ms * c["layers"]) * 1e3, tops=ops / ms / 1e9,
-                parallelism="single GPU" if world == 1 else f"ep{world}: {c['E'] // world} experts and {Lr} tokens per GPU, NCCL all-to-all")
+                parallelism="single GPU" if world == 1 else f"ep{world}: {c['E'] // world} experts and {Lr} tokens per GPU, {exchange}")
 
 
 def gemm_only_roofline(pkg, torch, stack, pk, reps=3):
@@ -358,11 +381,18 @@ def run_ours(args):
     g = torch.Generator(device="cuda").manual_seed(123)
     h0 = torch.randn((M, hidden), generator=g, device="cuda").to(torch.bfloat16)
     o0 = torch.randn((M, hidden), generator=g, device="cuda").to(torch.bfloat16)
+    collectives = "none"
     if world == 1:
         stack = pkg.fused_dense.DenseStack(lw, M, hidden, overlap=not args.no_overlap)
         hin, oin = h0, o0
     else:      # residual stream in segment layout [G, M, hidden/G]; this rank's columns of the attention output
-        stack = pkg.parallel.TensorParallelDense(pkg, lw, M, hidden)
+        try:      # all-gathers as kernels over peer memory: the step can be replayed from a CUDA graph
+            stack = pkg.parallel.PeerTensorParallelDense(pkg, lw, M, hidden, QWEN["groups"]["down"][1])
+            collectives = "store-based all-gather kernels over NVLink peer memory"
+        except Exception as e:   # noqa: BLE001
+            print(f"# peer-memory path unavailable ({type(e).__name__}: {e}); using NCCL all-gather, eager launches", file=sys.stderr)
+            stack = pkg.parallel.TensorParallelDense(pkg, lw, M, hidden)
+            collectives = "NCCL all-gather"
         w = hidden // world
         hin = h0.view(M, world, w).permute(1, 0, 2).contiguous()
         oin = o0[:, rank * w:(rank + 1) * w].contiguous()
@@ -377,8 +407,8 @@ def run_ours(args):
     torch.cuda.synchronize()
     pkg._lib.check_status()
     graph = None
-    # (multi-rank steps contain NCCL collectives and are timed as eager launches)
-    if not args.no_graph and world == 1:
+    # (a multi-rank step with NCCL collectives is timed as eager launches; with peer-memory kernels it is captured)
+    if not args.no_graph and (world == 1 or collectives.startswith("store")):
         try:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
@@ -443,7 +473,7 @@ def run_ours(args):
                 config=dict(workload="qwen3-1.7b-shaped dense prefill: 28 layers x (qkv, o, gate|up, down), M=2048 tokens, "
                                      "SC-MXFP4 W4A8, random-init N(0,0.02) weights",
                             parallelism="single GPU" if world == 1 else f"tp{world}: weights sharded by output column, "
-                                        "4 all-gathers per layer",
+                                        f"4 all-gathers per layer ({collectives})",
                             l2="inputs larger than L2: 718 MB of packed weights per step", cuda_graph=graph is not None),
                 clocks=clocks, e2e=e2e, gpu_launches=stack.launches_per_layer * layers * args.steps)
     if args.dense_only:

@@ -160,6 +160,37 @@ int scmx_moe_mm_static(const int8_t* xq, int64_t R, const uint32_t* codes, const
                        const int32_t* off, const int32_t* tstart, int E, int64_t N, int64_t K, const scmx_format* fmt,
                        int epi, const float* xscale, void* out, int tm, int32_t* status, void* stream);
 
+/* ---- expert-parallel exchange over peer memory (multi-GPU; the reference is single-device and has no counterpart) ----
+ * `*_peers` are HOST arrays of `world` device pointers: entry r is the buffer of that name on rank r's GPU, mapped into
+ * this process (CUDA IPC), entry `rank` the local one.  Buffers per GPU: rx_q int8 [world, cap, K], rx_s f32 [world, cap],
+ * rx_meta int32 [world, E/world + 1], y_back bf16 [cap, D], flags int32 [world] (zeroed once), epoch int32 [1] (zeroed once).
+ * cap = the most rows one rank can send (tokens_per_rank * topk).  world <= 8, E/world <= 128. */
+
+/* Stores every sorted assignment row (xq[tok[p]], xs[tok[p]]) into the owner rank's rx_q / rx_s at [rank][p - off[first
+ * expert of the owner]], and the per-expert counts plus that base row into the owner's rx_meta[rank]. */
+int scmx_ep_dispatch(const int8_t* xq, const float* xs, const int32_t* tok, const int32_t* esorted, const int32_t* off,
+                     int64_t R, int64_t K, int E, int world, int rank, int64_t cap, const void* const* rx_q_peers,
+                     const void* const* rx_s_peers, const void* const* rx_meta_peers, void* stream);
+/* All-gather by stores: writes `bytes` from src at dst_offset_bytes into every rank's buffer dst_peers[r] (own included).
+ * Follow with scmx_peer_barrier before reading the gathered buffer.  16-byte granularity. */
+int scmx_peer_put(const void* src, int64_t bytes, int64_t dst_offset_bytes, const void* const* dst_peers, int world, void* stream);
+/* All ranks signal each other and wait for everyone (bounded to 2 s, then status[0] = 20). */
+int scmx_peer_barrier(const void* const* flag_peers, int rank, int world, int32_t* epoch, int32_t* status, void* stream);
+/* From rx_meta: expert segments off2 / tstart2 [El+1], the regrouping gather list tok2 [r_cap + tm] (rows of rx_q in
+ * expert-major order), the return address (ret_rank, ret_row) of every regrouped row, and n_rows[0] = rows received. */
+int scmx_ep_plan(const int32_t* rx_meta, int world, int El, int64_t cap, int tm, int64_t r_cap, int32_t* off2,
+                 int32_t* tstart2, int32_t* tok2, int32_t* ret_rank, int32_t* ret_row, int32_t* n_rows, void* stream);
+/* Stores expert output row p (bf16 [D]) into rank ret_rank[p]'s y_back at row ret_row[p], for p < n_rows[0]. */
+int scmx_ep_return(const uint16_t* y, const int32_t* ret_rank, const int32_t* ret_row, const int32_t* n_rows, int64_t r_cap,
+                   int64_t D, int world, const void* const* y_back_peers, void* stream);
+/* gather_rows / act_quant over a device-side row count: rows >= n_rows[0] + pad are skipped, the pad rows after
+ * n_rows[0] are zero-filled. */
+int scmx_gather_rows_dyn(const int8_t* xq, const float* xs, const int32_t* tok, const int32_t* n_rows, int64_t r_cap, int pad,
+                         int64_t K, int8_t* dst_q, float* dst_s, void* stream);
+int scmx_act_quant_dyn(const uint16_t* x, const int32_t* n_rows, int64_t r_cap, int pad, int64_t K, int8_t* xq, float* xs,
+                       void* stream);
+int scmx_enable_peer_access(int peer_device);
+
 /* Weighted sequential-bf16 sum of the topk expert rows + residual (+ next RMSNorm + INT8 when quant != 0).
  * Replaces fused_olmoe.moe_combine (e2e/fused_olmoe.py:45-97).  y bf16 [R,K], pos int32 [M*topk], scores bf16
  * [M,topk], res bf16 [Mp,K] -> h bf16 [Mp,K], xq int8 [Mp,K], xs f32 [Mp]. */

@@ -50,6 +50,14 @@ SIGNATURES = {
                     c_int, c_vp, c_i64, c_vp, c_vp],
     "scmx_moe_mm_static": [c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, _FMT_P, c_int, c_vp, c_vp, c_int,
                            c_vp, c_vp],
+    "scmx_ep_dispatch": [c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_int, c_int, c_i64, c_vp, c_vp, c_vp, c_vp],
+    "scmx_peer_put": [c_vp, c_i64, c_i64, c_vp, c_int, c_vp],
+    "scmx_peer_barrier": [c_vp, c_int, c_int, c_vp, c_vp, c_vp],
+    "scmx_ep_plan": [c_vp, c_int, c_int, c_i64, c_int, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp],
+    "scmx_ep_return": [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_int, c_vp, c_vp],
+    "scmx_gather_rows_dyn": [c_vp, c_vp, c_vp, c_vp, c_i64, c_int, c_i64, c_vp, c_vp, c_vp],
+    "scmx_act_quant_dyn": [c_vp, c_vp, c_i64, c_int, c_i64, c_vp, c_vp, c_vp],
+    "scmx_enable_peer_access": [c_int],
     "scmx_moe_combine": [c_vp, c_vp, c_vp, c_vp, c_vp, c_float, c_i64, c_i64, c_i64, c_int, c_int, c_vp, c_vp, c_vp,
                          c_vp],
     "scmx_gemv": [c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, _FMT_P, c_int, c_vp, c_vp, c_int, c_int, c_int, c_vp,

@@ -70,6 +70,7 @@ class TensorParallelDense:
     def __init__(self, pkg, layers_local, M, hidden, group=None, eps=1e-6):
         """layers_local: this rank's row shards {group: (codes, bcodes, wscale, N_local, K)} (shard_packed)."""
         self.S, self.layers, self.M, self.hidden, self.eps, self.group = pkg.sc_kernels, layers_local, M, hidden, eps, group
+        self.pkg_lib = pkg._lib
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         dev = layers_local[0]["qkv"][0].device
@@ -143,3 +144,153 @@ class ExpertParallelMoe:
         y_back = exchange_rows(y_rx, recv_splits, send_splits, self.group)
         hout, _, _ = M_.moe_combine(y_back, pos, scores, h, blk.nw, blk.eps, Lr, quant=False)
         return hout
+
+
+# ---- expert parallelism over peer memory (no host round trip, capturable in a CUDA graph) -------------------------------
+def _lib_enable_peer(peer_device):
+    from . import _lib
+    _lib.call("scmx_enable_peer_access", int(peer_device))
+
+
+def share_tensor(t, group=None):
+    """Every rank passes its own CUDA tensor `t` (same shape and dtype everywhere); returns the list of all ranks' tensors
+    as seen from this process: entry `rank` is `t` itself, the others are CUDA-IPC mappings of the peers' memory."""
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    meta = (t.untyped_storage()._share_cuda_(), t.storage_offset(), tuple(t.shape), t.dtype)
+    metas = [None] * world
+    dist.all_gather_object(metas, meta, group=group)
+    views = []
+    for r, (m, off, shape, dtype) in enumerate(metas):
+        if r == rank:
+            views.append(t)
+            continue
+        # Open the peer's allocation with THIS rank's device current: the mapping then belongs to the context the kernels of
+        # this rank run in (a mapping opened under the exporter's device index is not addressable from this device).
+        me = torch.cuda.current_device()
+        dist_dev = m[0]
+        if dist_dev != me:
+            _lib_enable_peer(dist_dev)
+        st = torch.UntypedStorage._new_shared_cuda(me, *m[1:])
+        views.append(torch.empty(0, dtype=dtype, device=st.device).set_(st, off, shape))
+    return views
+
+
+class PeerExpertParallelMoe:
+    """ExpertParallelMoe whose dispatch and return are kernels storing into peer GPUs' memory (scmx_ep_*): the counts never
+    visit the host, so the whole half-block is one stream of launches and can be replayed from a CUDA graph."""
+
+    def __init__(self, pkg, block_local, n_experts, topk, tokens_local, group=None):
+        import ctypes
+        self.pkg, self.block, self.E, self.k, self.group = pkg, block_local, n_experts, topk, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        assert n_experts % self.world == 0 and block_local.E == n_experts // self.world and self.world <= 8
+        L_ = pkg._lib
+        dev = block_local.nw.device
+        G, D, El, TM = self.world, block_local.D, block_local.E, pkg.sc_moe.TM
+        self.Lr, self.cap = tokens_local, tokens_local * topk
+        self.r_cap = G * self.cap
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.rx_q = torch.empty((G, self.cap, D), dtype=torch.int8, device=dev)
+        self.rx_s = torch.empty((G, self.cap), dtype=torch.float32, device=dev)
+        self.rx_meta = torch.zeros((G, El + 1), **i32)
+        self.y_back = torch.empty((self.cap, D), dtype=torch.bfloat16, device=dev)
+        self.flags = torch.zeros(G, **i32)
+        self.epoch = torch.zeros(1, **i32)
+        torch.cuda.synchronize()
+        self._views = {}
+        self._peers = {}
+        for name in ("rx_q", "rx_s", "rx_meta", "y_back", "flags"):
+            views = share_tensor(getattr(self, name), group)
+            self._views[name] = views                      # keep the mappings alive
+            self._peers[name] = (ctypes.c_void_p * 8)(*[v.data_ptr() for v in views], *([None] * (8 - G)))
+        dist.barrier(group)
+        self.off2 = torch.empty(El + 1, **i32)
+        self.ts2 = torch.empty(El + 1, **i32)
+        self.tok2 = torch.empty(self.r_cap + TM, **i32)
+        self.ret_rank = torch.empty(self.r_cap, **i32)
+        self.ret_row = torch.empty(self.r_cap, **i32)
+        self.n_rows = torch.zeros(1, **i32)
+
+    def _barrier(self):
+        L_ = self.pkg._lib
+        L_.call("scmx_peer_barrier", self._peers["flags"], self.rank, self.world, L_.ptr(self.epoch), L_.ptr(L_.status_buffer()),
+                L_.stream())
+
+    def step(self, h, logits):
+        """h bf16 [Lr, D] local tokens, logits f32 [Lr, E] -> new residual rows bf16 [Lr, D]."""
+        S, M_, L_ = self.pkg.sc_kernels, self.pkg.sc_moe, self.pkg._lib
+        blk, G, k = self.block, self.world, self.k
+        Lr, D = h.shape
+        assert Lr == self.Lr
+        R, TM, F = Lr * k, M_.TM, blk.F
+        xq, xs = S.rmsnorm_quant(h, blk.nw, blk.eps, Lr)
+        inds, scores = M_.router_topk(logits, k)
+        pos, tok, es, off, _, _ = M_.route_sort(inds, self.E, TM)
+        L_.call("scmx_ep_dispatch", L_.ptr(xq), L_.ptr(xs), L_.ptr(tok), L_.ptr(es), L_.ptr(off), R, D, self.E, G, self.rank, self.cap,
+                self._peers["rx_q"], self._peers["rx_s"], self._peers["rx_meta"], L_.stream())
+        self._barrier()
+        L_.call("scmx_ep_plan", L_.ptr(self.rx_meta), G, blk.E, self.cap, TM, self.r_cap, L_.ptr(self.off2), L_.ptr(self.ts2),
+                L_.ptr(self.tok2), L_.ptr(self.ret_rank), L_.ptr(self.ret_row), L_.ptr(self.n_rows), L_.stream())
+        xq_r = torch.empty((self.r_cap + TM, D), dtype=torch.int8, device=h.device)
+        xs_r = torch.empty(self.r_cap + TM, dtype=torch.float32, device=h.device)
+        L_.call("scmx_gather_rows_dyn", L_.ptr(self.rx_q), L_.ptr(self.rx_s), L_.ptr(self.tok2), L_.ptr(self.n_rows), self.r_cap, TM, D,
+                L_.ptr(xq_r), L_.ptr(xs_r), L_.stream())
+        mt = -(-self.r_cap // TM) + blk.E
+        act = M_.moe_mm(xq_r, self.r_cap, *blk.gu, self.off2, self.ts2, mt, 2 * F, 3, xs_r)
+        xq2 = torch.empty((self.r_cap + TM, F), dtype=torch.int8, device=h.device)
+        xs2 = torch.empty(self.r_cap + TM, dtype=torch.float32, device=h.device)
+        L_.call("scmx_act_quant_dyn", L_.ptr(act), L_.ptr(self.n_rows), self.r_cap, TM, F, L_.ptr(xq2), L_.ptr(xs2), L_.stream())
+        yd = M_.moe_mm(xq2, self.r_cap, *blk.dn, self.off2, self.ts2, mt, D, 1, xs2)
+        L_.call("scmx_ep_return", L_.ptr(yd), L_.ptr(self.ret_rank), L_.ptr(self.ret_row), L_.ptr(self.n_rows), self.r_cap, D, G,
+                self._peers["y_back"], L_.stream())
+        self._barrier()
+        hout, _, _ = M_.moe_combine(self.y_back, pos, scores, h, blk.nw, blk.eps, Lr, quant=False)
+        return hout
+
+
+class PeerTensorParallelDense(TensorParallelDense):
+    """TensorParallelDense whose all-gathers are kernels storing each rank's column shard into every GPU's segment buffer
+    (scmx_peer_put + scmx_peer_barrier) instead of library collectives: the whole stack is one stream of launches and can be
+    replayed from a CUDA graph.  Two residual buffers alternate so that a gather never overwrites rows a peer still reads."""
+
+    def __init__(self, pkg, layers_local, M, hidden, ffn, group=None, eps=1e-6):
+        import ctypes
+        super().__init__(pkg, layers_local, M, hidden, group, eps)
+        G = self.world
+        dev = self.nw.device
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        self.bufs = dict(o=torch.empty((G, M, hidden // G), **bf), h0=torch.empty((G, M, hidden // G), **bf),
+                         h1=torch.empty((G, M, hidden // G), **bf), act=torch.empty((G, M, ffn // G), **bf),
+                         flags=torch.zeros(G, dtype=torch.int32, device=dev))
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+        torch.cuda.synchronize()
+        self._views, self._peers = {}, {}
+        for name, t in self.bufs.items():
+            views = share_tensor(t, group)
+            self._views[name] = views
+            self._peers[name] = (ctypes.c_void_p * 8)(*[v.data_ptr() for v in views], *([None] * (8 - G)))
+        dist.barrier(group)
+
+    def gather_to(self, local, name):
+        """Column shard [M, w] -> the shared segment buffer `name` [G, M, w], complete on every rank when this returns
+        (in stream order)."""
+        L_ = self.pkg_lib
+        nbytes = local.numel() * local.element_size()
+        L_.call("scmx_peer_put", L_.ptr(local), nbytes, self.rank * nbytes, self._peers[name], self.world, L_.stream())
+        L_.call("scmx_peer_barrier", self._peers["flags"], self.rank, self.world, L_.ptr(self.epoch), L_.ptr(L_.status_buffer()),
+                L_.stream())
+        return self.bufs[name]
+
+    def step(self, h_seg, o_local):
+        S, M, r = self.S, self.M, self.rank
+        cur = h_seg
+        for lw in self.layers:
+            xq, xs = S.rmsnorm_quant_seg(cur, self.nw, self.eps, M)
+            self._gemm(lw, "qkv", xq, xs, 1)
+            oq, os_ = S.act_quant_seg(self.gather_to(o_local, "o"), M)
+            nxt = self.gather_to(self._gemm(lw, "o", oq, os_, 2, res=cur[r]), "h0")
+            xq, xs = S.rmsnorm_quant_seg(nxt, self.nw, self.eps, M)
+            act = self._gemm(lw, "gu", xq, xs, 3)
+            aq, as_ = S.act_quant_seg(self.gather_to(act, "act"), M)
+            cur = self.gather_to(self._gemm(lw, "down", aq, as_, 2, res=nxt[r]), "h1")
+        return cur

@@ -30,6 +30,16 @@ def test_segmented_row_kernels(scmx, oracle, G, M, w):
 
 
 def _worker(rank, world, port, q):
+    """Runs _worker_body and reports an exception instead of leaving the peer blocked in a collective."""
+    try:
+        _worker_body(rank, world, port, q)
+    except BaseException as e:   # noqa: BLE001
+        import traceback
+        q.put((rank, "".join(traceback.format_exception(type(e), e, e.__traceback__))[-1500:]))
+        os._exit(1)
+
+
+def _worker_body(rank, world, port, q):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
@@ -63,6 +73,19 @@ def _worker(rank, world, port, q):
         tp = P.TensorParallelDense(pkg, local, M, hidden)
         out = tp.step(h.view(M, world, w).permute(1, 0, 2).contiguous(), o[:, rank * w:(rank + 1) * w].contiguous())
         ok["tp"] = bool(torch.equal(out.permute(1, 0, 2).reshape(M, hidden), ref)) and bool(torch.equal(ref, ref2))
+        # the same stack with store-based all-gathers over peer memory, eagerly and replayed from a CUDA graph
+        ptp = P.PeerTensorParallelDense(pkg, local, M, hidden, Fd)
+        hs, ol = h.view(M, world, w).permute(1, 0, 2).contiguous(), o[:, rank * w:(rank + 1) * w].contiguous()
+        out2 = ptp.step(hs, ol).clone()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out3 = ptp.step(hs, ol)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        ok["peer_tp"] = bool(torch.equal(out2.permute(1, 0, 2).reshape(M, hidden), ref)) and \
+            bool(torch.equal(out3.permute(1, 0, 2).reshape(M, hidden), ref))
         # ---- expert-parallel MoE block vs the single-GPU block
         E, k, D, Fm, L = 8, 2, 512, 256, 512
         perm = torch.from_numpy(S.interleave_gate_up(Fm)).cuda()
@@ -89,6 +112,20 @@ def _worker(rank, world, port, q):
         ep = P.ExpertParallelMoe(pkg, blk_loc, E, k)
         outm = ep.step(hm[rank * Lr:(rank + 1) * Lr].contiguous(), lg[rank * Lr:(rank + 1) * Lr].contiguous())
         ok["ep"] = bool(torch.equal(outm, refm[rank * Lr:(rank + 1) * Lr]))
+        # ---- the same block with kernel-side dispatch / return over peer memory, eagerly and replayed from a CUDA graph
+        pep = P.PeerExpertParallelMoe(pkg, blk_loc, E, k, Lr)
+        hl, ll = hm[rank * Lr:(rank + 1) * Lr].contiguous(), lg[rank * Lr:(rank + 1) * Lr].contiguous()
+        o1 = pep.step(hl, ll)
+        o2 = pep.step(hl, ll)
+        torch.cuda.synchronize()
+        ok["peer_ep"] = bool(torch.equal(o1, refm[rank * Lr:(rank + 1) * Lr])) and bool(torch.equal(o2, o1))
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            o3 = pep.step(hl, ll)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        ok["peer_ep_graph"] = bool(torch.equal(o3, refm[rank * Lr:(rank + 1) * Lr]))
         blk2 = pkg.fused_moe.MoeBlock(blk_full.gu, blk_full.dn, E, k, D, Fm, two_pass=True)
         ok["two_pass"] = bool(torch.equal(blk2.step(hm, lg), refm))
         torch.cuda.synchronize()
@@ -106,10 +143,16 @@ def test_tensor_and_expert_parallel_match_single_gpu():
     procs = [ctx.Process(target=_worker, args=(r, 2, 29651, q)) for r in range(2)]
     for p in procs:
         p.start()
-    res = dict(q.get(timeout=300) for _ in procs)
+    first = q.get(timeout=150)
+    res = dict([first])
+    if isinstance(first[1], dict):
+        res.update([q.get(timeout=60)])
     for p in procs:
-        p.join(60)
-    assert res == {0: dict(tp=True, ep=True, two_pass=True), 1: dict(tp=True, ep=True, two_pass=True)}
+        p.join(20)
+        if p.is_alive():
+            p.kill()
+    want = dict(tp=True, peer_tp=True, ep=True, peer_ep=True, peer_ep_graph=True, two_pass=True)
+    assert res == {0: want, 1: want}
 
 
 def test_dense_stack_overlap_equals_serial(scmx):
