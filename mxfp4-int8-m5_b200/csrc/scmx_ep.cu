@@ -100,20 +100,31 @@ __global__ void __launch_bounds__(1024) ep_plan_kernel(const int32_t* __restrict
     for (int i = tid; i < world * El; i += blockDim.x) cnt[i / El][i % El] = rx_meta[(i / El) * (El + 1) + (i % El)];
     if (tid < world) base[tid] = rx_meta[tid * (El + 1) + El];
     __syncthreads();
-    if (tid == 0) {
+    if (tid < 32) {
+        // exclusive scans over the local experts by one warp, 32 experts per round
         int o = 0, t = 0;
-        for (int le = 0; le < El; ++le) {
+        for (int b0 = 0; b0 < El; b0 += 32) {
+            const int le = b0 + tid;
             int c = 0;
-            for (int s = 0; s < world; ++s) c += cnt[s][le];
-            s_off[le] = o; off2[le] = o; tstart2[le] = t;
-            o += c; t += (c + tm - 1) / tm;
+            if (le < El)
+                for (int s = 0; s < world; ++s) c += cnt[s][le];
+            const int ti = (c + tm - 1) / tm;
+            int so = c, st = ti;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int a = __shfl_up_sync(0xffffffffu, so, d), b = __shfl_up_sync(0xffffffffu, st, d);
+                if (tid >= d) { so += a; st += b; }
+            }
+            if (le < El) { s_off[le] = o + so - c; off2[le] = o + so - c; tstart2[le] = t + st - ti; }
+            o += __shfl_sync(0xffffffffu, so, 31);
+            t += __shfl_sync(0xffffffffu, st, 31);
         }
-        s_off[El] = o; off2[El] = o; tstart2[El] = t;
-        n_rows[0] = o;
+        if (tid == 0) { s_off[El] = o; off2[El] = o; tstart2[El] = t; n_rows[0] = o; }
     }
-    if (tid < world) {
-        int a = tid * cap;
-        for (int le = 0; le < El; ++le) { src0[tid][le] = a; a += cnt[tid][le]; }
+    if (tid >= 32 && tid < 32 + world) {
+        const int sidx = tid - 32;
+        int a = sidx * cap;
+        for (int le = 0; le < El; ++le) { src0[sidx][le] = a; a += cnt[sidx][le]; }
     }
     __syncthreads();
     for (int le = tid; le < El; le += blockDim.x) {

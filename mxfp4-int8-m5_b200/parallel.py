@@ -204,6 +204,14 @@ class PeerExpertParallelMoe:
             self._views[name] = views                      # keep the mappings alive
             self._peers[name] = (ctypes.c_void_p * 8)(*[v.data_ptr() for v in views], *([None] * (8 - G)))
         dist.barrier(group)
+        # With few experts per rank the whole rank's expert weights decode to a modest INT8 buffer: the decode is started on a
+        # side stream at the top of every step and overlaps routing, dispatch and the barrier (weights do not depend on them).
+        F = block_local.F
+        self.early_decode = El * 3 * F * D <= (96 << 20)
+        if self.early_decode:
+            self.side = torch.cuda.Stream(device=dev)
+            self.gu8 = torch.empty((El * 2 * F, D), dtype=torch.int8, device=dev)
+            self.dn8 = torch.empty((El * D, F), dtype=torch.int8, device=dev)
         self.off2 = torch.empty(El + 1, **i32)
         self.ts2 = torch.empty(El + 1, **i32)
         self.tok2 = torch.empty(self.r_cap + TM, **i32)
@@ -223,6 +231,14 @@ class PeerExpertParallelMoe:
         Lr, D = h.shape
         assert Lr == self.Lr
         R, TM, F = Lr * k, M_.TM, blk.F
+        if self.early_decode:
+            main = torch.cuda.current_stream()
+            self.side.wait_stream(main)
+            with torch.cuda.stream(self.side):
+                S.unpack_i8(blk.gu[0].reshape(-1), blk.gu[1].reshape(blk.E * 2 * F, -1), blk.E * 2 * F, D, out=self.gu8)
+                S.unpack_i8(blk.dn[0].reshape(-1), blk.dn[1].reshape(blk.E * D, -1), blk.E * D, F, out=self.dn8)
+                decoded = torch.cuda.Event()
+                decoded.record(self.side)
         xq, xs = S.rmsnorm_quant(h, blk.nw, blk.eps, Lr)
         inds, scores = M_.router_topk(logits, k)
         pos, tok, es, off, _, _ = M_.route_sort(inds, self.E, TM)
@@ -236,11 +252,18 @@ class PeerExpertParallelMoe:
         L_.call("scmx_gather_rows_dyn", L_.ptr(self.rx_q), L_.ptr(self.rx_s), L_.ptr(self.tok2), L_.ptr(self.n_rows), self.r_cap, TM, D,
                 L_.ptr(xq_r), L_.ptr(xs_r), L_.stream())
         mt = -(-self.r_cap // TM) + blk.E
-        act = M_.moe_mm(xq_r, self.r_cap, *blk.gu, self.off2, self.ts2, mt, 2 * F, 3, xs_r)
+        if self.early_decode:
+            main.wait_event(decoded)
+            act = M_.moe_mm_i8(xq_r, self.r_cap, self.gu8, blk.gu[2], self.off2, self.ts2, mt, 2 * F, 3, xs_r)
+        else:
+            act = M_.moe_mm(xq_r, self.r_cap, *blk.gu, self.off2, self.ts2, mt, 2 * F, 3, xs_r)
         xq2 = torch.empty((self.r_cap + TM, F), dtype=torch.int8, device=h.device)
         xs2 = torch.empty(self.r_cap + TM, dtype=torch.float32, device=h.device)
         L_.call("scmx_act_quant_dyn", L_.ptr(act), L_.ptr(self.n_rows), self.r_cap, TM, F, L_.ptr(xq2), L_.ptr(xs2), L_.stream())
-        yd = M_.moe_mm(xq2, self.r_cap, *blk.dn, self.off2, self.ts2, mt, D, 1, xs2)
+        if self.early_decode:
+            yd = M_.moe_mm_i8(xq2, self.r_cap, self.dn8, blk.dn[2], self.off2, self.ts2, mt, D, 1, xs2)
+        else:
+            yd = M_.moe_mm(xq2, self.r_cap, *blk.dn, self.off2, self.ts2, mt, D, 1, xs2)
         L_.call("scmx_ep_return", L_.ptr(yd), L_.ptr(self.ret_rank), L_.ptr(self.ret_row), L_.ptr(self.n_rows), self.r_cap, D, G,
                 self._peers["y_back"], L_.stream())
         self._barrier()
