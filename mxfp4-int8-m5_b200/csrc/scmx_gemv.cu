@@ -299,6 +299,15 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv_stream_kernel(const Stream
 #pragma unroll
             for (int j = 0; j < 8; ++j) { xr[sidx][j] = xv[j]; xnr[sidx][j] = neg4(xv[j]); }
         }
+        // block-code byte offset and bit shift of the lane's (up to two cached) K offsets: the same for every row and tile
+        uint32_t bc_off[2], bc_sh[2];
+#pragma unroll
+        for (int sidx = 0; sidx < 2; ++sidx) {
+            const int blk = block_of(a.f, kbeg + lane * 32 + sidx * 1024);
+            bc_off[sidx] = (uint32_t)(blk >> a.f.pb_shift);
+            bc_sh[sidx] = (uint32_t)((blk & a.f.pb_mask) << a.f.bc_shift);
+        }
+        const uint32_t row_off = (uint32_t)(4 * rgi) * (uint32_t)row_bytes, rb_off = SG_STAGE_BYTES + (uint32_t)(4 * rgi) * (uint32_t)bc_row;
         int stage = 0, it = 0;
         uint32_t phase = 0;
         for (int t = blockIdx.x; t < sa.n_tiles; t += gridDim.x) {
@@ -327,15 +336,20 @@ __global__ void __launch_bounds__(SG_THREADS, 1) gemv_stream_kernel(const Stream
                     }
 #pragma unroll
                     for (int r = 0; r < 4; ++r) {
-                        const uint32_t row_s = st_s + (uint32_t)(4 * rgi + r) * (uint32_t)row_bytes;
+                        const uint32_t row_s = st_s + row_off + (uint32_t)r * (uint32_t)row_bytes;
                         const uint4 wv = lds128(row_s + (uint32_t)(k0 >> 1));
                         const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
                         if (sa.mode == 1) { tot[r] += (int)(ww[0] ^ ww[1] ^ ww[2] ^ ww[3] ^ x[r]); continue; }
-                        const uint32_t rb_s = st_s + SG_STAGE_BYTES + (uint32_t)(4 * rgi + r) * (uint32_t)bc_row;
+                        const uint32_t rb_s = st_s + rb_off + (uint32_t)r * (uint32_t)bc_row;
                         const uint8_t* rb = st + SG_STAGE_BYTES + (size_t)(4 * rgi + r) * bc_row;
                         if (B32) {
-                            const int blk = block_of(a.f, k0);
-                            const uint32_t code = (lds8(rb_s + (uint32_t)(blk >> a.f.pb_shift)) >> ((blk & a.f.pb_mask) << a.f.bc_shift)) & a.f.bc_mask;
+                            uint32_t code;
+                            if (xcache) {
+                                code = (lds8(rb_s + bc_off[sidx & 1]) >> bc_sh[sidx & 1]) & a.f.bc_mask;
+                            } else {
+                                const int blk = block_of(a.f, k0);
+                                code = (lds8(rb_s + (uint32_t)(blk >> a.f.pb_shift)) >> ((blk & a.f.pb_mask) << a.f.bc_shift)) & a.f.bc_mask;
+                            }
                             int bs = 0;
 #pragma unroll
                             for (int j = 0; j < 4; ++j) bs = word_dot(ww[j], x[2 * j], xn[2 * j], x[2 * j + 1], xn[2 * j + 1], mlo, mhi, bs);
