@@ -92,6 +92,20 @@ int scmx_swiglu_quant(const int32_t* acc, const float* xscale, const float* wsca
  * gate-value check the reference runs in e2e/test_sc_kernels.py:80-93. */
 int scmx_swiglu(const uint16_t* g, const uint16_t* u, int64_t n, uint16_t* out, void* stream);
 
+/* q/k/v epilogue between the fused q|k|v projection and attention.  src is the bf16 GEMM output y [L, (hq+2hk)d]
+ * (src_is_acc = 0) or its int32 accumulators with xscale [L] and wscale [(hq+2hk)d] (src_is_acc != 0).  q and k get
+ * T(w * T(x * inv)): per head over d values with qn / kn bf16 [d] (full = 0), or over the whole hq*d-wide q and hk*d-wide
+ * k with qn bf16 [hq*d], kn bf16 [hk*d] (full != 0); v is copied.  Outputs are head-major: q[(h*q_head_stride + row)*d],
+ * k and v at [(h*kv_head_stride + kv_row0 + row)*d], so k / v can be the rows of a cache of kv_head_stride positions.
+ * inv_freq f32 [d/2] non-null: rotary embedding (half-split pairs i, i + d/2) at position pos0 + row applied to the
+ * normalized q and k.  pos_dev non-null: one device int32 added to pos0 and kv_row0 (rows beyond the cache are dropped).
+ * Replaces qkv_epilogue_headnorm, qkv_headnorm_y, qkv_fullnorm_y (e2e/sc_kernels.py:333-423,597-637); the rotary step
+ * and cache append replace the MLX calls of e2e/fused_qwen3.py:197-203.  d a power of two, row <= 48 KB as float. */
+int scmx_qkv_norm(const void* src, int src_is_acc, const float* xscale, const float* wscale, const uint16_t* qn,
+                  const uint16_t* kn, float eps, int64_t L, int hq, int hk, int d, int full, const float* inv_freq,
+                  int64_t pos0, const int32_t* pos_dev, uint16_t* q, int64_t q_head_stride, uint16_t* k, uint16_t* v,
+                  int64_t kv_head_stride, int64_t kv_row0, void* stream);
+
 /* ---- dense prefill GEMM (tcgen05 kind::i8) -------------------------------------------------------------------- */
 
 /* out = epilogue(xq [M,K] . wq [N,K]^T).  epi 0: int32 [M,N] (mm_i8_i32, e2e/sc_kernels.py:53-71,486-495);

@@ -156,6 +156,13 @@ __device__ __forceinline__ double block_sum(double v, double* red) {
     return red[32];
 }
 
+// inv = 1 / sqrt(float(sum x^2) / K + eps).  Callers accumulate the sum of squares in float64 (exact for bf16 inputs of
+// ordinary dynamic range, hence independent of the reduction order); the reciprocal square root is taken in float64.
+__device__ __forceinline__ float rms_inverse(double ss, int K, float eps) {
+    const float m = __fadd_rn(__fdiv_rn((float)ss, (float)K), eps);
+    return (float)(1.0 / sqrt((double)m));
+}
+
 // s = amax / 127, qi = s > 0 ? 1 / s : 0 in IEEE float32 (e2e/sc_kernels.py:221-222).
 __device__ __forceinline__ void quant_scale(float amax, float& s, float& qi) {
     s = __fdiv_rn(amax, 127.0f);

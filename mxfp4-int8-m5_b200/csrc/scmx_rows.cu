@@ -93,10 +93,6 @@ __global__ void __launch_bounds__(256) act_quant_kernel(const uint16_t* __restri
 // ---- RMSNorm + quant (optionally writing the normalized bf16 row) -----------------------------------------------
 // inv = 1 / sqrt(float(sum x^2) / K + eps): the sum of squares is accumulated in float64 (exact for bf16 inputs of
 // ordinary dynamic range, hence independent of the reduction order), the reciprocal square root in float64.
-__device__ __forceinline__ float rms_inverse(double ss, int K, float eps) {
-    const float m = __fadd_rn(__fdiv_rn((float)ss, (float)K), eps);
-    return (float)(1.0 / sqrt((double)m));
-}
 
 __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(const uint16_t* __restrict__ x,
                                                             const uint16_t* __restrict__ nw, float eps, int64_t M, int K,

@@ -1,0 +1,161 @@
+"""Fused SC-MXFP4 W4A8 prefill for OLMoE-style mixture-of-experts decoders: the torch counterpart of the reference's
+FusedOlmoe (e2e/fused_olmoe.py:132-290) over libscmx.  Per block:
+
+    y = mm_epi(xq, unpack(Wq|Wk|Wv), EPI 1);  q, k, v = qkv_fullnorm_y(y)  (+ rotary embedding, KV-cache append)
+    o = sdpa(q, k, v);  h = mm_epi(act_quant(o), unpack(Wo), EPI 2, res=h)
+    xq, xs, xn = rmsnorm_quant_n(h);  inds, scores = router(xn)            softmax / top-k on the device
+    route_sort -> gather_rows -> moe_mm(gate|up, SwiGLU) -> act_quant -> moe_mm(down) -> moe_combine(+res, next norm + INT8)
+"""
+import os
+
+import numpy as np
+import torch
+
+from . import host_model as HM
+from . import packed_io
+from . import sc_format as F
+from . import sc_kernels as S
+from . import sc_moe as M_
+from .w4a8 import PackedWeight
+
+ATTN = ["self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj"]
+EXPERTS = ["gate_proj", "up_proj", "down_proj"]
+
+
+def pack_olmoe(model, cache_path=None, fmt=F.DEFAULT):
+    """SC-MXFP4 of every attention linear and expert matrix; keys layers.{i}.{path} and layers.{i}.experts.{name}.{e}
+    (e2e/fused_olmoe.py:102-129).  Returns {key: (codes, bcodes, wscale)} as NumPy."""
+    if cache_path and os.path.exists(cache_path):
+        return packed_io.load_packed(cache_path, fmt)
+    out = {}
+    for i, layer in enumerate(model.model.layers):
+        for path in ATTN:
+            parent, name = path.split(".")
+            w = getattr(getattr(layer, parent), name).weight.detach().to("cpu", torch.float64).numpy()
+            out[f"layers.{i}.{path}"] = F.quantize(w, fmt)[:3]
+        sw = layer.mlp.switch_mlp
+        for name in EXPERTS:
+            wt = getattr(sw, name).weight.detach().to("cpu", torch.float64).numpy()
+            for e in range(wt.shape[0]):
+                out[f"layers.{i}.experts.{name}.{e}"] = F.quantize(wt[e], fmt)[:3]
+    if cache_path:
+        packed_io.save_packed(cache_path, out)
+    return out
+
+
+class FusedOlmoe:
+    def __init__(self, model, flat, tile_gu=None, tile_d=None, bk=None, two_pass="auto", sort="count", compiled=True):
+        """model: host_model.CausalLM (num_experts > 0) on the GPU; flat: pack_olmoe's dict.  two_pass=True decodes all
+        experts to INT8 once per call and runs the grouped GEMM on that (moe_mm_i8); "auto": once the average expert has
+        >= 256 rows (e2e/fused_olmoe.py:135-141).  The tile arguments are Metal tuning hints: accepted and ignored."""
+        assert sort == "count"
+        self.model, self.args = model, model.args
+        a = self.args
+        assert not a.norm_topk_prob
+        self.eps, self.two_pass = a.rms_norm_eps, two_pass
+        dev = model.model.embed_tokens.weight.device
+        E, Fi = a.num_experts, a.intermediate_size
+        perm = S.interleave_gate_up(Fi)
+        self.layers = []
+        for i, layer in enumerate(model.model.layers):
+            parts = lambda p: flat[f"layers.{i}.{p}"]  # noqa: E731
+            qkv = PackedWeight([parts(p) for p in ATTN[:3]], device=dev)
+            o = PackedWeight([parts(ATTN[3])], device=dev)
+            gu_c, gu_b, gu_s, d_c, d_b, d_s = [], [], [], [], [], []
+            for e in range(E):
+                g, u, d = (parts(f"experts.{n}.{e}") for n in EXPERTS)
+                c = np.concatenate([np.asarray(g[0]).reshape(Fi, -1), np.asarray(u[0]).reshape(Fi, -1)])[perm]
+                gu_c.append(c.reshape(-1))
+                gu_b.append(np.concatenate([g[1], u[1]])[perm])
+                gu_s.append(np.concatenate([g[2], u[2]])[perm])
+                d_c.append(np.asarray(d[0]).reshape(-1)), d_b.append(d[1]), d_s.append(d[2])
+            st = lambda xs: F.to_device(np.stack(xs[0]), np.stack(xs[1]), np.stack(xs[2]), dev)  # noqa: E731
+            ex = dict(gu=st((gu_c, gu_b, gu_s)), down=st((d_c, d_b, d_s)))
+            self.layers.append((layer, dict(qkv=qkv, o=o), ex))
+        self.perm_gu = perm
+        for layer in model.model.layers:                      # drop the bf16 weights that the packed ones replace
+            for path in ATTN:
+                setattr(layer.self_attn, path.split(".")[1], None)
+            layer.mlp.switch_mlp = None
+        self.inv_freq = S.rope_inv_freq(a.head_dim, a.rope_theta, dev)
+        self.record, self.record_layers = None, ()
+        self.sdpa = HM.sdpa                                   # (q, k, v, scale, causal) -> [L, H * d]; replaceable
+
+    def weight_bytes(self):
+        n = 0
+        for _, ws, ex in self.layers:
+            n += ws["qkv"].nbytes() + ws["o"].nbytes()
+            n += sum(t.numel() * t.element_size() for t in ex["gu"] + ex["down"])
+        return n
+
+    def route(self, layer, xn, M):
+        """Router of the block on the normalized bf16 rows: softmax over experts then top-k (e2e/fused_olmoe.py:186-195)."""
+        logits = torch.nn.functional.linear(xn[:M], layer.mlp.gate.weight)
+        return M_.router_topk(logits.float(), self.args.num_experts_per_tok)
+
+    def experts(self, ex, xq, xs, inds, L):
+        """INT8 rows + routing -> (sorted expert outputs yd bf16 [R, D], pos)."""
+        a = self.args
+        k, E, F2, D = a.num_experts_per_tok, a.num_experts, 2 * a.intermediate_size, a.hidden_size
+        R = L * k
+        two_pass = self.two_pass if self.two_pass != "auto" else R // E >= 256
+        pos, tok_p, e_sorted, off, tstart, maxt = M_.route_sort(inds, E, M_.TM)
+        xq_s, xs_s = M_.gather_rows(xq, xs, tok_p, R)
+        (cg, bg, sg), (cd, bd, sd) = ex["gu"], ex["down"]
+        if two_pass:
+            act = M_.moe_mm_i8(xq_s, R, M_.unpack_experts(cg, bg, F2, D), sg, off, tstart, maxt, F2, 3, xs_s)
+        else:
+            act = M_.moe_mm(xq_s, R, cg, bg, sg, off, tstart, maxt, F2, 3, xs_s)
+        xq2, xs2 = S.act_quant(act, R + M_.TM)
+        if two_pass:
+            yd = M_.moe_mm_i8(xq2, R, M_.unpack_experts(cd, bd, D, F2 // 2), sd, off, tstart, maxt, D, 1, xs2)
+        else:
+            yd = M_.moe_mm(xq2, R, cd, bd, sd, off, tstart, maxt, D, 1, xs2)
+        return yd, pos, (xq_s, xs_s, act, xq2, xs2, e_sorted)
+
+    @torch.no_grad()
+    def hidden(self, ids, cache):
+        a = self.args
+        H, d, D = a.num_attention_heads, a.head_dim, a.hidden_size
+        h = self.model.model.embed_tokens(ids)[0]
+        L = h.shape[0]
+        Mp = S.pad_rows(L)
+        if Mp != L:
+            h = torch.nn.functional.pad(h, (0, 0, 0, Mp - L))
+        h = h.contiguous()
+        nl = len(self.layers)
+        xq, xs = S.rmsnorm_quant(h, self.layers[0][0].input_layernorm.weight, self.eps, Mp)
+        for i, (layer, ws, ex) in enumerate(self.layers):
+            at, c = layer.self_attn, cache[i]
+            wq, wo = ws["qkv"], ws["o"]
+            y = S.mm_epi(xq, wq.unpack(), xs, wq.wscale, 1)
+            q, kk, v = S.qkv_fullnorm_y(y, at.q_norm.weight, at.k_norm.weight, self.eps, L, H, d,
+                                        rope=(self.inv_freq, c.offset), cache=c)
+            c.offset += L
+            o = self.sdpa(q, kk, v, at.scale, True)
+            xq, xs = S.act_quant(o, Mp)
+            h = S.mm_epi(xq, wo.unpack(), xs, wo.wscale, 2, res=h)
+            xq, xs, xn = S.rmsnorm_quant_n(h, layer.post_attention_layernorm.weight, self.eps)
+            inds, scores = self.route(layer, xn, L)
+            yd, pos, rec = self.experts(ex, xq, xs, inds, L)
+            nn = self.layers[i + 1][0].input_layernorm.weight if i + 1 < nl else self.model.model.norm.weight
+            h_in = h
+            h, xq, xs = M_.moe_combine(yd, pos, scores, h, nn, self.eps, L)
+            if self.record is not None and i in self.record_layers:
+                self.record[(i, "experts")] = (h_in, xn, inds, scores, yd, pos, *rec)
+        xn = S.rmsnorm_quant_n(h, self.model.model.norm.weight, self.eps, Mp)[2]
+        return xn[:L][None]
+
+    def make_cache(self, capacity=4096):
+        return HM.make_prompt_cache(self.model, capacity)
+
+    def logits(self, h):
+        return self.model.head(h)
+
+    def __call__(self, ids, cache=None):
+        cache = cache if cache is not None else self.make_cache(max(ids.shape[1], 1))
+        return self.logits(self.hidden(ids, cache))
+
+
+def load_fused_olmoe(model, cache_path=None, **kw):
+    return FusedOlmoe(model, pack_olmoe(model, cache_path), **kw)

@@ -174,6 +174,52 @@ def sc_swiglu(g, u):
     return out
 
 
+def rope_inv_freq(d, base, device="cuda"):
+    """f32 [d/2]: base^(-2i/d), the frequencies of a half-split (non-interleaved) rotary embedding."""
+    i = torch.arange(0, d, 2, dtype=torch.float64)
+    return (1.0 / (float(base) ** (i / d))).to(torch.float32).to(device)
+
+
+def _qkv_norm(src, xscale, wscale, qn, kn, eps, L, hq, hk, d, full, rope, cache, pos_dev=None):
+    _lib.require_cuda(src, xscale, wscale, qn, kn)
+    ntot = (hq + 2 * hk) * d
+    assert src.shape[1] == ntot and src.shape[0] >= L and src.is_contiguous()
+    is_acc = src.dtype == torch.int32
+    assert is_acc or src.dtype == torch.bfloat16
+    inv_freq, pos0 = rope if rope is not None else (None, 0)
+    q = torch.empty((hq, L, d), dtype=torch.bfloat16, device=src.device)
+    if cache is None:
+        k = torch.empty((hk, L, d), dtype=torch.bfloat16, device=src.device)
+        v = torch.empty_like(k)
+        kbuf, vbuf, cap, row0 = k, v, L, 0
+    else:
+        kbuf, vbuf, cap, row0 = cache.k, cache.v, cache.k.shape[1], cache.offset
+        assert kbuf.shape == (hk, cap, d) and kbuf.is_contiguous() and vbuf.is_contiguous()
+        k, v = kbuf[:, :row0 + L], vbuf[:, :row0 + L]
+    _lib.call("scmx_qkv_norm", _lib.ptr(src), int(is_acc), _lib.ptr(xscale), _lib.ptr(wscale), _lib.ptr(qn), _lib.ptr(kn),
+              _eps(eps), L, hq, hk, d, int(full), _lib.ptr(inv_freq), int(pos0), _lib.ptr(pos_dev), _lib.ptr(q), L,
+              _lib.ptr(kbuf), _lib.ptr(vbuf), cap, row0, _lib.stream())
+    return q, k, v
+
+
+def qkv_epilogue_headnorm(acc, xscale, wscale, qn, kn, eps, L, hq, hk, d, dtype=torch.bfloat16, deps=(), rope=None,
+                          cache=None):
+    """acc int32 [Mp, (hq + 2 hk) d] -> q [hq, L, d], k [hk, L, d], v [hk, L, d] with per-head RMSNorm of q and k.
+    rope=(inv_freq, pos0): rotary embedding of q and k at positions pos0.. in the same kernel; cache (with .k, .v
+    [hk, capacity, d] and .offset): k and v are written into the cache rows and the filled prefix is returned."""
+    return _qkv_norm(acc, xscale, wscale, qn, kn, eps, L, hq, hk, d, False, rope, cache)
+
+
+def qkv_headnorm_y(y, qn, kn, eps, L, hq, hk, d, deps=(), rope=None, cache=None, pos_dev=None):
+    """bf16 y [Mp, (hq + 2 hk) d] -> q [hq, L, d], k [hk, L, d], v [hk, L, d] (q/k per-head RMSNorm)."""
+    return _qkv_norm(y, None, None, qn, kn, eps, L, hq, hk, d, False, rope, cache, pos_dev)
+
+
+def qkv_fullnorm_y(y, qn, kn, eps, L, h, d, deps=(), rope=None, cache=None, pos_dev=None):
+    """bf16 y [Mp, 3 h d] -> q, k, v [h, L, d] with RMSNorm over the full h*d-wide q and k."""
+    return _qkv_norm(y, None, None, qn, kn, eps, L, h, h, d, True, rope, cache, pos_dev)
+
+
 def set_gemm_tile(bn=0):
     """Tuning hint for the GEMM N tile (0 automatic, 128, 256)."""
     _lib.call("scmx_set_gemm_tile", bn)

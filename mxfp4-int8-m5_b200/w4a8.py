@@ -25,12 +25,24 @@ class PackedWeight:
         ws = np.concatenate([np.asarray(p[2], np.float32) for p in parts])
         if perm is not None:
             codes, bc, ws = codes[perm], bc[perm], ws[perm]
+        self.splits = [np.asarray(p[2]).shape[0] for p in parts]
+        self.perm = perm
         self.N, self.K = codes.shape[0], codes.shape[1] * 8
         self.codes, self.bcodes, self.wscale = F.to_device(codes.reshape(-1), bc, ws, device)
         self.wq = S.unpack_i8(self.codes, self.bcodes, self.N, self.K) if resident else None
 
     def int8(self):
         return self.wq if self.wq is not None else S.unpack_i8(self.codes, self.bcodes, self.N, self.K)
+
+    def unpack(self, deps=()):
+        return self.int8()
+
+    def nbytes(self):
+        return self.codes.numel() * 4 + self.bcodes.numel() + self.wscale.numel() * 4
+
+    def entry(self):
+        """(codes, bcodes, wscale, N, K) as the chained calls take it."""
+        return self.codes, self.bcodes, self.wscale, self.N, self.K
 
 
 class W4A8Linear(torch.nn.Module):
@@ -41,8 +53,12 @@ class W4A8Linear(torch.nn.Module):
     def __init__(self, codes, shifts, wscale, resident_int8=False, device="cuda"):
         super().__init__()
         shifts = np.asarray(shifts, np.uint8)
-        self.N, self.K = shifts.shape[0], shifts.shape[1] * 32
-        c, b, s = F.from_shift_layout(np.asarray(codes, np.uint32), shifts, wscale)
+        self.N = shifts.shape[0]
+        self.K = np.asarray(codes).size * 8 // self.N
+        if shifts.shape[1] * 32 == self.K:                 # one shift byte per 32-block (the reference's pack_linear)
+            c, b, s = F.from_shift_layout(np.asarray(codes, np.uint32), shifts, wscale)
+        else:                                              # already 2-bit block codes, four blocks per byte
+            c, b, s = np.asarray(codes, np.uint32), shifts, wscale
         self.codes, self.bcodes, self.wscale = F.to_device(c, b, s, device)
         self.wq = S.unpack_i8(self.codes, self.bcodes, self.N, self.K) if resident_int8 else None
 
@@ -56,3 +72,16 @@ class W4A8Linear(torch.nn.Module):
         xq, xs = S.act_quant(x2)                      # pads to a multiple of the M tile; padded rows are zero
         y = S.mm_epi(xq, self.int8_weight(), xs, self.wscale, 1)
         return y[:M].reshape(*lead, self.N).to(x.dtype)
+
+
+def apply_w4a8(model, packed, resident_int8=False):
+    """Swaps every transformer-block linear of a host_model.CausalLM for W4A8Linear (embeddings, norms, attention and the
+    output head unchanged), e2e/w4a8_mlx.py:197-207.  packed: {"layers.{i}.{path}": (codes, shifts or bcodes, wscale)}."""
+    from .host_model import LINEARS
+    dev = model.model.embed_tokens.weight.device
+    for i, layer in enumerate(model.model.layers):
+        for path in LINEARS:
+            parent_name, name = path.split(".")
+            parent = getattr(layer, parent_name)
+            setattr(parent, name, W4A8Linear(*packed[f"layers.{i}.{path}"], resident_int8=resident_int8, device=dev))
+    return model

@@ -370,6 +370,55 @@ def rmsnorm_quant(x, w, eps, Mp=None):
 
 
 # ---------------------------------------------------------------------------------------------------------------
+# q/k/v epilogue before attention (the callers' glue), e2e/sc_kernels.py:333-423,597-637; rotary step as
+# mlx.nn.RoPE(traditional=False) which e2e/fused_qwen3.py:197-203 calls
+# ---------------------------------------------------------------------------------------------------------------
+
+def rope_inv_freq(d, base):
+    """f32 [d/2]: base^(-2i/d)."""
+    i = np.arange(0, d, 2, dtype=np.float64)
+    return (1.0 / (float(base) ** (i / d))).astype(np.float32)
+
+
+def rope_half(x, inv_freq, pos0=0):
+    """Half-split rotary embedding of bf16-valued x [h, L, d] at positions pos0 + row: out[i] = x[i] cos - x[i + d/2] sin,
+    out[i + d/2] = x[i] sin + x[i + d/2] cos; products and the sum in float32, result rounded to bf16."""
+    x = np.asarray(x, np.float32)
+    L, d = x.shape[1], x.shape[2]
+    ang = (np.arange(pos0, pos0 + L, dtype=np.float32)[:, None] * np.asarray(inv_freq, np.float32)[None, :]).astype(np.float32)
+    c = np.cos(ang.astype(np.float64)).astype(np.float32)[None]
+    s = np.sin(ang.astype(np.float64)).astype(np.float32)[None]
+    x1, x2 = x[..., :d // 2], x[..., d // 2:]
+    lo = (x1 * c).astype(np.float32) - (x2 * s).astype(np.float32)
+    hi = (x1 * s).astype(np.float32) + (x2 * c).astype(np.float32)
+    return bf16_round(np.concatenate([lo, hi], -1))
+
+
+def qkv_norm(y, qn, kn, eps, L, hq, hk, d, full=False, inv_freq=None, pos0=0):
+    """bf16-valued y [>=L, (hq + 2 hk) d] -> q [hq, L, d], k [hk, L, d], v [hk, L, d].  full=False: RMSNorm of every q and
+    k head over its d values with weights qn / kn [d] (qkv_headnorm_y, e2e/sc_kernels.py:355-378); full=True: RMSNorm over
+    the whole q (hq*d) and k (hk*d) vectors with qn [hq*d], kn [hk*d] (qkv_fullnorm_y, :389-423).  Sum of squares in
+    float64 (reduction order unpinned, as for rmsnorm_bf16).  inv_freq: rotary embedding of the normalized q and k."""
+    y = np.asarray(y, np.float32)[:L]
+    parts = np.split(y, [hq * d, (hq + hk) * d], axis=1)
+    out = []
+    for x, w, h in ((parts[0], qn, hq), (parts[1], kn, hk)):
+        if full:
+            n = rmsnorm_bf16(x, w, eps).reshape(L, h, d)
+        else:
+            n = rmsnorm_bf16(x.reshape(L * h, d), w, eps).reshape(L, h, d)
+        n = n.transpose(1, 0, 2)
+        out.append(rope_half(n, inv_freq, pos0) if inv_freq is not None else n)
+    out.append(parts[2].reshape(L, hk, d).transpose(1, 0, 2))
+    return tuple(np.ascontiguousarray(o) for o in out)
+
+
+def qkv_epilogue_headnorm(acc, xs, ws, qn, kn, eps, L, hq, hk, d, **kw):
+    """The same from INT32 accumulators: EPI 1 scaling first (e2e/sc_kernels.py:333-354)."""
+    return qkv_norm(epilogue(acc, xs, ws, 1), qn, kn, eps, L, hq, hk, d, **kw)
+
+
+# ---------------------------------------------------------------------------------------------------------------
 # a15-a18: MoE routing, grouped GEMM, combine.  e2e/sc_moe.py:114-185, e2e/fused_olmoe.py:34-66
 # ---------------------------------------------------------------------------------------------------------------
 
