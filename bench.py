@@ -502,6 +502,104 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def bench_models(pkg, torch, reps=5, lengths=(512, 2048, 8192), kinds=("qwen3", "olmoe")):
+    """Whole-model numbers through the fused callers (attention, KV cache and the output head included): time to first
+    token = prefill + the last position's logits, and batch-1 decode tokens/s, for synthetic-weight models of the two
+    architectures, next to the same torch model in bf16 (unfused, torch's GEMMs)."""
+    HM, FQ, FO, DEC = pkg.host_model, pkg.fused_qwen3, pkg.fused_olmoe, pkg.decode
+    out = {}
+
+    def timed(fn, n):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(n):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return float(np.median(ts))
+
+    for kind in kinds:
+        a = HM.QWEN3_1_7B if kind == "qwen3" else HM.OLMOE_1B_7B
+        with torch.device("cuda"):
+            model = HM.CausalLM(a)
+        model.init_random(seed=0, scale=0.02)
+        res = {"params_b": round(sum(p.numel() for p in model.parameters()) / 1e9, 2)}
+        ids_all = torch.randint(0, a.vocab_size, (1, max(lengths) + 64), device="cuda")
+        cap = max(lengths) + 64
+
+        def bf16_prefill(L):
+            cache = HM.make_prompt_cache(model, cap)
+            h = model.model.embed_tokens(ids_all[:, :L])[0]
+            for layer, c in zip(model.model.layers, cache):
+                h = layer(h, c)
+            return model.head(model.model.norm(h[-1:])[None])
+
+        with torch.no_grad():
+            if kind == "qwen3":          # the loop over experts of the unfused MoE block is not a fair bf16 baseline
+                res["bf16_ttft_ms"] = {str(L): round(timed(lambda: bf16_prefill(L), reps), 3) for L in lengths}
+        fused = (FQ.FusedQwen3(model, FQ.pack_model(model, on_device=True)) if kind == "qwen3"
+                 else FO.FusedOlmoe(model, FO.pack_olmoe(model, on_device=True)))
+        res["packed_gb"] = round(fused.weight_bytes() / 1e9, 3)
+        cache = fused.make_cache(cap)
+
+        def prefill(L):
+            for c in cache:
+                c.offset = 0
+            return fused.logits(fused.hidden(ids_all[:, :L], cache)[:, -1:])
+
+        res["ttft_ms"], res["ttft_graph_ms"] = {}, {}
+        for L in lengths:
+            res["ttft_ms"][str(L)] = round(timed(lambda: prefill(L), reps), 3)
+            try:
+                g = torch.cuda.CUDAGraph()
+                s = torch.cuda.Stream()
+                s.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(s):
+                    prefill(L)
+                    torch.cuda.synchronize()
+                    with torch.cuda.graph(g, stream=s):
+                        prefill(L)
+                torch.cuda.current_stream().wait_stream(s)
+                res["ttft_graph_ms"][str(L)] = round(timed(g.replay, reps), 3)
+                del g
+            except Exception as e:  # noqa: BLE001
+                res["ttft_graph_ms"][str(L)] = f"capture failed: {str(e)[:80]}"
+        # decode: 64 tokens after a 512-token prompt, eager step() calls and one CUDA graph replayed per token
+        dec = (DEC.DecodeQwen3 if kind == "qwen3" else DEC.DecodeOlmoe)(fused)
+        prefill(512)
+        torch.cuda.synchronize()
+        n_tok = 64
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for rep in range(2):                                   # first pass warms up, second is timed
+            for c in cache:
+                c.offset = 512
+            tok = ids_all[:, 512:513]
+            e0.record()
+            for _ in range(n_tok):
+                tok = dec.step(tok, cache)[:, -1].argmax(-1, keepdim=True)
+            e1.record()
+            torch.cuda.synchronize()
+        res["decode_tok_s_eager"] = round(n_tok / (e0.elapsed_time(e1) / 1e3), 1)
+        for rep in range(2):
+            for c in cache:
+                c.offset = 512
+            e0.record()
+            dec.generate(ids_all[:, 512:513], cache, n_tok)
+            e1.record()
+            torch.cuda.synchronize()
+        res["decode_tok_s"] = round(n_tok / (e0.elapsed_time(e1) / 1e3), 1)
+        pkg._lib.check_status()
+        out[kind] = res
+        del fused, dec, cache, model
+        torch.cuda.empty_cache()
+    return out
+
+
 def run_case(args):
     """Small single-kernel cases for profiler captures (a few launches, a few hundred MB at most)."""
     import torch
@@ -534,6 +632,9 @@ def run_case(args):
         xs = torch.full((1,), 1e-2, device="cuda")
         for _ in range(3):
             G.gemv(xq, c, b, xs, w_, 151936, 1)
+    elif args.case == "models":
+        print(json.dumps(dict(case="models", models=bench_models(pkg, torch))))
+        return
     else:
         bench_moe(pkg, torch, None, reps=1)
     torch.cuda.synchronize()
@@ -551,7 +652,7 @@ def main():
     ap.add_argument("--no-overlap", action="store_true", help="decode weights on the main stream instead of a side stream")
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic stream serialization")
     ap.add_argument("--dense-only", action="store_true", help="skip the roofline / decode / MoE / CPU sections")
-    ap.add_argument("--case", choices=["gemm", "gemv", "gemvbig", "moe"], help="run one small kernel case (for profiler captures) and exit")
+    ap.add_argument("--case", choices=["gemm", "gemv", "gemvbig", "moe", "models"], help="run one small kernel case (for profiler captures) and exit")
     args = ap.parse_args()
     if args.case:
         run_case(args)

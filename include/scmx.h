@@ -98,13 +98,26 @@ int scmx_swiglu(const uint16_t* g, const uint16_t* u, int64_t n, uint16_t* out, 
  * k with qn bf16 [hq*d], kn bf16 [hk*d] (full != 0); v is copied.  Outputs are head-major: q[(h*q_head_stride + row)*d],
  * k and v at [(h*kv_head_stride + kv_row0 + row)*d], so k / v can be the rows of a cache of kv_head_stride positions.
  * inv_freq f32 [d/2] non-null: rotary embedding (half-split pairs i, i + d/2) at position pos0 + row applied to the
- * normalized q and k.  pos_dev non-null: one device int32 added to pos0 and kv_row0 (rows beyond the cache are dropped).
+ * normalized q and k; rope_table (optional) f32 [rope_rows, d] holds cos (d/2 values) then sin (d/2) of
+ * position * inv_freq per position, (float)cos((double)(float)(pos * inv_freq)): used instead of evaluating them
+ * for positions < rope_rows.  pos_dev non-null: one device int32 added to pos0 and kv_row0 (rows beyond the cache are dropped).
  * Replaces qkv_epilogue_headnorm, qkv_headnorm_y, qkv_fullnorm_y (e2e/sc_kernels.py:333-423,597-637); the rotary step
  * and cache append replace the MLX calls of e2e/fused_qwen3.py:197-203.  d a power of two, row <= 48 KB as float. */
 int scmx_qkv_norm(const void* src, int src_is_acc, const float* xscale, const float* wscale, const uint16_t* qn,
                   const uint16_t* kn, float eps, int64_t L, int hq, int hk, int d, int full, const float* inv_freq,
-                  int64_t pos0, const int32_t* pos_dev, uint16_t* q, int64_t q_head_stride, uint16_t* k, uint16_t* v,
+                  const float* rope_table, int64_t rope_rows, int64_t pos0, const int32_t* pos_dev, uint16_t* q, int64_t q_head_stride, uint16_t* k, uint16_t* v,
                   int64_t kv_head_stride, int64_t kv_row0, void* stream);
+
+/* Batch-1 decode attention: out[h] = softmax(scale * q[h] K^T) V over the first T positions of a KV cache
+ * (k_cache, v_cache bf16 [hk, capacity, d]; q bf16 [hq, d]; out bf16 [hq * d]).  T = pos_dev[0] + 1 when pos_dev is
+ * non-null (a position counter kept on the device, so the call can be replayed from a CUDA graph while the sequence
+ * grows), else n_pos.  The positions are split over nsplit CTAs per key/value head; partials f32 [hq, nsplit, d + 2]
+ * and counters int32 [hk] (zero before the first call, left zero) are caller-provided scratch.
+ * No counterpart in the reference, which calls MLX's scaled_dot_product_attention here (e2e/decode.py:103); outside
+ * the W4A8 arithmetic: float32 online softmax, bf16 output.  d in {64, 128}, hq / hk in {1, 2, 4}. */
+int scmx_attn_decode(const uint16_t* q, const uint16_t* k_cache, const uint16_t* v_cache, int64_t capacity,
+                     const int32_t* pos_dev, int64_t n_pos, float scale, int hq, int hk, int d, int nsplit,
+                     float* partials, int32_t* counters, uint16_t* out, void* stream);
 
 /* ---- dense prefill GEMM (tcgen05 kind::i8) -------------------------------------------------------------------- */
 

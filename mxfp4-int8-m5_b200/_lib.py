@@ -38,8 +38,9 @@ SIGNATURES = {
     "scmx_res_epilogue": [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp],
     "scmx_swiglu_quant": [c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp],
     "scmx_swiglu": [c_vp, c_vp, c_i64, c_vp, c_vp],
-    "scmx_qkv_norm": [c_vp, c_int, c_vp, c_vp, c_vp, c_vp, c_float, c_i64, c_int, c_int, c_int, c_int, c_vp, c_i64, c_vp, c_vp,
+    "scmx_qkv_norm": [c_vp, c_int, c_vp, c_vp, c_vp, c_vp, c_float, c_i64, c_int, c_int, c_int, c_int, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp,
                       c_i64, c_vp, c_vp, c_i64, c_i64, c_vp],
+    "scmx_attn_decode": [c_vp, c_vp, c_vp, c_i64, c_vp, c_i64, c_float, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp],
     "scmx_mm_i8": [c_vp, c_vp, c_i64, c_i64, c_i64, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp],
     "scmx_set_gemm_tile": [c_int],
     "scmx_set_pdl": [c_int],

@@ -14,6 +14,8 @@ struct QkvArgs {
     const uint16_t* kn;       // bf16 [d] or [hk*d]
     const float* inv_freq;    // f32 [d/2] or null: no rotary embedding
     const int32_t* pos_dev;   // null, or one int32 added to pos0 and kv_row0 (a step counter kept on the device)
+    const float* rope_cs;     // null, or a table f32 [rope_rows, d]: cos (d/2) then sin (d/2) of position * inv_freq
+    int64_t rope_rows;
     uint16_t *q, *k, *v;
     int64_t q_hs, kv_hs, kv_row0, pos0;
     float eps;
@@ -49,25 +51,37 @@ __global__ void __launch_bounds__(256) qkv_norm_kernel(const QkvArgs a) {
         }
     }
     if (a.inv_freq != nullptr) {
+        const int64_t pos = a.pos0 + step + row;
         for (int i = tid; i < half; i += 256) {
-            const float ang = __fmul_rn((float)(a.pos0 + step + row), a.inv_freq[i]);
-            double s, c;
-            sincos((double)ang, &s, &c);
-            cs[i] = (float)c;
-            sn[i] = (float)s;
+            if (a.rope_cs != nullptr && pos < a.rope_rows) {    // the same values, computed once on the host side
+                cs[i] = a.rope_cs[pos * d + i];
+                sn[i] = a.rope_cs[pos * d + half + i];
+            } else {
+                const float ang = __fmul_rn((float)pos, a.inv_freq[i]);
+                double s, c;
+                sincos((double)ang, &s, &c);
+                cs[i] = (float)c;
+                sn[i] = (float)s;
+            }
         }
     }
     __syncthreads();
 
     if (!a.full) {
-        for (int g = warp; g < nh; g += 8) {
+        // 8 lanes per head, 4 heads per warp at a time (the trip count is uniform over the warp)
+        const int sub = lane >> 3, l8 = lane & 7;
+        for (int g0 = warp * 4; g0 < nh; g0 += 32) {
+            const int g = g0 + sub;
             double ss = 0.0;
-            for (int i = lane; i < d; i += 32) {
-                const double x = (double)vals[g * d + i];
-                ss += x * x;
-            }
-            ss = warp_sum(ss);
-            if (lane == 0) inv[g] = rms_inverse(ss, d, a.eps);
+            if (g < nh)
+                for (int i = l8; i < d; i += 8) {
+                    const double x = (double)vals[g * d + i];
+                    ss += x * x;
+                }
+            ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+            ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+            ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+            if (g < nh && l8 == 0) inv[g] = rms_inverse(ss, d, a.eps);
         }
     } else {
         for (int part = 0; part < 2; ++part) {
@@ -122,7 +136,7 @@ using namespace scmx;
 
 extern "C" int scmx_qkv_norm(const void* src, int src_is_acc, const float* xscale, const float* wscale, const uint16_t* qn,
                              const uint16_t* kn, float eps, int64_t L, int hq, int hk, int d, int full, const float* inv_freq,
-                             int64_t pos0, const int32_t* pos_dev, uint16_t* q, int64_t q_head_stride, uint16_t* k, uint16_t* v,
+                             const float* rope_table, int64_t rope_rows, int64_t pos0, const int32_t* pos_dev, uint16_t* q, int64_t q_head_stride, uint16_t* k, uint16_t* v,
                              int64_t kv_head_stride, int64_t kv_row0, void* stream) {
     SCMX_REQUIRE(L >= 0 && hq > 0 && hk > 0, SCMX_EINVAL, "qkv_norm: L=%lld hq=%d hk=%d", (long long)L, hq, hk);
     SCMX_REQUIRE(d >= 8 && (d & (d - 1)) == 0, SCMX_EINVAL, "qkv_norm: head size %d must be a power of two >= 8", d);
@@ -137,6 +151,7 @@ extern "C" int scmx_qkv_norm(const void* src, int src_is_acc, const float* xscal
     if (L == 0) return SCMX_OK;
     QkvArgs a;
     a.src = src; a.xscale = xscale; a.wscale = wscale; a.qn = qn; a.kn = kn; a.inv_freq = inv_freq; a.pos_dev = pos_dev;
+    a.rope_cs = rope_table; a.rope_rows = rope_table ? rope_rows : 0;
     a.q = q; a.k = k; a.v = v;
     a.q_hs = q_head_stride; a.kv_hs = kv_head_stride; a.kv_row0 = kv_row0; a.pos0 = pos0;
     a.eps = eps; a.hq = hq; a.hk = hk; a.d = d; a.full = full ? 1 : 0;

@@ -22,24 +22,34 @@ ATTN = ["self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o
 EXPERTS = ["gate_proj", "up_proj", "down_proj"]
 
 
-def pack_olmoe(model, cache_path=None, fmt=F.DEFAULT):
+def pack_olmoe(model, cache_path=None, fmt=F.DEFAULT, on_device=False):
     """SC-MXFP4 of every attention linear and expert matrix; keys layers.{i}.{path} and layers.{i}.experts.{name}.{e}
-    (e2e/fused_olmoe.py:102-129).  Returns {key: (codes, bcodes, wscale)} as NumPy."""
+    (e2e/fused_olmoe.py:102-129).  Returns {key: (codes, bcodes, wscale)} as NumPy, or with on_device=True as CUDA tensors
+    (the experts of a layer are quantized in one call: the format is per output row, so the bits are the same)."""
     if cache_path and os.path.exists(cache_path):
         return packed_io.load_packed(cache_path, fmt)
     out = {}
+
+    def q(w):
+        if on_device:
+            return F.quantize_device(w.contiguous(), fmt, want_qw=False)[:3]
+        return F.quantize(w.to("cpu", torch.float64).numpy(), fmt)[:3]
+
     for i, layer in enumerate(model.model.layers):
         for path in ATTN:
             parent, name = path.split(".")
-            w = getattr(getattr(layer, parent), name).weight.detach().to("cpu", torch.float64).numpy()
-            out[f"layers.{i}.{path}"] = F.quantize(w, fmt)[:3]
+            out[f"layers.{i}.{path}"] = q(getattr(getattr(layer, parent), name).weight.detach())
         sw = layer.mlp.switch_mlp
         for name in EXPERTS:
-            wt = getattr(sw, name).weight.detach().to("cpu", torch.float64).numpy()
-            for e in range(wt.shape[0]):
-                out[f"layers.{i}.experts.{name}.{e}"] = F.quantize(wt[e], fmt)[:3]
+            wt = getattr(sw, name).weight.detach()
+            E, n, k = wt.shape
+            c, b, s = q(wt.reshape(E * n, k))
+            c, b, s = c.reshape(E, n * k // 8), b.reshape(E, n, -1), s.reshape(E, n)
+            for e in range(E):
+                out[f"layers.{i}.experts.{name}.{e}"] = (c[e], b[e], s[e])
     if cache_path:
-        packed_io.save_packed(cache_path, out)
+        packed_io.save_packed(cache_path, {k: tuple(t.cpu().numpy() if torch.is_tensor(t) else t for t in v)
+                                           for k, v in out.items()})
     return out
 
 
@@ -56,21 +66,28 @@ class FusedOlmoe:
         dev = model.model.embed_tokens.weight.device
         E, Fi = a.num_experts, a.intermediate_size
         perm = S.interleave_gate_up(Fi)
+        idx = torch.as_tensor(perm, device=dev, dtype=torch.long)
+
+        def cu(x, np_dtype):
+            if isinstance(x, torch.Tensor):
+                return x.to(dev)
+            a = np.ascontiguousarray(np.asarray(x, np_dtype))
+            return torch.from_numpy(a.view(np.int32) if np_dtype == np.uint32 else a).to(dev)
+
         self.layers = []
         for i, layer in enumerate(model.model.layers):
             parts = lambda p: flat[f"layers.{i}.{p}"]  # noqa: E731
             qkv = PackedWeight([parts(p) for p in ATTN[:3]], device=dev)
             o = PackedWeight([parts(ATTN[3])], device=dev)
-            gu_c, gu_b, gu_s, d_c, d_b, d_s = [], [], [], [], [], []
-            for e in range(E):
-                g, u, d = (parts(f"experts.{n}.{e}") for n in EXPERTS)
-                c = np.concatenate([np.asarray(g[0]).reshape(Fi, -1), np.asarray(u[0]).reshape(Fi, -1)])[perm]
-                gu_c.append(c.reshape(-1))
-                gu_b.append(np.concatenate([g[1], u[1]])[perm])
-                gu_s.append(np.concatenate([g[2], u[2]])[perm])
-                d_c.append(np.asarray(d[0]).reshape(-1)), d_b.append(d[1]), d_s.append(d[2])
-            st = lambda xs: F.to_device(np.stack(xs[0]), np.stack(xs[1]), np.stack(xs[2]), dev)  # noqa: E731
-            ex = dict(gu=st((gu_c, gu_b, gu_s)), down=st((d_c, d_b, d_s)))
+            st = {}
+            for n in EXPERTS:
+                ps = [parts(f"experts.{n}.{e}") for e in range(E)]
+                rows = int(ps[0][2].shape[0])
+                st[n] = (torch.stack([cu(p[0], np.uint32).reshape(rows, -1) for p in ps]),
+                         torch.stack([cu(p[1], np.uint8) for p in ps]), torch.stack([cu(p[2], np.float32) for p in ps]))
+            g, u, d = st["gate_proj"], st["up_proj"], st["down_proj"]
+            gu = tuple(torch.cat([a_, b_], 1)[:, idx].contiguous() for a_, b_ in zip(g, u))
+            ex = dict(gu=(gu[0].reshape(E, -1), gu[1], gu[2]), down=(d[0].reshape(E, -1).contiguous(), d[1].contiguous(), d[2].contiguous()))
             self.layers.append((layer, dict(qkv=qkv, o=o), ex))
         self.perm_gu = perm
         for layer in model.model.layers:                      # drop the bf16 weights that the packed ones replace
@@ -78,6 +95,7 @@ class FusedOlmoe:
                 setattr(layer.self_attn, path.split(".")[1], None)
             layer.mlp.switch_mlp = None
         self.inv_freq = S.rope_inv_freq(a.head_dim, a.rope_theta, dev)
+        self.rope_cs = S.rope_table(self.inv_freq, 16384)          # cos / sin of the first positions, read by the q/k/v kernel
         self.record, self.record_layers = None, ()
         self.sdpa = HM.sdpa                                   # (q, k, v, scale, causal) -> [L, H * d]; replaceable
 
@@ -130,7 +148,7 @@ class FusedOlmoe:
             wq, wo = ws["qkv"], ws["o"]
             y = S.mm_epi(xq, wq.unpack(), xs, wq.wscale, 1)
             q, kk, v = S.qkv_fullnorm_y(y, at.q_norm.weight, at.k_norm.weight, self.eps, L, H, d,
-                                        rope=(self.inv_freq, c.offset), cache=c)
+                                        rope=(self.inv_freq, c.offset, self.rope_cs), cache=c)
             c.offset += L
             o = self.sdpa(q, kk, v, at.scale, True)
             xq, xs = S.act_quant(o, Mp)

@@ -33,9 +33,10 @@ def _get(layer, path):
     return layer
 
 
-def pack_model(model, cache_path=None, fmt=F.DEFAULT):
-    """Packs every transformer-block linear; returns {"layers.{i}.{path}": (codes, bcodes, wscale)} as NumPy, cached as one
-    safetensors file when cache_path is given (e2e/w4a8_mlx.py:176-196, with 2-bit block codes as e2e/pack_format.py:83-109)."""
+def pack_model(model, cache_path=None, fmt=F.DEFAULT, on_device=False):
+    """Packs every transformer-block linear; returns {"layers.{i}.{path}": (codes, bcodes, wscale)}, cached as one safetensors
+    file when cache_path is given (e2e/w4a8_mlx.py:176-196, with 2-bit block codes as e2e/pack_format.py:83-109).  NumPy
+    arrays by default; on_device=True keeps the quantizer's CUDA tensors (no host copies; same bits)."""
     import os
     if cache_path and os.path.exists(cache_path):
         return packed_io.load_packed(cache_path, fmt)
@@ -43,10 +44,14 @@ def pack_model(model, cache_path=None, fmt=F.DEFAULT):
     for i, layer in enumerate(model.model.layers):
         for g in GROUPS.values():
             for path in g:
-                w = _get(layer, path).weight.detach().to("cpu", torch.float64).numpy()
-                out[f"layers.{i}.{path}"] = F.quantize(w, fmt)[:3]
+                w = _get(layer, path).weight.detach()
+                if on_device:
+                    out[f"layers.{i}.{path}"] = F.quantize_device(w.contiguous(), fmt, want_qw=False)[:3]
+                else:
+                    out[f"layers.{i}.{path}"] = F.quantize(w.to("cpu", torch.float64).numpy(), fmt)[:3]
     if cache_path:
-        packed_io.save_packed(cache_path, out)
+        packed_io.save_packed(cache_path, {k: tuple(t.cpu().numpy() if torch.is_tensor(t) else t for t in v)
+                                           for k, v in out.items()})
     return out
 
 
@@ -90,6 +95,7 @@ class FusedQwen3:
         self.seq = [ws[g].entry() for _, ws in self.layers for g in GROUPS]
         self.ring = None if resident else FD.DecodeRing(max(e[3] * e[4] for e in self.seq), dev, overlap)
         self.inv_freq = S.rope_inv_freq(self.args.head_dim, self.args.rope_theta, dev)
+        self.rope_cs = S.rope_table(self.inv_freq, 16384)          # cos / sin of the first positions, read by the q/k/v kernel
         self.record, self.record_layers = None, ()
         self.sdpa = HM.sdpa                                   # (q, k, v, scale, causal) -> [L, hq * d]; replaceable
 
@@ -119,7 +125,7 @@ class FusedQwen3:
     def _qkv(self, at, c, src, xs, ws, L):
         a = self.args
         hq, hk, d = a.num_attention_heads, a.num_key_value_heads, a.head_dim
-        kw = dict(rope=(self.inv_freq, c.offset), cache=c) if self.fuse_rope else {}
+        kw = dict(rope=(self.inv_freq, c.offset, self.rope_cs), cache=c) if self.fuse_rope else {}
         if src.dtype == torch.int32:
             q, k, v = S.qkv_epilogue_headnorm(src, xs, ws, at.q_norm.weight, at.k_norm.weight, self.eps, L, hq, hk, d, **kw)
         else:

@@ -120,7 +120,7 @@ class Attention(torch.nn.Module):
         self.q_proj, self.k_proj, self.v_proj, self.o_proj = _linear(D, hq * d), _linear(D, hk * d), _linear(D, hk * d), _linear(hq * d, D)
         self.q_norm = RMSNorm(hq * d if self.full_norm else d, a.rms_norm_eps)
         self.k_norm = RMSNorm(hk * d if self.full_norm else d, a.rms_norm_eps)
-        self.register_buffer("inv_freq", S.rope_inv_freq(d, a.rope_theta, "cpu"), persistent=False)
+        self.register_buffer("inv_freq", S.rope_inv_freq(d, a.rope_theta, None), persistent=False)
 
     def forward(self, x, cache):
         L = x.shape[0]
@@ -227,13 +227,15 @@ class CausalLM(torch.nn.Module):
 
     @torch.no_grad()
     def init_random(self, seed=0, scale=0.02):
-        """Seeded synthetic weights of the architecture (no checkpoint is read)."""
-        g = torch.Generator().manual_seed(seed)
+        """Seeded synthetic weights of the architecture (no checkpoint is read), generated on the parameters' device."""
+        dev = self.model.embed_tokens.weight.device
+        g = torch.Generator(device=dev).manual_seed(seed)
         for name, p in self.named_parameters():
+            r = torch.randn(p.shape, generator=g, device=dev, dtype=torch.float32)
             if name.endswith("norm.weight") or "layernorm" in name:
-                p.copy_((1.0 + 0.1 * torch.randn(p.shape, generator=g)).to(p.dtype))
+                p.copy_((1.0 + 0.1 * r).to(p.dtype))
             else:
-                p.copy_((scale * torch.randn(p.shape, generator=g)).to(p.dtype))
+                p.copy_((scale * r).to(p.dtype))
         return self
 
     @torch.no_grad()

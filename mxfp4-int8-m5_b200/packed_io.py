@@ -22,7 +22,8 @@ def save_packed(path, packed):
     """packed: {name: (codes, bcodes, wscale)} -> one safetensors file, written under a temporary name first."""
     flat = {}
     for name, (c, b, s) in packed.items():
-        flat[name + ".codes"] = np.ascontiguousarray(np.asarray(c, np.uint32).reshape(-1))
+        c = np.asarray(c)
+        flat[name + ".codes"] = np.ascontiguousarray((c.view(np.uint32) if c.dtype == np.int32 else c.astype(np.uint32)).reshape(-1))
         flat[name + ".bcodes"] = np.ascontiguousarray(np.asarray(b, np.uint8))
         flat[name + ".wscale"] = np.ascontiguousarray(np.asarray(s, np.float32))
     os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)

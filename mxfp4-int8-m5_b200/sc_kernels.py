@@ -176,8 +176,15 @@ def sc_swiglu(g, u):
 
 def rope_inv_freq(d, base, device="cuda"):
     """f32 [d/2]: base^(-2i/d), the frequencies of a half-split (non-interleaved) rotary embedding."""
-    i = torch.arange(0, d, 2, dtype=torch.float64)
-    return (1.0 / (float(base) ** (i / d))).to(torch.float32).to(device)
+    i = torch.arange(0, d, 2, dtype=torch.float64, device=device)   # device=None: torch's current default device
+    return (1.0 / (float(base) ** (i / d))).to(torch.float32)
+
+
+def rope_table(inv_freq, rows):
+    """f32 [rows, d]: cos then sin of position * inv_freq (the product in float32, the functions in float64, rounded to
+    float32): what the q/k/v kernel evaluates per call, precomputed."""
+    ang = (torch.arange(rows, device=inv_freq.device, dtype=torch.float32)[:, None] * inv_freq[None, :]).double()
+    return torch.cat([torch.cos(ang), torch.sin(ang)], 1).float().contiguous()
 
 
 def _qkv_norm(src, xscale, wscale, qn, kn, eps, L, hq, hk, d, full, rope, cache, pos_dev=None):
@@ -186,7 +193,8 @@ def _qkv_norm(src, xscale, wscale, qn, kn, eps, L, hq, hk, d, full, rope, cache,
     assert src.shape[1] == ntot and src.shape[0] >= L and src.is_contiguous()
     is_acc = src.dtype == torch.int32
     assert is_acc or src.dtype == torch.bfloat16
-    inv_freq, pos0 = rope if rope is not None else (None, 0)
+    inv_freq, pos0 = (rope[0], rope[1]) if rope is not None else (None, 0)
+    table = rope[2] if rope is not None and len(rope) > 2 else None      # optional rope_table(...) of the same inv_freq
     q = torch.empty((hq, L, d), dtype=torch.bfloat16, device=src.device)
     if cache is None:
         k = torch.empty((hk, L, d), dtype=torch.bfloat16, device=src.device)
@@ -197,7 +205,8 @@ def _qkv_norm(src, xscale, wscale, qn, kn, eps, L, hq, hk, d, full, rope, cache,
         assert kbuf.shape == (hk, cap, d) and kbuf.is_contiguous() and vbuf.is_contiguous()
         k, v = kbuf[:, :row0 + L], vbuf[:, :row0 + L]
     _lib.call("scmx_qkv_norm", _lib.ptr(src), int(is_acc), _lib.ptr(xscale), _lib.ptr(wscale), _lib.ptr(qn), _lib.ptr(kn),
-              _eps(eps), L, hq, hk, d, int(full), _lib.ptr(inv_freq), int(pos0), _lib.ptr(pos_dev), _lib.ptr(q), L,
+              _eps(eps), L, hq, hk, d, int(full), _lib.ptr(inv_freq), _lib.ptr(table),
+              0 if table is None else table.shape[0], int(pos0), _lib.ptr(pos_dev), _lib.ptr(q), L,
               _lib.ptr(kbuf), _lib.ptr(vbuf), cap, row0, _lib.stream())
     return q, k, v
 
@@ -205,7 +214,7 @@ def _qkv_norm(src, xscale, wscale, qn, kn, eps, L, hq, hk, d, full, rope, cache,
 def qkv_epilogue_headnorm(acc, xscale, wscale, qn, kn, eps, L, hq, hk, d, dtype=torch.bfloat16, deps=(), rope=None,
                           cache=None):
     """acc int32 [Mp, (hq + 2 hk) d] -> q [hq, L, d], k [hk, L, d], v [hk, L, d] with per-head RMSNorm of q and k.
-    rope=(inv_freq, pos0): rotary embedding of q and k at positions pos0.. in the same kernel; cache (with .k, .v
+    rope=(inv_freq, pos0[, rope_table]): rotary embedding of q and k at positions pos0.. in the same kernel; cache (with .k, .v
     [hk, capacity, d] and .offset): k and v are written into the cache rows and the filled prefix is returned."""
     return _qkv_norm(acc, xscale, wscale, qn, kn, eps, L, hq, hk, d, False, rope, cache)
 
@@ -218,6 +227,31 @@ def qkv_headnorm_y(y, qn, kn, eps, L, hq, hk, d, deps=(), rope=None, cache=None,
 def qkv_fullnorm_y(y, qn, kn, eps, L, h, d, deps=(), rope=None, cache=None, pos_dev=None):
     """bf16 y [Mp, 3 h d] -> q, k, v [h, L, d] with RMSNorm over the full h*d-wide q and k."""
     return _qkv_norm(y, None, None, qn, kn, eps, L, h, h, d, True, rope, cache, pos_dev)
+
+
+class DecodeAttention:
+    """Batch-1 attention over a KV cache (scmx_attn_decode) with its scratch: q [hq, 1, d] or [hq, d], cache with .k / .v
+    [hk, capacity, d] -> bf16 [1, hq * d].  n_pos positions are attended, or pos_dev[0] + 1 when pos_dev (int32 [1] on the
+    device) is given, which keeps the call replayable from a CUDA graph while the sequence grows."""
+
+    def __init__(self, hq, hk, d, device="cuda", n_sm=148):
+        self.hq, self.hk, self.d = hq, hk, d
+        self.nsplit = max(1, min(32, n_sm // hk))
+        self.part = torch.empty((hq, self.nsplit, d + 2), dtype=torch.float32, device=device)
+        self.counters = torch.zeros(hk, dtype=torch.int32, device=device)
+
+    @staticmethod
+    def supports(hq, hk, d):
+        return d in (64, 128) and hq % hk == 0 and hq // hk in (1, 2, 4)
+
+    def __call__(self, q, cache, scale, n_pos=None, pos_dev=None):
+        _lib.require_cuda(q, cache.k, cache.v, pos_dev)
+        assert q.dtype == torch.bfloat16 and q.is_contiguous() and q.numel() == self.hq * self.d
+        out = torch.empty((1, self.hq * self.d), dtype=torch.bfloat16, device=q.device)
+        _lib.call("scmx_attn_decode", _lib.ptr(q), _lib.ptr(cache.k), _lib.ptr(cache.v), cache.k.shape[1], _lib.ptr(pos_dev),
+                  int(n_pos or 0), float(scale), self.hq, self.hk, self.d, self.nsplit, _lib.ptr(self.part),
+                  _lib.ptr(self.counters), _lib.ptr(out), _lib.stream())
+        return out
 
 
 def set_gemm_tile(bn=0):

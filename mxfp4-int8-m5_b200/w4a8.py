@@ -20,15 +20,26 @@ class PackedWeight:
     (e.g. interleave_gate_up for the SwiGLU epilogue); holds CUDA tensors."""
 
     def __init__(self, parts, perm=None, resident=False, device="cuda"):
-        codes = np.concatenate([np.asarray(p[0], np.uint32).reshape(p[1].shape[0], -1) for p in parts])
-        bc = np.concatenate([np.asarray(p[1], np.uint8) for p in parts])
-        ws = np.concatenate([np.asarray(p[2], np.float32) for p in parts])
-        if perm is not None:
-            codes, bc, ws = codes[perm], bc[perm], ws[perm]
-        self.splits = [np.asarray(p[2]).shape[0] for p in parts]
+        """parts: list of (codes [N*K/8], bcodes [N, K/128], wscale [N]) as NumPy arrays (uint32 / uint8 / f32) or as the
+        CUDA tensors quantize_device returns."""
+        dev = device
+
+        def cu(x, np_dtype):
+            if isinstance(x, torch.Tensor):
+                return x.to(dev)
+            a = np.ascontiguousarray(np.asarray(x, np_dtype))
+            return torch.from_numpy(a.view(np.int32) if np_dtype == np.uint32 else a).to(dev)
+
+        self.splits = [int(p[2].shape[0]) for p in parts]
+        codes = torch.cat([cu(p[0], np.uint32).reshape(n, -1) for p, n in zip(parts, self.splits)])
+        bc = torch.cat([cu(p[1], np.uint8) for p in parts])
+        ws = torch.cat([cu(p[2], np.float32) for p in parts])
         self.perm = perm
+        if perm is not None:
+            idx = torch.as_tensor(np.asarray(perm), device=dev, dtype=torch.long)
+            codes, bc, ws = codes[idx], bc[idx], ws[idx]
         self.N, self.K = codes.shape[0], codes.shape[1] * 8
-        self.codes, self.bcodes, self.wscale = F.to_device(codes.reshape(-1), bc, ws, device)
+        self.codes, self.bcodes, self.wscale = codes.reshape(-1).contiguous(), bc.contiguous(), ws.contiguous()
         self.wq = S.unpack_i8(self.codes, self.bcodes, self.N, self.K) if resident else None
 
     def int8(self):

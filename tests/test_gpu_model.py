@@ -55,6 +55,14 @@ def test_qkv_norm_matches_oracle(scmx, oracle, full, from_acc, rope):
     # rows outside [offset, offset + L) of the cache are untouched
     assert bool((cache.k[:, :off] == 7).all()) and bool((cache.k[:, off + L:] == 7).all())
     assert bool((cache.v[:, :off] == 7).all()) and bool((cache.v[:, off + L:] == 7).all())
+    if rope:       # the precomputed cos / sin table gives the same bits; positions past its end fall back to evaluation
+        for rows in (64, off + 10):
+            tab = S.rope_table(H.cuda(inv), rows)
+            c3 = HM.KVCache(hk, d, 64)
+            c3.offset = off
+            q3, k3, v3 = S._qkv_norm(src, cxs, cws, H.to_bf16_cuda(qn), H.to_bf16_cuda(kn), eps, L, hq, hk, d, full,
+                                     (H.cuda(inv), off, tab), c3)
+            assert torch.equal(q3, q) and torch.equal(k3[:, off:], k[:, off:])
     # without a cache the outputs are fresh [h, L, d] tensors with the same values
     q2, k2, v2 = S._qkv_norm(src, cxs, cws, H.to_bf16_cuda(qn), H.to_bf16_cuda(kn), eps, L, hq, hk, d, full,
                              (H.cuda(inv), off) if rope else None, None)
@@ -83,6 +91,26 @@ def test_qkv_norm_device_side_position(scmx, oracle):
     S.qkv_headnorm_y(y, qn, kn, 1e-6, 1, hq, hk, d, rope=(inv, 0), cache=b, pos_dev=step)
     torch.cuda.synchronize()
     assert torch.equal(before, b.k)
+
+
+@pytest.mark.parametrize("hq,hk,d", [(4, 4, 64), (16, 8, 128), (8, 2, 128)])
+@pytest.mark.parametrize("T", [1, 17, 600, 2049])
+def test_decode_attention_kernel(scmx, hq, hk, d, T):
+    S, HM = _mod("sc_kernels"), _mod("host_model")
+    g = torch.Generator(device="cuda").manual_seed(T + d)
+    cap = 2304
+    c = HM.KVCache(hk, d, cap)
+    c.k.copy_(torch.randn(c.k.shape, generator=g, device="cuda") * 1.5)
+    c.v.copy_(torch.randn(c.v.shape, generator=g, device="cuda"))
+    q = (torch.randn((hq, 1, d), generator=g, device="cuda") * 1.5).to(torch.bfloat16)
+    att = S.DecodeAttention(hq, hk, d)
+    want = HM.sdpa_f64(q, c.k[:, :T], c.v[:, :T], d ** -0.5, False).float()
+    got = att(q, c, d ** -0.5, n_pos=T).float()
+    assert H.rel_l2(got.cpu().numpy(), want.cpu().numpy()) < 4e-3          # one bf16 rounding of a float32 result
+    pos = torch.tensor([T - 1], dtype=torch.int32, device="cuda")
+    again = att(q, c, d ** -0.5, pos_dev=pos).float()                       # device-side length, second use of the scratch
+    assert torch.equal(got, again)
+    assert int(att.counters.abs().sum()) == 0
 
 
 # ---- whole models ------------------------------------------------------------------------------------------------------
@@ -159,28 +187,39 @@ def test_fused_equals_unfused_w4a8_linear_model(scmx, kind):
         ref = unfused(ids).float().cpu().numpy()[0]
     got = H.bf16_np(fused(ids))[0]
     # the unfused model rounds gate and up to bf16 separately and uses torch's silu: not bit-equal, same function
-    assert H.rel_l2(got, ref) < 2e-2
+    assert H.rel_l2(got, ref) < 5e-2
 
 
 @pytest.mark.parametrize("kind", ["qwen3", "olmoe"])
 def test_decode_steps_match_prefill(scmx, kind):
-    DEC = _mod("decode")
+    DEC, HM = _mod("decode"), _mod("host_model")
     model, a = _tiny(kind)
     fused, packed = _fused(kind, model)
-    dec = (DEC.DecodeQwen3 if kind == "qwen3" else DEC.DecodeOlmoe)(fused)
+    cls = DEC.DecodeQwen3 if kind == "qwen3" else DEC.DecodeOlmoe
     ids = _ids(40, a.vocab_size, 15)
     n0 = 36
+    # attention in float64 on both sides: what remains are the GEMVs against the GEMMs (exact integers both) and the row
+    # kernels at M = 1 against M = 128 k, so a decode step reproduces the prefill's logits
+    fused.sdpa = HM.sdpa_f64
+    dec = cls(fused, attention="torch")
     cache = fused.make_cache(64)
-    logits = fused(ids[:, :n0], cache)
+    fused(ids[:, :n0], cache)
     full = fused(ids)                                   # logits of every prefix from one prefill
-    assert H.rel_l2(H.bf16_np(logits[0, -1]), H.bf16_np(full[0, n0 - 1])) < 1e-2
     for t in range(n0, 40):
         step = dec.step(ids[:, t:t + 1], cache)
         assert cache[0].offset == t + 1
         got, want = H.bf16_np(step[0, 0]), H.bf16_np(full[0, t])
-        # the GEMVs give the GEMMs' exact integers; attention at L = 1 runs another torch kernel than the prefill
-        assert H.rel_l2(got, want) < 1.5e-2
+        assert H.rel_l2(got, want) < 1e-3
         assert got.argmax() == want.argmax()
+    # default attention (torch's kernel in the prefill, the library's decode kernel in the step): last-bit differences
+    # of the attention outputs, amplified by the INT8 steps of a small random model
+    fused.sdpa = HM.sdpa
+    dec = cls(fused)
+    cache = fused.make_cache(64)
+    fused(ids[:, :n0], cache)
+    full = fused(ids)
+    step = dec.step(ids[:, n0:n0 + 1], cache)
+    assert H.rel_l2(H.bf16_np(step[0, 0]), H.bf16_np(full[0, n0])) < 8e-2
 
 
 def test_prefill_into_offset_cache(scmx):
@@ -191,7 +230,7 @@ def test_prefill_into_offset_cache(scmx):
     cache = fused.make_cache(128)
     fused(ids[:, :50], cache)
     second = fused(ids[:, 50:], cache)
-    assert H.rel_l2(H.bf16_np(second[0]), H.bf16_np(whole[0, 50:])) < 1.5e-2
+    assert H.rel_l2(H.bf16_np(second[0]), H.bf16_np(whole[0, 50:])) < 8e-2
 
 
 def test_pack_cache_file_round_trip(scmx, tmp_path):
@@ -209,4 +248,41 @@ def test_pack_cache_file_round_trip(scmx, tmp_path):
     ids = _ids(64, a.vocab_size, 17)
     a1 = FQ.FusedQwen3(copy.deepcopy(model), packed)(ids)
     a2 = FQ.FusedQwen3(copy.deepcopy(model), loaded)(ids)
-    assert torch.equal(a1, a2)
+    a3 = FQ.FusedQwen3(copy.deepcopy(model), FQ.pack_model(model, on_device=True))(ids)
+    assert torch.equal(a1, a2) and torch.equal(a1, a3)
+
+
+@pytest.mark.parametrize("kind", ["qwen3", "olmoe"])
+def test_graph_generate_equals_eager_steps(scmx, kind):
+    DEC = _mod("decode")
+    model, a = _tiny(kind)
+    fused, _ = _fused(kind, model)
+    dec = (DEC.DecodeQwen3 if kind == "qwen3" else DEC.DecodeOlmoe)(fused)
+    assert dec.attention == "kernel"
+    ids = _ids(24, a.vocab_size, 18)
+    n = 12
+
+    def prompt():
+        cache = fused.make_cache(64)
+        logits = fused(ids, cache)
+        return cache, logits[:, -1].argmax(-1, keepdim=True)
+
+    cache, tok = prompt()
+    eager = []
+    for _ in range(n):
+        tok = dec.step(tok, cache)[:, -1].argmax(-1, keepdim=True)
+        eager.append(int(tok))
+    cache2, tok2 = prompt()
+    got = dec.generate(tok2, cache2, n).tolist()
+    assert got == eager and cache2[0].offset == 24 + n
+    assert torch.equal(cache[0].k[:, :24 + n], cache2[0].k[:, :24 + n])
+    # a second run on the same cache object reuses the captured graph from a new start position
+    for c in cache2:
+        c.offset = 24
+    assert dec.generate(tok2, cache2, n).tolist() == eager
+    # the kernel attention and torch's agree to bf16 accuracy on a step
+    dec_t = (DEC.DecodeQwen3 if kind == "qwen3" else DEC.DecodeOlmoe)(fused, attention="torch")
+    c1, t1 = prompt()
+    c2, _ = prompt()
+    l1, l2 = dec.step(t1, c1), dec_t.step(t1, c2)
+    assert H.rel_l2(H.bf16_np(l1[0, 0]), H.bf16_np(l2[0, 0])) < 8e-2
