@@ -237,6 +237,47 @@ int scmx_gemv(const int8_t* xq, const float* xscale, const uint32_t* codes, cons
               int64_t N, int64_t K, const scmx_format* fmt, int epi, const uint16_t* res, const int32_t* eidx,
               int n_routed, int shared, int xstride, void* out, int pdl, void* stream);
 
+/* scmx_gemv on a bf16 input row (or rows, xstride = 1) quantized inside the kernel: pro = 1 per-token INT8
+ * (scmx_act_quant's arithmetic), pro = 2 RMSNorm with weights nw bf16 [K] and eps first (scmx_rmsnorm_quant's).
+ * Every CTA computes the INT8 row in shared memory after its weight loads are in flight; results are bit-identical to
+ * the row kernel followed by scmx_gemv.  Replaces the PRO 1 / PRO 2 prologues of sc_decode.gemv
+ * (e2e/sc_decode.py:50-65).  K <= 8192, epi in 1..3; always the register kernel (no streaming variant). */
+int scmx_gemv_pro(const uint16_t* x, int pro, const uint16_t* nw, float eps, const uint32_t* codes, const uint8_t* bcodes,
+                  const float* wscale, int64_t N, int64_t K, const scmx_format* fmt, int epi, const uint16_t* res,
+                  const int32_t* eidx, int n_routed, int shared, int xstride, void* out, int pdl, void* stream);
+
+/* ---- one decode step of a dense stack as a persistent kernel ------------------------------------------------------------- */
+
+/* Weights of one decoder layer for scmx_decode_step_dense: [0] q|k|v rows concatenated, [1] o, [2] gate|up with rows
+ * interleaved for the SwiGLU epilogue, [3] down; SC-MXFP4 in the default format (block 32, shifts).  k_cache / v_cache:
+ * bf16 [hk, capacity, d]. */
+typedef struct scmx_decode_layer {
+    const uint32_t* codes[4];
+    const uint8_t* bcodes[4];
+    const float* wscale[4];
+    const uint16_t* ln_in;     /* input RMSNorm weights, bf16 [D] */
+    const uint16_t* ln_post;   /* post-attention RMSNorm weights, bf16 [D] */
+    const uint16_t* q_norm;    /* bf16 [d] */
+    const uint16_t* k_norm;    /* bf16 [d] */
+    uint16_t* k_cache;
+    uint16_t* v_cache;
+} scmx_decode_layer;
+
+/* All layers of one batch-1 decode step in one cooperative launch: h bf16 [D] (in: the token's embedding, out: the residual
+ * stream after the last layer) goes through n_layers of RMSNorm + INT8 -> q|k|v GEMV -> q/k head RMSNorm + rotary embedding
+ * + cache append at row pos_dev[0] -> attention over pos_dev[0] + 1 positions -> o GEMV + residual -> RMSNorm + INT8 ->
+ * gate|up GEMV with SwiGLU -> INT8 -> down GEMV + residual, the chain of e2e/decode.py:58-110, with grid-wide barriers
+ * between the steps instead of kernel boundaries.  Same bits as scmx_rmsnorm_quant / scmx_gemv / scmx_qkv_norm /
+ * scmx_attn_decode (with the same nsplit) / scmx_act_quant called in that order.
+ * layers: device array; y bf16 [(hq + 2 hk) d], act bf16 [F], partials f32 [hq, nsplit, d + 2], barrier uint32 [2] are
+ * scratch; status int32 [1] receives 100 + k if barrier k timed out (0.5 s), after which the step's outputs are invalid.
+ * Limits: d = 128; D, F and hq*d multiples of 1024 up to 6144; hq/hk in {1, 2, 4}; hk * nsplit <= number of SMs.
+ * Not to be run concurrently with other work on the same device: the launch needs every SM. */
+int scmx_decode_step_dense(const scmx_decode_layer* layers, int n_layers, int D, int F, int hq, int hk, int d, float eps,
+                           float scale, const float* inv_freq, const float* rope_table, int64_t rope_rows, int64_t capacity,
+                           const int32_t* pos_dev, uint16_t* h, uint16_t* y, uint16_t* act, float* partials, int nsplit,
+                           uint32_t* barrier, int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -19,6 +19,13 @@ class ScmxFormat(ctypes.Structure):
                 ("code_mag", ctypes.c_int32 * 8), ("mult", ctypes.c_int32 * 16)]
 
 
+class ScmxDecodeLayer(ctypes.Structure):
+    """Mirror of `scmx_decode_layer` in include/scmx.h."""
+    _fields_ = [("codes", ctypes.c_void_p * 4), ("bcodes", ctypes.c_void_p * 4), ("wscale", ctypes.c_void_p * 4),
+                ("ln_in", ctypes.c_void_p), ("ln_post", ctypes.c_void_p), ("q_norm", ctypes.c_void_p),
+                ("k_norm", ctypes.c_void_p), ("k_cache", ctypes.c_void_p), ("v_cache", ctypes.c_void_p)]
+
+
 class ScmxError(RuntimeError):
     """A libscmx entry point returned a non-zero status."""
 
@@ -63,6 +70,10 @@ SIGNATURES = {
     "scmx_enable_peer_access": [c_int],
     "scmx_moe_combine": [c_vp, c_vp, c_vp, c_vp, c_vp, c_float, c_i64, c_i64, c_i64, c_int, c_int, c_vp, c_vp, c_vp,
                          c_vp],
+    "scmx_decode_step_dense": [c_vp, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_vp, c_vp, c_i64, c_i64, c_vp,
+                               c_vp, c_vp, c_vp, c_vp, c_int, c_vp, c_vp, c_vp],
+    "scmx_gemv_pro": [c_vp, c_int, c_vp, c_float, c_vp, c_vp, c_vp, c_i64, c_i64, _FMT_P, c_int, c_vp, c_vp, c_int, c_int, c_int,
+                      c_vp, c_int, c_vp],
     "scmx_gemv": [c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, _FMT_P, c_int, c_vp, c_vp, c_int, c_int, c_int, c_vp,
                   c_int, c_vp],
 }

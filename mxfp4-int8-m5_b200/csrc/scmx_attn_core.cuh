@@ -1,0 +1,165 @@
+// Device functions of the batch-1 decode attention, shared by the stand-alone kernel and the persistent decode kernel so
+// that both produce the same bits: position chunking, one (key/value head, split) task with a float32 online softmax,
+// and the combination of the splits.
+#pragma once
+#include "scmx_common.cuh"
+
+namespace scmx {
+
+constexpr int AD_THREADS = 128;        // 4 warps x 4 position slots x 8 lanes per position
+constexpr int AD_MIN_CHUNK = 64;       // positions per split at least: short sequences use the first few splits only
+constexpr float LOG2E = 1.4426950408889634f;
+
+template <int G, int D>
+struct AttnSmem {
+    float acc[4][G][D];
+    float ml[4][G][2];
+};
+
+// T positions over nsplit splits -> positions per split (a multiple of 16) and the number of splits that have work.
+__device__ __forceinline__ void attn_chunking(int64_t T, int nsplit, int64_t& chunk, int& active) {
+    chunk = (T + nsplit - 1) / nsplit;
+    chunk = chunk < AD_MIN_CHUNK ? AD_MIN_CHUNK : ((chunk + 15) & ~(int64_t)15);
+    active = (int)((T + chunk - 1) / chunk);
+}
+
+// merge (m2, l2, a2) into (m, l, a): two partial softmax states over disjoint positions
+template <int E>
+__device__ __forceinline__ void merge_state(float& m, float& l, float (&a)[E], float m2, float l2, const float (&a2)[E]) {
+    const float mn = fmaxf(m, m2);
+    if (mn == -INFINITY) return;
+    const float c1 = exp2f(m - mn), c2 = exp2f(m2 - mn);
+    l = l * c1 + l2 * c2;
+#pragma unroll
+    for (int i = 0; i < E; ++i) a[i] = a[i] * c1 + a2[i] * c2;
+    m = mn;
+}
+
+// One (key/value head, split) task, run by the first AD_THREADS threads of the CTA (every thread of the CTA must call it:
+// it contains __syncthreads).  q: bf16 [G][D] of the G query heads sharing this key/value head; kb / vb: the head's cache
+// rows [cap][D]; positions [t0, t1).  Position t_new (or -1) is read from knew / vnew (bf16 [D]) instead of the cache.
+// q, knew, vnew may point to shared or global memory.  Writes the G partial states to part + g * part_stride_g:
+// D unnormalized outputs, the running maximum (log2 domain), the running sum.
+template <int G, int D>
+__device__ __forceinline__ void attn_split(const uint16_t* q, const uint16_t* kb, const uint16_t* vb, int64_t t0, int64_t t1,
+                                           int64_t t_new, const uint16_t* knew, const uint16_t* vnew, float scale, float* part,
+                                           size_t part_stride_g, AttnSmem<G, D>& sm) {
+    constexpr int E = D / 8;                  // elements per lane
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, slot = lane >> 3, l8 = lane & 7;
+    if (tid < AD_THREADS) {
+        float qf[G][E], acc[G][E], m[G], l[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const uint16_t* qp = q + (size_t)g * D + l8 * E;
+#pragma unroll
+            for (int i = 0; i < E; ++i) {
+                qf[g][i] = bf16_to_f32(qp[i]) * (scale * LOG2E);
+                acc[g][i] = 0.0f;
+            }
+            m[g] = -INFINITY;
+            l[g] = 0.0f;
+        }
+        // the trip count is uniform over the warp (the shuffles below need every lane); slots past the end are masked
+        for (int64_t tb = t0 + warp * 4; tb < t1; tb += 16) {
+            const int64_t t = tb + slot;
+            const bool valid = t < t1;
+            const uint16_t* kp = (t == t_new) ? knew + l8 * E : kb + t * D + l8 * E;
+            const uint16_t* vp = (t == t_new) ? vnew + l8 * E : vb + t * D + l8 * E;
+            float kf[E], vf[E];
+#pragma unroll
+            for (int c = 0; c < E / 8; ++c) {
+                uint4 kw = make_uint4(0, 0, 0, 0), vw = make_uint4(0, 0, 0, 0);
+                if (valid) {
+                    kw = *reinterpret_cast<const uint4*>(kp + 8 * c);
+                    vw = *reinterpret_cast<const uint4*>(vp + 8 * c);
+                }
+                const uint32_t ku[4] = {kw.x, kw.y, kw.z, kw.w}, vu[4] = {vw.x, vw.y, vw.z, vw.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    kf[8 * c + 2 * i] = __uint_as_float(ku[i] << 16);
+                    kf[8 * c + 2 * i + 1] = __uint_as_float(ku[i] & 0xFFFF0000u);
+                    vf[8 * c + 2 * i] = __uint_as_float(vu[i] << 16);
+                    vf[8 * c + 2 * i + 1] = __uint_as_float(vu[i] & 0xFFFF0000u);
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float s = 0.0f;
+#pragma unroll
+                for (int i = 0; i < E; ++i) s = fmaf(qf[g][i], kf[i], s);
+                s += __shfl_xor_sync(0xffffffffu, s, 1);
+                s += __shfl_xor_sync(0xffffffffu, s, 2);
+                s += __shfl_xor_sync(0xffffffffu, s, 4);
+                if (valid) {
+                    const float mn = fmaxf(m[g], s);
+                    const float corr = exp2f(m[g] - mn), p = exp2f(s - mn);
+                    l[g] = l[g] * corr + p;
+#pragma unroll
+                    for (int i = 0; i < E; ++i) acc[g][i] = acc[g][i] * corr + p * vf[i];
+                    m[g] = mn;
+                }
+            }
+        }
+        // merge the 4 position slots of a warp
+#pragma unroll
+        for (int off = 8; off <= 16; off <<= 1) {
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float m2 = __shfl_xor_sync(0xffffffffu, m[g], off), l2 = __shfl_xor_sync(0xffffffffu, l[g], off);
+                float a2[E];
+#pragma unroll
+                for (int i = 0; i < E; ++i) a2[i] = __shfl_xor_sync(0xffffffffu, acc[g][i], off);
+                merge_state<E>(m[g], l[g], acc[g], m2, l2, a2);
+            }
+        }
+        if (slot == 0) {
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+#pragma unroll
+                for (int i = 0; i < E; ++i) sm.acc[warp][g][l8 * E + i] = acc[g][i];
+                if (l8 == 0) {
+                    sm.ml[warp][g][0] = m[g];
+                    sm.ml[warp][g][1] = l[g];
+                }
+            }
+        }
+    }
+    __syncthreads();
+    // merge the 4 warps; thread e < D owns output element e of every q head of this kv head
+    if (tid < AD_THREADS) {
+        for (int g = 0; g < G; ++g) {
+            float mm = -INFINITY;
+            for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sm.ml[w][g][0]);
+            float ll = 0.0f, av = 0.0f;
+            for (int w = 0; w < 4; ++w) {
+                const float c = mm == -INFINITY ? 0.0f : exp2f(sm.ml[w][g][0] - mm);
+                ll += sm.ml[w][g][1] * c;
+                if (tid < D) av += sm.acc[w][g][tid] * c;
+            }
+            float* p = part + (size_t)g * part_stride_g;
+            if (tid < D) p[tid] = av;
+            if (tid == 0) {
+                p[D] = mm;
+                p[D + 1] = ll;
+            }
+        }
+    }
+}
+
+// Output element e of one query head from the partial states of its `active` splits (consecutive, stride D + 2 floats).
+template <int D>
+__device__ __forceinline__ float attn_combine(const float* p, int active, int e) {
+    constexpr int stride = D + 2;
+    float mm = -INFINITY;
+    for (int s = 0; s < active; ++s) mm = fmaxf(mm, __ldcg(p + s * stride + D));
+    float ll = 0.0f, av = 0.0f;
+    for (int s = 0; s < active; ++s) {
+        const float ms = __ldcg(p + s * stride + D);
+        const float c = ms == -INFINITY ? 0.0f : exp2f(ms - mm);
+        ll += __ldcg(p + s * stride + D + 1) * c;
+        av += __ldcg(p + s * stride + e) * c;
+    }
+    return av / ll;
+}
+
+}  // namespace scmx

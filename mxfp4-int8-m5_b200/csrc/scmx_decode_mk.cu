@@ -1,0 +1,506 @@
+// One decode step of a dense (Qwen3-style) stack as ONE persistent kernel: every SM keeps a CTA resident for the whole
+// step and the CTAs move through the phases of each layer together, separated by grid-wide barriers instead of kernel
+// boundaries.  A batch-1 step is a chain of ~10 tiny dependent kernels per layer; launched separately (even from a CUDA
+// graph, with programmatic dependent launch) each link costs a grid drain and a launch, about 5 us, while the weights it
+// reads would take 1 us at HBM speed.  Here a link costs one barrier, the activations are re-quantized redundantly by every
+// CTA in shared memory (instead of by a one-CTA kernel that everything waits for), and each warp issues the weight loads of
+// its first rows BEFORE it enters the barrier, because they do not depend on the activations.
+//
+// Per layer (5 barriers):
+//   P1  RMSNorm + INT8 of h (each CTA, shared memory) -> q|k|v GEMV rows spread over all warps -> y (bf16)
+//   P3  per (kv head, split) CTA: q/k RMSNorm + rotary embedding of the new token, cache append, attention over its
+//       positions -> partial softmax states
+//   P4  every CTA combines the partials to o, INT8 of o -> o-projection GEMV + residual -> h
+//   P5  RMSNorm + INT8 of h -> gate|up GEMV with SwiGLU -> act
+//   P6  INT8 of act -> down GEMV + residual -> h
+// Arithmetic: the device functions of the stand-alone kernels (row kernels, GEMV, q/k/v epilogue, decode attention), so the
+// step produces the same bits as the chain of those kernels.  Callers: e2e/decode.py:29-110 of the reference is the chain.
+//
+// Every wait is bounded (MK_WAIT_NS): a CTA that gives up raises the abort word, writes the status word and returns; the
+// others see the abort word in their own waits and return too.  The launch is cooperative, so all CTAs are co-resident.
+#include "scmx_attn_core.cuh"
+#include "scmx_common.cuh"
+#include "scmx_gemv_core.cuh"
+#include "scmx_ptx.cuh"
+
+namespace scmx {
+
+constexpr int MK_THREADS = 256;
+constexpr int MK_WARPS = MK_THREADS / 32;
+constexpr int MK_MAXSTEPS = 6;                       // K <= 6144: a lane holds 32 codes of 4 rows per step
+constexpr int MK_MAXK = 1024 * MK_MAXSTEPS;
+constexpr int MK_MAXHQ = 32;
+constexpr uint64_t MK_WAIT_NS = 500000000ull;        // 0.5 s
+
+struct MkArgs {
+    const scmx_decode_layer* layers;
+    int n_layers, D, F, hq, hk, nsplit;
+    float eps, scale;
+    const float* inv_freq;
+    const float* rope_cs;
+    int64_t rope_rows, cap;
+    const int32_t* pos_dev;
+    uint16_t* h;          // bf16 [D] residual stream, in and out
+    uint16_t* y;          // bf16 [(hq + 2 hk) d]
+    uint16_t* act;        // bf16 [F]
+    float* part;          // f32 [hq, nsplit, d + 2]
+    uint32_t* bar;        // [0] arrivals, [1] abort word; both zero at launch
+    int32_t* status;
+};
+
+struct RowRegs {
+    uint4 w[MK_MAXSTEPS][4];
+    uint32_t bc[MK_MAXSTEPS];     // byte r = block-code byte of row r
+};
+
+struct MkSmem {
+    __align__(16) int8_t xq[MK_MAXK];
+    __align__(16) uint4 xn[MK_MAXK / 8];
+    float red[33];
+    double dred[33];
+    float coef[MK_MAXHQ][33];     // per head: weight of each split, [32] = 1 / sum
+    float ml[MK_MAXHQ * 32][2];
+    int ok;
+};
+
+// ---- grid-wide barrier ------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ bool grid_barrier(const MkArgs& a, uint32_t target, int* ok) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        atomicAdd(a.bar, 1u);
+        int good = 1;
+        uint64_t t0 = 0;
+        for (uint32_t it = 0;; ++it) {
+            uint32_t v;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(a.bar) : "memory");
+            if (v >= target) break;
+            if ((it & 255u) == 255u) {
+                uint32_t ab;
+                asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(ab) : "l"(a.bar + 1) : "memory");
+                if (ab) { good = 0; break; }
+                const uint64_t now = globaltimer_ns();
+                if (!t0) t0 = now;
+                else if (now - t0 > MK_WAIT_NS) {
+                    atomicExch(a.bar + 1, 1u);
+                    atomicCAS((int*)a.status, 0, 100 + (int)(target / gridDim.x));   // which barrier gave up
+                    good = 0;
+                    break;
+                }
+            }
+        }
+        *ok = good;
+    }
+    __syncthreads();
+    return *ok != 0;
+}
+
+// ---- activation prologues: bf16 row -> INT8 row in shared memory, returns the scale ------------------------------------------
+__device__ __forceinline__ uint4 ldcg4(const uint4* p) { return __ldcg(p); }
+
+// INT8 of the bf16 row staged in sm.xn (nv vectors of 8), arithmetic of act_quant; amax is this thread's partial maximum.
+__device__ __forceinline__ float quantize_staged(MkSmem& sm, int nv, float amax) {
+    amax = block_max(amax, sm.red);
+    float s, qi;
+    quant_scale(amax, s, qi);
+    for (int v = threadIdx.x; v < nv; v += MK_THREADS) {
+        const uint4 r = sm.xn[v];
+        const uint32_t x[4] = {r.x, r.y, r.z, r.w};
+        float f[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            f[2 * j] = __uint_as_float(x[j] << 16);
+            f[2 * j + 1] = __uint_as_float(x[j] & 0xFFFF0000u);
+        }
+        reinterpret_cast<uint2*>(sm.xq)[v] = make_uint2(quant4(f[0], f[1], f[2], f[3], qi), quant4(f[4], f[5], f[6], f[7], qi));
+    }
+    __syncthreads();
+    return s;
+}
+
+__device__ __forceinline__ float amax8(const uint4& r) {
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+    float m = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) m = fmaxf(m, fmaxf(fabsf(__uint_as_float(w[j] << 16)), fabsf(__uint_as_float(w[j] & 0xFFFF0000u))));
+    return m;
+}
+
+__device__ __forceinline__ float pro_act(MkSmem& sm, const uint16_t* x, int K) {
+    const int nv = K / 8;
+    float amax = 0.0f;
+    for (int v = threadIdx.x; v < nv; v += MK_THREADS) {
+        const uint4 r = ldcg4(reinterpret_cast<const uint4*>(x) + v);
+        sm.xn[v] = r;
+        amax = fmaxf(amax, amax8(r));
+    }
+    return quantize_staged(sm, nv, amax);
+}
+
+__device__ __forceinline__ float pro_norm(MkSmem& sm, const uint16_t* x, const uint16_t* nw, float eps, int K) {
+    const int nv = K / 8;
+    double ss = 0.0;
+    for (int v = threadIdx.x; v < nv; v += MK_THREADS) {
+        const uint4 r = ldcg4(reinterpret_cast<const uint4*>(x) + v);
+        sm.xn[v] = r;
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float f0 = __uint_as_float(w[j] << 16), f1 = __uint_as_float(w[j] & 0xFFFF0000u);
+            ss += (double)f0 * (double)f0 + (double)f1 * (double)f1;
+        }
+    }
+    ss = block_sum(ss, sm.dred);
+    const float inv = rms_inverse(ss, K, eps);
+    float amax = 0.0f;
+    const uint4* nw4 = reinterpret_cast<const uint4*>(nw);
+    for (int v = threadIdx.x; v < nv; v += MK_THREADS) {       // the vectors this thread staged itself
+        const uint4 r = sm.xn[v], wv = nw4[v];
+        const uint32_t x4[4] = {r.x, r.y, r.z, r.w}, w[4] = {wv.x, wv.y, wv.z, wv.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float f0 = rbf(__fmul_rn(__uint_as_float(w[j] << 16), rbf(__fmul_rn(__uint_as_float(x4[j] << 16), inv))));
+            const float f1 = rbf(__fmul_rn(__uint_as_float(w[j] & 0xFFFF0000u), rbf(__fmul_rn(__uint_as_float(x4[j] & 0xFFFF0000u), inv))));
+            amax = fmaxf(amax, fmaxf(fabsf(f0), fabsf(f1)));
+            o[j] = (__float_as_uint(f0) >> 16) | (__float_as_uint(f1) & 0xFFFF0000u);
+        }
+        sm.xn[v] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+    return quantize_staged(sm, nv, amax);
+}
+
+// o = attention output from the partial states of all heads (the arithmetic of attn_combine), then its INT8.
+template <int HD>
+__device__ __forceinline__ float pro_attn(MkSmem& sm, const MkArgs& a, int active) {
+    constexpr int stride = HD + 2;
+    const int tid = threadIdx.x, hq = a.hq;
+    for (int i = tid; i < hq * active; i += MK_THREADS) {
+        const int head = i / active, s = i - head * active;
+        const float* p = a.part + ((size_t)head * a.nsplit + s) * stride;
+        sm.ml[head * 32 + s][0] = __ldcg(p + HD);
+        sm.ml[head * 32 + s][1] = __ldcg(p + HD + 1);
+    }
+    __syncthreads();
+    for (int head = tid; head < hq; head += MK_THREADS) {
+        float mm = -INFINITY;
+        for (int s = 0; s < active; ++s) mm = fmaxf(mm, sm.ml[head * 32 + s][0]);
+        float ll = 0.0f;
+        for (int s = 0; s < active; ++s) {
+            const float ms = sm.ml[head * 32 + s][0];
+            const float c = ms == -INFINITY ? 0.0f : exp2f(ms - mm);
+            ll += sm.ml[head * 32 + s][1] * c;
+            sm.coef[head][s] = c;
+        }
+        sm.coef[head][32] = ll;
+    }
+    __syncthreads();
+    const int n = hq * HD;
+    float amax = 0.0f;
+    uint16_t* stage = reinterpret_cast<uint16_t*>(sm.xn);
+    for (int e = tid; e < n; e += MK_THREADS) {
+        const int head = e / HD, dd = e - head * HD;
+        const float* p = a.part + (size_t)head * a.nsplit * stride + dd;
+        float av = 0.0f;
+        for (int s = 0; s < active; ++s) av += __ldcg(p + s * stride) * sm.coef[head][s];
+        const uint16_t ob = f32_to_bf16(av / sm.coef[head][32]);
+        stage[e] = ob;
+        amax = fmaxf(amax, fabsf(bf16_to_f32(ob)));
+    }
+    __syncthreads();
+    return quantize_staged(sm, n / 8, amax);
+}
+
+// ---- GEMV rows: a warp computes 4 consecutive output rows over the whole K -------------------------------------------------
+__device__ __forceinline__ void load_rows(RowRegs& r, const uint32_t* codes, const uint8_t* bcodes, int K, int steps, int n0,
+                                          int lane) {
+    const int wpr = K / 8, bcr = K / 128;
+#pragma unroll
+    for (int s = 0; s < MK_MAXSTEPS; ++s) {
+        if (s < steps) {
+            const int k0 = (s * 32 + lane) * 32;
+            uint32_t b = 0;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                r.w[s][q] = ldg_stream(reinterpret_cast<const uint4*>(codes + (size_t)(n0 + q) * wpr + k0 / 8));
+                b |= (uint32_t)__ldg(bcodes + (size_t)(n0 + q) * bcr + (k0 >> 7)) << (8 * q);
+            }
+            r.bc[s] = b;
+        }
+    }
+}
+
+__device__ __forceinline__ void compute_rows(const RowRegs& r, const int8_t* xq, int steps, int lane, int (&tot)[4]) {
+    const uint32_t mlo = 0x03020100u, mhi = 0x0C080604u;      // 2 x E2M1 magnitudes 0 1 2 3 | 4 6 8 12
+#pragma unroll
+    for (int q = 0; q < 4; ++q) tot[q] = 0;
+#pragma unroll
+    for (int s = 0; s < MK_MAXSTEPS; ++s) {
+        if (s < steps) {
+            const int k0 = (s * 32 + lane) * 32;
+            const uint4 xa = *reinterpret_cast<const uint4*>(xq + k0);
+            const uint4 xb = *reinterpret_cast<const uint4*>(xq + k0 + 16);
+            const uint32_t x[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+            uint32_t xn[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) xn[j] = neg4(x[j]);
+            const int sh = ((k0 >> 5) & 3) * 2;               // the lane's 32-block inside its block-code byte
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint32_t ww[4] = {r.w[s][q].x, r.w[s][q].y, r.w[s][q].z, r.w[s][q].w};
+                const uint32_t code = (r.bc[s] >> (8 * q + sh)) & 3u;
+                int bs = 0;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t sel = ww[j] & 0x77777777u;
+                    const uint32_t ssel = ((ww[j] >> 1) & 0x44444444u) | 0x32103210u;
+                    bs = dp4a_ss(prmt(x[2 * j], xn[2 * j], ssel), prmt(mlo, mhi, sel), bs);
+                    bs = dp4a_ss(prmt(x[2 * j + 1], xn[2 * j + 1], ssel >> 16), prmt(mlo, mhi, sel >> 16), bs);
+                }
+                tot[q] += bs << code;
+            }
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) tot[q] = warp_sum(tot[q]);
+}
+
+// epi 1: out[n] = T(acc xs ws); 2: out[n] = T(res[n] + T(..)); 3: SwiGLU of rows [g0 g1 u0 u1] -> out[n0/2], out[n0/2 + 1]
+__device__ __forceinline__ void epilogue_rows(const int (&tot)[4], float xs, const float* wscale, int n0, int epi, const uint16_t* res,
+                                              uint16_t* out, int lane) {
+    if (epi == 3) {
+        if (lane < 2) {
+            const float g = scale_acc(tot[lane], xs, __ldg(wscale + n0 + lane));
+            const float u = scale_acc(tot[lane + 2], xs, __ldg(wscale + n0 + lane + 2));
+            out[n0 / 2 + lane] = f32_to_bf16(swiglu_bf16(g, u));
+        }
+        return;
+    }
+    if (lane < 4) {
+        float y = scale_acc(tot[lane], xs, __ldg(wscale + n0 + lane));
+        if (epi == 2) y = __fadd_rn(bf16_to_f32(__ldcg(res + n0 + lane)), y);
+        out[n0 + lane] = f32_to_bf16(y);
+    }
+}
+
+struct GemvJob {
+    const uint32_t* codes;
+    const uint8_t* bcodes;
+    const float* wscale;
+    int N, K, steps;
+};
+
+__device__ __forceinline__ GemvJob make_job(const scmx_decode_layer& L, int which, int N, int K) {
+    GemvJob j;
+    j.codes = L.codes[which];
+    j.bcodes = L.bcodes[which];
+    j.wscale = L.wscale[which];
+    j.N = N;
+    j.K = K;
+    j.steps = K / 1024;
+    return j;
+}
+
+// first row group of this warp: its weight loads go out before the barrier that the activations wait for
+__device__ __forceinline__ void prefetch_job(const GemvJob& j, RowRegs& r, int gw, int lane) {
+    if (gw * 4 < j.N) load_rows(r, j.codes, j.bcodes, j.K, j.steps, gw * 4, lane);
+}
+
+__device__ __forceinline__ void run_job(const GemvJob& j, RowRegs& r, const int8_t* xq, float xs, int epi, const uint16_t* res,
+                                        uint16_t* out, int gw, int nw, int lane) {
+    bool first = true;
+    for (int grp = gw; grp * 4 < j.N; grp += nw) {
+        if (!first) load_rows(r, j.codes, j.bcodes, j.K, j.steps, grp * 4, lane);
+        first = false;
+        int tot[4];
+        compute_rows(r, xq, j.steps, lane, tot);
+        epilogue_rows(tot, xs, j.wscale, grp * 4, epi, res, out, lane);
+    }
+}
+
+// ---- the new token's q (G heads), k, v of one key/value head: RMSNorm, rotary embedding (arithmetic of qkv_norm_kernel) ----
+template <int G, int HD>
+struct QkvSmem {
+    float vals[(G + 2) * HD];
+    float inv[G + 1];
+    float cs[HD / 2], sn[HD / 2];
+    __align__(16) uint16_t q[G * HD];
+    __align__(16) uint16_t k[HD];
+    __align__(16) uint16_t v[HD];
+};
+
+template <int G, int HD>
+__device__ __forceinline__ void qkv_prepare(QkvSmem<G, HD>& qs, const MkArgs& a, const scmx_decode_layer& L, int kvh, int64_t pos) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    constexpr int half = HD / 2, NE = (G + 2) * HD;
+    for (int e = tid; e < NE; e += MK_THREADS) {
+        const int hh = e / HD, dd = e - hh * HD;
+        const int src = hh < G ? (kvh * G + hh) * HD : (hh == G ? (a.hq + kvh) * HD : (a.hq + a.hk + kvh) * HD);
+        qs.vals[e] = bf16_to_f32(__ldcg(a.y + src + dd));
+    }
+    for (int i = tid; i < half; i += MK_THREADS) {
+        if (a.rope_cs != nullptr && pos < a.rope_rows) {
+            qs.cs[i] = a.rope_cs[pos * HD + i];
+            qs.sn[i] = a.rope_cs[pos * HD + half + i];
+        } else {
+            const float ang = __fmul_rn((float)pos, a.inv_freq[i]);
+            double s, c;
+            sincos((double)ang, &s, &c);
+            qs.cs[i] = (float)c;
+            qs.sn[i] = (float)s;
+        }
+    }
+    __syncthreads();
+    for (int hh = warp; hh < G + 1; hh += MK_WARPS) {
+        double ss = 0.0;
+        for (int i = lane; i < HD; i += 32) {
+            const double x = (double)qs.vals[hh * HD + i];
+            ss += x * x;
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) qs.inv[hh] = rms_inverse(ss, HD, a.eps);
+    }
+    __syncthreads();
+    auto normed = [&](int hh, int dd) -> float {
+        const uint16_t* w = hh < G ? L.q_norm : L.k_norm;
+        return rbf(__fmul_rn(bf16_to_f32(w[dd]), rbf(__fmul_rn(qs.vals[hh * HD + dd], qs.inv[hh]))));
+    };
+    for (int e = tid; e < NE; e += MK_THREADS) {
+        const int hh = e / HD, dd = e - hh * HD;
+        if (hh > G) {
+            qs.v[dd] = f32_to_bf16(qs.vals[e]);
+            continue;
+        }
+        const bool lo = dd < half;
+        const float self = normed(hh, dd), other = normed(hh, lo ? dd + half : dd - half);
+        const int i = lo ? dd : dd - half;
+        const float r = lo ? rbf(__fsub_rn(__fmul_rn(self, qs.cs[i]), __fmul_rn(other, qs.sn[i])))
+                           : rbf(__fadd_rn(__fmul_rn(other, qs.sn[i]), __fmul_rn(self, qs.cs[i])));
+        if (hh < G) qs.q[hh * HD + dd] = f32_to_bf16(r);
+        else qs.k[dd] = f32_to_bf16(r);
+    }
+    __syncthreads();
+}
+
+// ---- the kernel ------------------------------------------------------------------------------------------------------------
+template <int G, int HD>
+__global__ void __launch_bounds__(MK_THREADS, 1) decode_step_kernel(const MkArgs a) {
+    __shared__ MkSmem sm;
+    __shared__ QkvSmem<G, HD> qs;
+    __shared__ AttnSmem<G, HD> as;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // row groups are dealt warp-major, so that a job with fewer groups than warps still uses every SM
+    const int gw = warp * gridDim.x + blockIdx.x, nw = gridDim.x * MK_WARPS;
+    const int D = a.D, F = a.F, QD = a.hq * HD, NQKV = (a.hq + 2 * a.hk) * HD;
+    uint32_t target = 0;
+    RowRegs regs;
+
+    int64_t pos = a.pos_dev[0];
+    pos = pos < 0 ? 0 : pos;
+    const bool in_cache = pos < a.cap;
+    int64_t T = in_cache ? pos + 1 : a.cap;
+    int64_t chunk;
+    int active;
+    attn_chunking(T, a.nsplit, chunk, active);
+    constexpr int stride = HD + 2;
+
+#define MK_BARRIER()                                          \
+    do {                                                      \
+        target += gridDim.x;                                  \
+        if (!grid_barrier(a, target, &sm.ok)) return;         \
+    } while (0)
+
+    for (int li = 0; li < a.n_layers; ++li) {
+        const scmx_decode_layer& L = a.layers[li];
+        // P1: input RMSNorm + INT8, q|k|v projection
+        GemvJob job = make_job(L, 0, NQKV, D);
+        prefetch_job(job, regs, gw, lane);
+        if (li > 0) MK_BARRIER();                             // h of the previous layer complete
+        float xs = pro_norm(sm, a.h, L.ln_in, a.eps, D);
+        run_job(job, regs, sm.xq, xs, 1, nullptr, a.y, gw, nw, lane);
+        // P3: attention of one (kv head, split) per CTA
+        MK_BARRIER();
+        {
+            const int kvh = blockIdx.x % a.hk, split = blockIdx.x / a.hk;
+            if (split < active) {                             // uniform over the CTA
+                qkv_prepare<G, HD>(qs, a, L, kvh, pos);
+                uint16_t* kc = L.k_cache + (size_t)kvh * a.cap * HD;
+                uint16_t* vc = L.v_cache + (size_t)kvh * a.cap * HD;
+                if (split == 0 && in_cache && tid < HD / 8) {
+                    reinterpret_cast<uint4*>(kc + pos * HD)[tid] = reinterpret_cast<const uint4*>(qs.k)[tid];
+                    reinterpret_cast<uint4*>(vc + pos * HD)[tid] = reinterpret_cast<const uint4*>(qs.v)[tid];
+                }
+                const int64_t t0 = (int64_t)split * chunk, t1 = t0 + chunk < T ? t0 + chunk : T;
+                attn_split<G, HD>(qs.q, kc, vc, t0, t1, in_cache ? pos : -1, qs.k, qs.v, a.scale,
+                                  a.part + ((size_t)kvh * G * a.nsplit + split) * stride, (size_t)a.nsplit * stride, as);
+            }
+        }
+        // P4: combine the splits, INT8 of o, o-projection + residual
+        job = make_job(L, 1, D, QD);
+        prefetch_job(job, regs, gw, lane);
+        MK_BARRIER();
+        xs = pro_attn<HD>(sm, a, active);
+        run_job(job, regs, sm.xq, xs, 2, a.h, a.h, gw, nw, lane);
+        // P5: post-attention RMSNorm + INT8, gate|up projection with SwiGLU
+        job = make_job(L, 2, 2 * F, D);
+        prefetch_job(job, regs, gw, lane);
+        MK_BARRIER();
+        xs = pro_norm(sm, a.h, L.ln_post, a.eps, D);
+        run_job(job, regs, sm.xq, xs, 3, nullptr, a.act, gw, nw, lane);
+        // P6: INT8 of act, down projection + residual
+        job = make_job(L, 3, D, F);
+        prefetch_job(job, regs, gw, lane);
+        MK_BARRIER();
+        xs = pro_act(sm, a.act, F);
+        run_job(job, regs, sm.xq, xs, 2, a.h, a.h, gw, nw, lane);
+    }
+#undef MK_BARRIER
+}
+
+}  // namespace scmx
+
+using namespace scmx;
+
+extern "C" int scmx_decode_step_dense(const scmx_decode_layer* layers, int n_layers, int D, int F, int hq, int hk, int d, float eps,
+                                      float scale, const float* inv_freq, const float* rope_table, int64_t rope_rows,
+                                      int64_t capacity, const int32_t* pos_dev, uint16_t* h, uint16_t* y, uint16_t* act,
+                                      float* partials, int nsplit, uint32_t* barrier, int32_t* status, void* stream) {
+    SCMX_REQUIRE(layers && pos_dev && h && y && act && partials && barrier && status && inv_freq, SCMX_EINVAL, "decode_step: null buffer");
+    SCMX_REQUIRE(n_layers > 0 && hq > 0 && hk > 0 && hq % hk == 0 && hq <= MK_MAXHQ, SCMX_EINVAL, "decode_step: hq=%d hk=%d", hq, hk);
+    SCMX_REQUIRE(d == 128, SCMX_ELIMIT, "decode_step: head size %d (128)", d);
+    const int G = hq / hk;
+    SCMX_REQUIRE(G == 1 || G == 2 || G == 4, SCMX_ELIMIT, "decode_step: %d query heads per key/value head (1, 2 or 4)", G);
+    SCMX_REQUIRE(D % 1024 == 0 && F % 1024 == 0 && (hq * d) % 1024 == 0 && D <= MK_MAXK && F <= MK_MAXK && hq * d <= MK_MAXK,
+                 SCMX_ELIMIT, "decode_step: widths D=%d F=%d hq*d=%d must be multiples of 1024 up to %d", D, F, hq * d, MK_MAXK);
+    SCMX_REQUIRE(capacity >= 1 && nsplit >= 1 && nsplit <= 32, SCMX_EINVAL, "decode_step: capacity=%lld nsplit=%d", (long long)capacity, nsplit);
+    static int n_sm = 0, coop = 0;
+    if (!n_sm) {
+        int dev = 0;
+        SCMX_CUDA_OK(cudaGetDevice(&dev));
+        SCMX_CUDA_OK(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
+        SCMX_CUDA_OK(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+    }
+    SCMX_REQUIRE(coop, SCMX_EDEVICE, "decode_step: the device does not support cooperative launches");
+    SCMX_REQUIRE(hk * nsplit <= n_sm, SCMX_EINVAL, "decode_step: hk * nsplit = %d exceeds the %d CTAs of the grid", hk * nsplit, n_sm);
+    MkArgs a;
+    a.layers = layers; a.n_layers = n_layers; a.D = D; a.F = F; a.hq = hq; a.hk = hk; a.nsplit = nsplit; a.eps = eps; a.scale = scale;
+    a.inv_freq = inv_freq; a.rope_cs = rope_table; a.rope_rows = rope_table ? rope_rows : 0; a.cap = capacity; a.pos_dev = pos_dev;
+    a.h = h; a.y = y; a.act = act; a.part = partials; a.bar = barrier; a.status = status;
+    cudaStream_t st = (cudaStream_t)stream;
+    SCMX_CUDA_OK(cudaMemsetAsync(barrier, 0, 2 * sizeof(uint32_t), st));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)n_sm);
+    cfg.blockDim = dim3(MK_THREADS);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = G == 1 ? cudaLaunchKernelEx(&cfg, decode_step_kernel<1, 128>, a)
+                  : G == 2 ? cudaLaunchKernelEx(&cfg, decode_step_kernel<2, 128>, a)
+                           : cudaLaunchKernelEx(&cfg, decode_step_kernel<4, 128>, a);
+    SCMX_PDL_OK("decode_step_kernel", e);
+    return SCMX_OK;
+}

@@ -12,6 +12,7 @@
 // the previous kernel, so they overlap its tail; activations, scales and expert ids are read after the wait.
 #include "scmx_common.cuh"
 #include "scmx_ptx.cuh"
+#include "scmx_gemv_core.cuh"
 
 namespace scmx {
 
@@ -28,34 +29,12 @@ struct GemvArgs {
     int sk;            // K splits (warps per row group)
     int rg;            // row groups per CTA
     int bc_row_bytes;
+    const uint16_t* xbf;   // prologue forms: bf16 input row(s) [K] instead of xq / xscale
+    const uint16_t* nw;    // RMSNorm weights (prologue 2)
+    float eps;
     DevFormat f;
 };
 
-__device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-
-// Per-byte two's-complement negation of four INT8 without carries between bytes:
-// -b = ~b + 1; the low seven bits of ~b plus one never overflow the byte, and the top bit is folded in with an XOR.
-__device__ __forceinline__ uint32_t neg4(uint32_t x) {
-    const uint32_t nx = ~x;
-    return ((nx & 0x7F7F7F7Fu) + 0x01010101u) ^ (nx & 0x80808080u);
-}
-
-// prmt.b32 in its default mode: selector nibble bits 0-2 pick one of the eight source bytes (every selector built below
-// has bit 3 of each nibble clear, so no sanitising AND is needed).
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-    uint32_t d;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
-    return d;
-}
-__device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) {
-    int d;
-    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
 // sum over the 8 codes of word w of (+-x) * magnitude: 11 instructions
 __device__ __forceinline__ int word_dot(uint32_t w, uint32_t x0, uint32_t xn0, uint32_t x1, uint32_t xn1, uint32_t mlo, uint32_t mhi,
                                         int acc) {
@@ -75,9 +54,72 @@ __device__ __forceinline__ uint32_t lds8(uint32_t addr) {
     return v;
 }
 
-template <int STEPS, bool B32>
+// PRO 0: INT8 input row and its scale are given.  PRO 1 / 2: the input is a bf16 row; every CTA first computes the
+// per-token INT8 row (PRO 2: of its RMSNorm) in shared memory with the arithmetic of the row kernels (act_quant,
+// rmsnorm_quant), after the weight loads are in flight, so the separate kernel and its launch disappear from the chain.
+// Replaces the PRO 1 / PRO 2 prologues of e2e/sc_decode.py:50-65.
+constexpr int GEMV_PRO_MAXK = 8192;
+
+template <int PRO>
+__device__ __forceinline__ float gemv_prologue(const GemvArgs& a, int slot, int8_t* xq_s, uint4* xn_s, float* red, double* dred) {
+    const int K = a.K, nv = K / 8, nt = blockDim.x;
+    const uint4* xrow = reinterpret_cast<const uint4*>(a.xbf + (size_t)slot * a.xstride * K);
+    float amax = 0.0f;
+    double ss = 0.0;
+    for (int v = threadIdx.x; v < nv; v += nt) {
+        const uint4 r = xrow[v];
+        xn_s[v] = r;
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float f0 = __uint_as_float(w[j] << 16), f1 = __uint_as_float(w[j] & 0xFFFF0000u);
+            if (PRO == 2) ss += (double)f0 * (double)f0 + (double)f1 * (double)f1;
+            else amax = fmaxf(amax, fmaxf(fabsf(f0), fabsf(f1)));
+        }
+    }
+    if (PRO == 2) {
+        ss = block_sum(ss, dred);
+        const float inv = rms_inverse(ss, K, a.eps);
+        const uint4* nw4 = reinterpret_cast<const uint4*>(a.nw);
+        for (int v = threadIdx.x; v < nv; v += nt) {       // the vectors this thread staged itself
+            const uint4 r = xn_s[v], wv = nw4[v];
+            const uint32_t x[4] = {r.x, r.y, r.z, r.w}, w[4] = {wv.x, wv.y, wv.z, wv.w};
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float f0 = rbf(__fmul_rn(__uint_as_float(w[j] << 16), rbf(__fmul_rn(__uint_as_float(x[j] << 16), inv))));
+                const float f1 = rbf(__fmul_rn(__uint_as_float(w[j] & 0xFFFF0000u), rbf(__fmul_rn(__uint_as_float(x[j] & 0xFFFF0000u), inv))));
+                amax = fmaxf(amax, fmaxf(fabsf(f0), fabsf(f1)));
+                o[j] = (__float_as_uint(f0) >> 16) | (__float_as_uint(f1) & 0xFFFF0000u);
+            }
+            xn_s[v] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+    amax = block_max(amax, red);
+    float s, qi;
+    quant_scale(amax, s, qi);
+    for (int v = threadIdx.x; v < nv; v += nt) {
+        const uint4 r = xn_s[v];
+        const uint32_t x[4] = {r.x, r.y, r.z, r.w};
+        float f[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            f[2 * j] = __uint_as_float(x[j] << 16);
+            f[2 * j + 1] = __uint_as_float(x[j] & 0xFFFF0000u);
+        }
+        reinterpret_cast<uint2*>(xq_s)[v] = make_uint2(quant4(f[0], f[1], f[2], f[3], qi), quant4(f[4], f[5], f[6], f[7], qi));
+    }
+    __syncthreads();
+    return s;
+}
+
+template <int STEPS, bool B32, int PRO>
 __global__ void __launch_bounds__(256) gemv_kernel(const GemvArgs a) {
     __shared__ int part[8 * 4];
+    __shared__ __align__(16) int8_t xq_s[PRO ? GEMV_PRO_MAXK : 16];
+    __shared__ __align__(16) uint4 xn_s[PRO ? GEMV_PRO_MAXK / 8 : 1];
+    __shared__ float red[33];
+    __shared__ double dred[33];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int ks = wid % a.sk, rgi = wid / a.sk;
     const int n0 = (blockIdx.x * a.rg + rgi) * 4;
@@ -123,7 +165,9 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvArgs a) {
     }
     if (!a.eidx) asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    const int8_t* xq = a.xq + (size_t)slot * a.xstride * K;
+    float xs_pro = 0.0f;
+    if (PRO) xs_pro = gemv_prologue<PRO>(a, slot, xq_s, xn_s, red, dred);
+    const int8_t* xq = PRO ? xq_s : a.xq + (size_t)slot * a.xstride * K;
     int tot[4] = {0, 0, 0, 0};
 #pragma unroll
     for (int s = 0; s < STEPS; ++s) {
@@ -187,7 +231,7 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvArgs a) {
         for (int r = 0; r < 4; ++r) o[r] = tot[r];
         return;
     }
-    const float xs = a.xscale[(size_t)slot * a.xstride];
+    const float xs = PRO ? xs_pro : a.xscale[(size_t)slot * a.xstride];
     float y[4];
 #pragma unroll
     for (int r = 0; r < 4; ++r) y[r] = scale_acc(tot[r], xs, ws[r]);
@@ -445,7 +489,11 @@ static cudaError_t launch_gemv(const GemvArgs& a, dim3 grid, int threads, int pd
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, gemv_kernel<STEPS, B32>, a);
+    if (a.xbf != nullptr) {
+        if (a.nw != nullptr) return cudaLaunchKernelEx(&cfg, gemv_kernel<STEPS, B32, 2>, a);
+        return cudaLaunchKernelEx(&cfg, gemv_kernel<STEPS, B32, 1>, a);
+    }
+    return cudaLaunchKernelEx(&cfg, gemv_kernel<STEPS, B32, 0>, a);
 }
 
 }  // namespace scmx
@@ -458,12 +506,22 @@ extern "C" int scmx_set_gemv_stream(int enable) {
     return SCMX_OK;
 }
 
-extern "C" int scmx_gemv(const int8_t* xq, const float* xscale, const uint32_t* codes, const uint8_t* bcodes,
-                         const float* wscale, int64_t N, int64_t K, const scmx_format* fmt, int epi, const uint16_t* res,
-                         const int32_t* eidx, int n_routed, int shared, int xstride, void* out, int pdl, void* stream) {
+static int gemv_impl(const int8_t* xq, const float* xscale, const uint16_t* xbf, const uint16_t* nw, float eps, const uint32_t* codes,
+                     const uint8_t* bcodes, const float* wscale, int64_t N, int64_t K, const scmx_format* fmt, int epi,
+                     const uint16_t* res, const int32_t* eidx, int n_routed, int shared, int xstride, void* out, int pdl,
+                     void* stream) {
     GemvArgs a;
     int rc = make_dev_format(fmt, &a.f);
     if (rc) return rc;
+    a.xbf = xbf; a.nw = nw; a.eps = eps;
+    if (xbf != nullptr) {
+        SCMX_REQUIRE(K <= GEMV_PRO_MAXK, SCMX_ELIMIT, "gemv_pro: K=%lld above %d", (long long)K, GEMV_PRO_MAXK);
+        SCMX_REQUIRE((reinterpret_cast<uintptr_t>(xbf) & 15) == 0 && (reinterpret_cast<uintptr_t>(nw) & 15) == 0, SCMX_EINVAL,
+                     "gemv_pro: x and nw must be 16-byte aligned");
+        xq = reinterpret_cast<const int8_t*>(xbf);          // stands in for the checks below; never read
+        static const float one = 1.0f;
+        if (xscale == nullptr) xscale = &one;                 // likewise
+    }
     SCMX_REQUIRE(K > 0 && K % 128 == 0 && K <= (1 << 20), SCMX_EINVAL, "gemv: K=%lld must be a multiple of 128", (long long)K);
     SCMX_REQUIRE(N > 0 && N % 4 == 0 && N < (1ll << 30), SCMX_EINVAL, "gemv: N=%lld must be a multiple of 4", (long long)N);
     SCMX_REQUIRE(epi >= 0 && epi <= 3, SCMX_EINVAL, "gemv: epi=%d outside 0..3", epi);
@@ -486,7 +544,7 @@ extern "C" int scmx_gemv(const int8_t* xq, const float* xscale, const uint32_t* 
     a.bc_row_bytes = (int)(K / (a.f.block * a.f.blocks_per_byte));
     // ---- streaming kernel for dense GEMVs whose tiles satisfy the bulk-copy alignment rules
     // (matrices under 16 MB finish within a few microseconds either way and start faster with the register kernel below)
-    if (!eidx && (g_gemv_stream == 2 || g_gemv_stream == 3 || N * K / 2 >= (16ll << 20)) && K <= SG_X_BYTES && K % 32 == 0 && (a.bc_row_bytes % 4) == 0 && (reinterpret_cast<uintptr_t>(bcodes) & 15) == 0 &&
+    if (!eidx && xbf == nullptr && (g_gemv_stream == 2 || g_gemv_stream == 3 || N * K / 2 >= (16ll << 20)) && K <= SG_X_BYTES && K % 32 == 0 && (a.bc_row_bytes % 4) == 0 && (reinterpret_cast<uintptr_t>(bcodes) & 15) == 0 &&
         g_gemv_stream) {
         int tr = 64;
         while (tr > 4 && ((int64_t)tr * (K / 2) > SG_STAGE_BYTES || (N + tr - 1) / tr < 96)) tr >>= 1;
@@ -552,4 +610,22 @@ extern "C" int scmx_gemv(const int8_t* xq, const float* xscale, const uint32_t* 
         return SCMX_ECUDA;
     }
     return SCMX_OK;
+}
+
+extern "C" int scmx_gemv(const int8_t* xq, const float* xscale, const uint32_t* codes, const uint8_t* bcodes,
+                         const float* wscale, int64_t N, int64_t K, const scmx_format* fmt, int epi, const uint16_t* res,
+                         const int32_t* eidx, int n_routed, int shared, int xstride, void* out, int pdl, void* stream) {
+    SCMX_REQUIRE(xq != nullptr, SCMX_EINVAL, "gemv: xq is NULL");
+    return gemv_impl(xq, xscale, nullptr, nullptr, 0.0f, codes, bcodes, wscale, N, K, fmt, epi, res, eidx, n_routed, shared, xstride,
+                     out, pdl, stream);
+}
+
+extern "C" int scmx_gemv_pro(const uint16_t* x, int pro, const uint16_t* nw, float eps, const uint32_t* codes,
+                             const uint8_t* bcodes, const float* wscale, int64_t N, int64_t K, const scmx_format* fmt, int epi,
+                             const uint16_t* res, const int32_t* eidx, int n_routed, int shared, int xstride, void* out, int pdl,
+                             void* stream) {
+    SCMX_REQUIRE(x != nullptr && (pro == 1 || (pro == 2 && nw != nullptr)), SCMX_EINVAL, "gemv_pro: pro=%d (1, or 2 with nw)", pro);
+    SCMX_REQUIRE(epi != 0, SCMX_EINVAL, "gemv_pro: epi 0 has no scale to report; use the row kernel and scmx_gemv");
+    return gemv_impl(nullptr, nullptr, x, pro == 2 ? nw : nullptr, eps, codes, bcodes, wscale, N, K, fmt, epi, res, eidx, n_routed,
+                     shared, xstride, out, pdl, stream);
 }

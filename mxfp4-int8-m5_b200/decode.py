@@ -9,9 +9,18 @@ by mx.compile'ing the halves of a step (e2e/decode.py:31-33).
 
 fuse_prologue selects where the per-token INT8 of a GEMV input is computed in the reference (inside the GEMV or in a row
 kernel); here both forms run the row kernel followed by the GEMV and give the same values, so the argument only keeps the
-signature."""
+signature.
+
+persistent=True (DecodeQwen3) runs all layers of a step as ONE cooperative kernel (scmx_decode_step_dense): the phases of a
+layer are separated by grid-wide barriers instead of kernel boundaries, each CTA re-quantizes the activations it needs in
+shared memory, and weight loads are issued ahead of the barriers.  Same bits as the chain of kernels; used where its limits
+hold (head size 128, widths multiples of 1024 up to 6144) and attention="kernel"."""
+import ctypes
+
+import numpy as np
 import torch
 
+from . import _lib
 from . import sc_decode as G
 from . import sc_kernels as S
 from . import sc_moe as M_
@@ -33,6 +42,7 @@ class _Decoder:
         self.attention = attention
         self.attn = S.DecodeAttention(hq, hk, d, fused.inv_freq.device) if attention == "kernel" else None
         self._graph = None
+        self._mk = None                                       # persistent-kernel state, built per cache
 
     def _attend(self, at, c, q, k, v, pos_dev):
         if self.attn is not None:
@@ -92,27 +102,80 @@ class _Decoder:
 class DecodeQwen3(_Decoder):
     """Built from a FusedQwen3 with epilogue="gemm" (gate/up rows interleaved for the SwiGLU epilogue)."""
 
-    def __init__(self, fused, head="model", compiled=True, fuse_prologue=None, act_tile=None, attention="kernel"):
+    def __init__(self, fused, head="model", compiled=True, fuse_prologue=None, act_tile=None, attention="kernel",
+                 persistent=True):
         assert fused.epilogue == "gemm"
         super().__init__(fused, head, attention)
+        a = self.args
+        fits = lambda n: n % 1024 == 0 and n <= 6144  # noqa: E731
+        self.persistent = bool(persistent and self.attn is not None and a.head_dim == 128 and fits(a.hidden_size)
+                               and fits(a.intermediate_size) and fits(a.num_attention_heads * a.head_dim)
+                               and a.num_attention_heads <= 32 and fused.fmt == type(fused.fmt)())
+
+    def _persistent_state(self, cache):
+        """Layer table (device pointers of the packed weights, norms and this cache's tensors) and scratch buffers."""
+        if self._mk is not None and self._mk["cache"] is cache:
+            return self._mk
+        f, a = self.f, self.args
+        dev = f.inv_freq.device
+        table = (_lib.ScmxDecodeLayer * len(f.layers))()
+        for i, (layer, ws) in enumerate(f.layers):
+            t, at, c = table[i], layer.self_attn, cache[i]
+            for j, g in enumerate(("qkv", "o", "gu", "down")):
+                t.codes[j], t.bcodes[j], t.wscale[j] = ws[g].codes.data_ptr(), ws[g].bcodes.data_ptr(), ws[g].wscale.data_ptr()
+            t.ln_in, t.ln_post = layer.input_layernorm.weight.data_ptr(), layer.post_attention_layernorm.weight.data_ptr()
+            t.q_norm, t.k_norm = at.q_norm.weight.data_ptr(), at.k_norm.weight.data_ptr()
+            t.k_cache, t.v_cache = c.k.data_ptr(), c.v.data_ptr()
+        raw = np.frombuffer(ctypes.string_at(ctypes.addressof(table), ctypes.sizeof(table)), dtype=np.uint8).copy()
+        hq, hk, d = a.num_attention_heads, a.num_key_value_heads, a.head_dim
+        self._mk = dict(cache=cache, table=torch.from_numpy(raw).to(dev),
+                        y=torch.empty((hq + 2 * hk) * d, dtype=torch.bfloat16, device=dev),
+                        act=torch.empty(a.intermediate_size, dtype=torch.bfloat16, device=dev),
+                        bar=torch.zeros(2, dtype=torch.int32, device=dev),
+                        status=torch.zeros(1, dtype=torch.int32, device=dev),
+                        pos=torch.zeros(1, dtype=torch.int32, device=dev))
+        return self._mk
+
+    def check_status(self):
+        """Raises if a barrier of the persistent kernel timed out (synchronizes)."""
+        if self._mk is not None:
+            st = int(self._mk["status"].item())
+            if st:
+                raise _lib.ScmxError(f"persistent decode kernel gave up at barrier {st - 100}")
+
+    def _step_persistent(self, tok, cache, pos_dev):
+        f, a = self.f, self.args
+        mk = self._persistent_state(cache)
+        if pos_dev is None:
+            pos_dev = mk["pos"]
+            pos_dev.fill_(cache[0].offset)
+        hq, hk, d = a.num_attention_heads, a.num_key_value_heads, a.head_dim
+        h = self.model.model.embed_tokens(tok)[0].clone()     # [1, D]; the kernel updates it in place
+        _lib.call("scmx_decode_step_dense", _lib.ptr(mk["table"]), len(f.layers), a.hidden_size, a.intermediate_size, hq, hk, d,
+                  float(f.eps), float(f.layers[0][0].self_attn.scale), _lib.ptr(f.inv_freq), _lib.ptr(f.rope_cs),
+                  f.rope_cs.shape[0], cache[0].k.shape[1], _lib.ptr(pos_dev), _lib.ptr(h), _lib.ptr(mk["y"]), _lib.ptr(mk["act"]),
+                  _lib.ptr(self.attn.part), self.attn.nsplit, _lib.ptr(mk["bar"]), _lib.ptr(mk["status"]), _lib.stream())
+        xn = S.rmsnorm_quant_n(h, self.model.model.norm.weight, f.eps, 1)[2]
+        return self.head(xn[None])
 
     def _step(self, tok, cache, pos_dev):
         f, a = self.f, self.args
         S.set_format(f.fmt)
+        if self.persistent:
+            return self._step_persistent(tok, cache, pos_dev)
         hq, hk, d, eps = a.num_attention_heads, a.num_key_value_heads, a.head_dim, f.eps
         h = self.model.model.embed_tokens(tok)[0]             # [1, D]
         for i, (layer, ws) in enumerate(f.layers):
             at, c = layer.self_attn, cache[i]
             w = ws["qkv"]
-            xq, xs = S.rmsnorm_quant(h, layer.input_layernorm.weight, eps, 1)
-            y = G.gemv(xq, w.codes, w.bcodes, xs, w.wscale, w.N, 1)
+            y = G.gemv(h, w.codes, w.bcodes, None, w.wscale, w.N, 1, pro=2, nw=layer.input_layernorm.weight, eps=eps)
             q, k, v = S.qkv_headnorm_y(y[None], at.q_norm.weight, at.k_norm.weight, eps, 1, hq, hk, d,
                                        rope=(f.inv_freq, c.offset, f.rope_cs), cache=c, pos_dev=pos_dev)
             o = self._attend(at, c, q, k, v, pos_dev)
             wo, wg, wd = ws["o"], ws["gu"], ws["down"]
             h = G.gemv(o, wo.codes, wo.bcodes, None, wo.wscale, wo.N, 2, res=h, pro=1)[None]
-            xq, xs = S.rmsnorm_quant(h, layer.post_attention_layernorm.weight, eps, 1)
-            act = G.gemv(xq, wg.codes, wg.bcodes, xs, wg.wscale, wg.N, 3)
+            act = G.gemv(h, wg.codes, wg.bcodes, None, wg.wscale, wg.N, 3, pro=2, nw=layer.post_attention_layernorm.weight,
+                         eps=eps)
             h = G.gemv(act[None], wd.codes, wd.bcodes, None, wd.wscale, wd.N, 2, res=h, pro=1)[None]
         xn = S.rmsnorm_quant_n(h, self.model.model.norm.weight, eps, 1)[2]
         return self.head(xn[None])
@@ -134,8 +197,7 @@ class DecodeOlmoe(_Decoder):
         for i, (layer, ws, ex) in enumerate(f.layers):
             at, c = layer.self_attn, cache[i]
             w, wo = ws["qkv"], ws["o"]
-            xq, xs = S.rmsnorm_quant(h, layer.input_layernorm.weight, eps, 1)
-            y = G.gemv(xq, w.codes, w.bcodes, xs, w.wscale, 3 * H * d, 1)
+            y = G.gemv(h, w.codes, w.bcodes, None, w.wscale, 3 * H * d, 1, pro=2, nw=layer.input_layernorm.weight, eps=eps)
             q, kk, v = S.qkv_fullnorm_y(y[None], at.q_norm.weight, at.k_norm.weight, eps, 1, H, d,
                                         rope=(f.inv_freq, c.offset, f.rope_cs), cache=c, pos_dev=pos_dev)
             o = self._attend(at, c, q, kk, v, pos_dev)
@@ -146,8 +208,7 @@ class DecodeOlmoe(_Decoder):
             e = inds.reshape(-1)
             (cg, bg, sg), (cd, bd, sd) = ex["gu"], ex["down"]
             act = G.gemv(xq, cg, bg, xs, sg, F2, 3, eidx=e, xstride=0)            # [k, F]
-            xq2, xs2 = S.act_quant(act, k)
-            yd = G.gemv(xq2, cd, bd, xs2, sd, D, 1, eidx=e, xstride=1)            # [k, D]
+            yd = G.gemv(act, cd, bd, None, sd, D, 1, eidx=e, xstride=1, pro=1)    # [k, D], per-row INT8 in the prologue
             h = M_.moe_combine(yd, self.pos, scores, h, pn, eps, 1, quant=False)[0]
         xn = S.rmsnorm_quant_n(h, self.model.model.norm.weight, eps, 1)[2]
         return self.head(xn[None])

@@ -1,7 +1,8 @@
 """Batch-1 decode GEMV that reads the packed SC-MXFP4 weights directly, with the call signature of the reference's
 e2e/sc_decode.py `gemv`.  The kernel accumulates exact INT32 totals (DP4A) and applies the GEMM's epilogues, so
 decode and prefill produce the same bits.  Prologues pro=1 / pro=2 (activation quantization / RMSNorm + quantization
-of a bf16 input row) run as the separate row kernel followed by the GEMV, which computes the same values."""
+of a bf16 input row) run inside the GEMV kernel (scmx_gemv_pro) when K <= 8192 and the matrix is small enough for
+the register kernel; otherwise as the separate row kernel followed by the GEMV.  Both give the same bits."""
 import torch
 
 from . import _lib
@@ -9,6 +10,7 @@ from . import sc_format as F
 from . import sc_kernels as S
 
 USE_PDL = True   # programmatic dependent launch: weight loads overlap the previous kernel's tail
+FUSE_PROLOGUE = (1, 2)   # which prologues run inside the GEMV kernel where it applies; () = always the separate row kernel
 
 
 def gemv(xq, codes, bcodes, xscale, wscale, N, epi, dtype=torch.bfloat16, res=None, nsg=None, eidx=None, xstride=0,
@@ -19,9 +21,16 @@ def gemv(xq, codes, bcodes, xscale, wscale, N, epi, dtype=torch.bfloat16, res=No
     MoE (eidx int32 [S] given): codes [E, ...], bcodes [E, N, ...], wscale [E, N]; output row j uses expert eidx[j] and
     input row j if xstride = 1 (else the single input row) -> [S, N or N/2].  shared = e: one more slot uses expert e.
     nsg / rows / vpl / splitk are Metal tile hints: accepted and ignored."""
+    xbf = None
     if pro:
         x2 = xq.reshape(-1, xq.shape[-1])
-        xq, xscale = (S.act_quant(x2, x2.shape[0]) if pro == 1 else S.rmsnorm_quant(x2, nw, eps, x2.shape[0]))
+        Kp = x2.shape[-1]
+        fused = (pro in (FUSE_PROLOGUE if isinstance(FUSE_PROLOGUE, tuple) else ((1, 2) if FUSE_PROLOGUE else ())) and epi != 0 and Kp <= 8192 and x2.dtype == torch.bfloat16 and x2.is_contiguous()
+                 and (eidx is not None or N * Kp // 2 < (16 << 20)))
+        if fused:
+            xbf = x2
+        else:
+            xq, xscale = (S.act_quant(x2, x2.shape[0]) if pro == 1 else S.rmsnorm_quant(x2, nw, eps, x2.shape[0]))
     _lib.require_cuda(xq, codes, bcodes, xscale, wscale, res, eidx)
     K = xq.shape[-1]
     nslot = 0 if eidx is None else eidx.numel()
@@ -32,7 +41,14 @@ def gemv(xq, codes, bcodes, xscale, wscale, N, epi, dtype=torch.bfloat16, res=No
     out = torch.empty(S_ * no, dtype=torch.int32 if epi == 0 else torch.bfloat16, device=xq.device)
     if eidx is not None:
         eidx = eidx.to(torch.int32)
-    _lib.call("scmx_gemv", _lib.ptr(xq), _lib.ptr(xscale), _lib.ptr(codes), _lib.ptr(bcodes), _lib.ptr(wscale), N, K,
-              F.DEFAULT.c_struct(), epi, _lib.ptr(res) if epi == 2 else None, _lib.ptr(eidx), nslot,
-              -1 if shared is None else int(shared), xstride, _lib.ptr(out), int(USE_PDL), _lib.stream())
+    if xbf is not None:
+        _lib.require_cuda(nw)
+        _lib.call("scmx_gemv_pro", _lib.ptr(xbf), pro, _lib.ptr(nw) if pro == 2 else None, S._eps(eps) if pro == 2 else 0.0,
+                  _lib.ptr(codes), _lib.ptr(bcodes), _lib.ptr(wscale), N, K, F.DEFAULT.c_struct(), epi,
+                  _lib.ptr(res) if epi == 2 else None, _lib.ptr(eidx), nslot, -1 if shared is None else int(shared), xstride,
+                  _lib.ptr(out), int(USE_PDL), _lib.stream())
+    else:
+        _lib.call("scmx_gemv", _lib.ptr(xq), _lib.ptr(xscale), _lib.ptr(codes), _lib.ptr(bcodes), _lib.ptr(wscale), N, K,
+                  F.DEFAULT.c_struct(), epi, _lib.ptr(res) if epi == 2 else None, _lib.ptr(eidx), nslot,
+                  -1 if shared is None else int(shared), xstride, _lib.ptr(out), int(USE_PDL), _lib.stream())
     return out if eidx is None else out.reshape(S_, no)

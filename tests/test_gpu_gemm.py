@@ -357,3 +357,42 @@ def test_other_formats_gemv_and_grouped_gemm(scmx, oracle, kw):
         assert np.array_equal(acc.cpu().numpy(), oracle.gemm_i32(xq, q))
     finally:
         S.set_format(F.Format())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("K", [2048, 6144])
+def test_gemv_fused_prologue_equals_row_kernel_then_gemv(scmx, oracle, K):
+    """The in-kernel prologues (scmx_gemv_pro) against the separate row kernels, bit for bit, for every epilogue and for
+    per-slot input rows of the expert form."""
+    G, S, F = scmx.sc_decode, scmx.sc_kernels, scmx.sc_format
+    rng = np.random.default_rng(K)
+    N = 1024
+    oc, ob, ows, _ = oracle.quantize(rng.standard_normal((N, K)) * 0.02)
+    c, b, s = F.to_device(oc, ob, ows)
+    x = to_bf16_cuda(oracle.bf16_round((rng.standard_normal((1, K)) * rng.lognormal(0, 1, K)).astype(np.float32)))
+    nw = to_bf16_cuda(oracle.bf16_round(rng.lognormal(0, 0.3, K).astype(np.float32)))
+    res = to_bf16_cuda(oracle.bf16_round(rng.standard_normal(N).astype(np.float32)))
+    for pro in (1, 2):
+        for epi in (1, 2, 3):
+            outs = []
+            for fuse in (True, False):
+                G.FUSE_PROLOGUE = fuse
+                outs.append(G.gemv(x, c, b, None, s, N, epi, res=res if epi == 2 else None, pro=pro, nw=nw, eps=1e-6))
+            G.FUSE_PROLOGUE = True
+            assert torch.equal(outs[0], outs[1]), (pro, epi)
+    # zero row: scale 0, all-zero codes, output exactly the residual
+    z = torch.zeros_like(x)
+    y = G.gemv(z, c, b, None, s, N, 2, res=res, pro=1)
+    assert torch.equal(y, res)
+    # expert form with one input row per slot
+    E, Ne = 4, 256
+    packs = [oracle.quantize(rng.standard_normal((Ne, K)) * 0.02) for _ in range(E)]
+    cE, bE, sE = (torch.stack([F.to_device(*p[:3])[i] for p in packs]) for i in range(3))
+    xr = to_bf16_cuda(oracle.bf16_round(rng.standard_normal((3, K)).astype(np.float32) * 2))
+    e = cuda(np.array([3, 0, 2], np.int32))
+    outs = []
+    for fuse in (True, False):
+        G.FUSE_PROLOGUE = fuse
+        outs.append(G.gemv(xr, cE, bE, None, sE, Ne, 1, eidx=e, xstride=1, pro=1))
+    G.FUSE_PROLOGUE = True
+    assert torch.equal(outs[0], outs[1])

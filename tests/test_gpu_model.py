@@ -286,3 +286,39 @@ def test_graph_generate_equals_eager_steps(scmx, kind):
     c2, _ = prompt()
     l1, l2 = dec.step(t1, c1), dec_t.step(t1, c2)
     assert H.rel_l2(H.bf16_np(l1[0, 0]), H.bf16_np(l2[0, 0])) < 8e-2
+
+
+def test_persistent_decode_kernel_equals_kernel_chain(scmx):
+    """All layers of a step in one cooperative kernel against the chain of stand-alone kernels: same logits, bit for bit,
+    same cache contents, eagerly and replayed from a CUDA graph."""
+    HM, FQ, DEC = _mod("host_model"), _mod("fused_qwen3"), _mod("decode")
+    a = HM.ModelArgs(1024, 3072, 2, 8, 4, 128, 1e-6, 1e6, 512, True)
+    model = HM.CausalLM(a).init_random(seed=21, scale=0.05).cuda()
+    fused = FQ.FusedQwen3(model, FQ.pack_model(model, on_device=True))
+    chain = DEC.DecodeQwen3(fused, persistent=False)
+    mk = DEC.DecodeQwen3(fused, persistent=True)
+    assert mk.persistent and not chain.persistent
+    ids = _ids(150, a.vocab_size, 22)
+    n = 6
+
+    def prompt(L):
+        cache = fused.make_cache(256)
+        return cache, fused(ids[:, :L], cache)[:, -1].argmax(-1, keepdim=True)
+
+    for L in (5, 70, 150):                                # 1, 2 and 3 attention splits in use
+        c1, t1 = prompt(L)
+        c2, t2 = prompt(L)
+        for _ in range(n):
+            l1, l2 = chain.step(t1, c1), mk.step(t2, c2)
+            assert torch.equal(l1, l2)
+            t1 = l1[:, -1].argmax(-1, keepdim=True)
+            t2 = l2[:, -1].argmax(-1, keepdim=True)
+        mk.check_status()
+        for x, y in zip(c1, c2):
+            assert x.offset == y.offset == L + n
+            assert torch.equal(x.k[:, :L + n], y.k[:, :L + n]) and torch.equal(x.v[:, :L + n], y.v[:, :L + n])
+    c1, t1 = prompt(40)
+    c2, t2 = prompt(40)
+    assert chain.generate(t1, c1, n).tolist() == mk.generate(t2, c2, n).tolist()
+    mk.check_status()
+    assert torch.equal(c1[1].k[:, :40 + n], c2[1].k[:, :40 + n])
