@@ -269,14 +269,20 @@ typedef struct scmx_decode_layer {
  * gate|up GEMV with SwiGLU -> INT8 -> down GEMV + residual, the chain of e2e/decode.py:58-110, with grid-wide barriers
  * between the steps instead of kernel boundaries.  Same bits as scmx_rmsnorm_quant / scmx_gemv / scmx_qkv_norm /
  * scmx_attn_decode (with the same nsplit) / scmx_act_quant called in that order.
- * layers: device array; y bf16 [(hq + 2 hk) d], act bf16 [F], partials f32 [hq, nsplit, d + 2], barrier uint32 [2] are
- * scratch; status int32 [1] receives 100 + k if barrier k timed out (0.5 s), after which the step's outputs are invalid.
+ * layers: device array; y bf16 [(hq + 2 hk) d], act bf16 [F], o bf16 [hq d], partials f32 [hq, nsplit, d + 2], barrier
+ * uint32 [2] are scratch; counters int32 [hk] must be zero before the first call and is left zero; status int32 [1] receives 100 + k if barrier k timed out (0.5 s), after which the step's outputs are invalid.
  * Limits: d = 128; D, F and hq*d multiples of 1024 up to 6144; hq/hk in {1, 2, 4}; hk * nsplit <= number of SMs.
  * Not to be run concurrently with other work on the same device: the launch needs every SM. */
 int scmx_decode_step_dense(const scmx_decode_layer* layers, int n_layers, int D, int F, int hq, int hk, int d, float eps,
                            float scale, const float* inv_freq, const float* rope_table, int64_t rope_rows, int64_t capacity,
-                           const int32_t* pos_dev, uint16_t* h, uint16_t* y, uint16_t* act, float* partials, int nsplit,
-                           uint32_t* barrier, int32_t* status, void* stream);
+                           const int32_t* pos_dev, uint16_t* h, uint16_t* y, uint16_t* act, uint16_t* o, float* partials,
+                           int nsplit, int32_t* counters, uint32_t* barrier, int32_t* status, void* stream);
+/* Diagnostic: while device_buf is set, CTA 0 of scmx_decode_step_dense stores its SM cycle counter in device_buf[0 .. n)
+ * at every phase boundary (barrier entry / exit, end of each activation prologue), layer after layer; with
+ * n_and_barrier = n | (b << 16), b > 0, every CTA also stores the global nanosecond timer at its arrival at barrier b
+ * (1-based) in device_buf[n + CTA index].  device_buf: uint64 [n + number of SMs].  0 switches it off.  Process-wide; no
+ * counterpart in the reference. */
+int scmx_set_decode_trace(unsigned long long* device_buf, int n_and_barrier);
 
 #ifdef __cplusplus
 }

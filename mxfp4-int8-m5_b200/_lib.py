@@ -71,7 +71,8 @@ SIGNATURES = {
     "scmx_moe_combine": [c_vp, c_vp, c_vp, c_vp, c_vp, c_float, c_i64, c_i64, c_i64, c_int, c_int, c_vp, c_vp, c_vp,
                          c_vp],
     "scmx_decode_step_dense": [c_vp, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_vp, c_vp, c_i64, c_i64, c_vp,
-                               c_vp, c_vp, c_vp, c_vp, c_int, c_vp, c_vp, c_vp],
+                               c_vp, c_vp, c_vp, c_vp, c_vp, c_int, c_vp, c_vp, c_vp, c_vp],
+    "scmx_set_decode_trace": [c_vp, c_int],
     "scmx_gemv_pro": [c_vp, c_int, c_vp, c_float, c_vp, c_vp, c_vp, c_i64, c_i64, _FMT_P, c_int, c_vp, c_vp, c_int, c_int, c_int,
                       c_vp, c_int, c_vp],
     "scmx_gemv": [c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, _FMT_P, c_int, c_vp, c_vp, c_int, c_int, c_int, c_vp,

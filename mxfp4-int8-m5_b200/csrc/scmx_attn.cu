@@ -43,10 +43,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const AttnArgs 
     if (s_ticket != active - 1) return;
     __threadfence();
     // the last CTA of this kv head combines the splits
-    for (int g = 0; g < G; ++g) {
-        const float* p = a.part + (size_t)(kvh * G + g) * a.nsplit * stride;
-        if (tid < D) a.out[(size_t)(kvh * G + g) * D + tid] = f32_to_bf16(attn_combine<D>(p, active, tid));
-    }
+    attn_combine_cta<G, D>(a.part + (size_t)kvh * G * a.nsplit * stride, a.nsplit, active, a.out + (size_t)kvh * G * D, sm);
     if (tid == 0) a.counters[kvh] = 0;
 }
 
@@ -69,7 +66,7 @@ extern "C" int scmx_attn_decode(const uint16_t* q, const uint16_t* k_cache, cons
     SCMX_REQUIRE(hq > 0 && hk > 0 && hq % hk == 0, SCMX_EINVAL, "attn_decode: hq=%d hk=%d", hq, hk);
     const int G = hq / hk;
     SCMX_REQUIRE(G == 1 || G == 2 || G == 4, SCMX_ELIMIT, "attn_decode: %d query heads per key/value head (1, 2 or 4)", G);
-    SCMX_REQUIRE(nsplit >= 1 && nsplit <= 64, SCMX_EINVAL, "attn_decode: nsplit=%d", nsplit);
+    SCMX_REQUIRE(nsplit >= 1 && nsplit <= 32, SCMX_EINVAL, "attn_decode: nsplit=%d (1..32)", nsplit);
     SCMX_REQUIRE(capacity >= 1 && (pos_dev != nullptr || (n_pos >= 1 && n_pos <= capacity)), SCMX_EINVAL,
                  "attn_decode: %lld positions in a cache of %lld", (long long)n_pos, (long long)capacity);
     SCMX_REQUIRE(((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0, SCMX_EINVAL, "attn_decode: cache not 16-byte aligned");

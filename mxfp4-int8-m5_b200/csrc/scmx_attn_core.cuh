@@ -7,13 +7,15 @@
 namespace scmx {
 
 constexpr int AD_THREADS = 128;        // 4 warps x 4 position slots x 8 lanes per position
-constexpr int AD_MIN_CHUNK = 64;       // positions per split at least: short sequences use the first few splits only
+constexpr int AD_MIN_CHUNK = 32;       // positions per split at least: short sequences use the first few splits only
 constexpr float LOG2E = 1.4426950408889634f;
 
 template <int G, int D>
 struct AttnSmem {
     float acc[4][G][D];
     float ml[4][G][2];
+    float cml[G * 32][2];     // combination: running maximum and sum of every (head, split)
+    float coef[G][33];        // weight of every split, [32] = the normalizer
 };
 
 // T positions over nsplit splits -> positions per split (a multiple of 16) and the number of splits that have work.
@@ -146,20 +148,45 @@ __device__ __forceinline__ void attn_split(const uint16_t* q, const uint16_t* kb
     }
 }
 
-// Output element e of one query head from the partial states of its `active` splits (consecutive, stride D + 2 floats).
-template <int D>
-__device__ __forceinline__ float attn_combine(const float* p, int active, int e) {
+// The G heads of one key/value head from the partial states of their `active` splits, by the whole CTA (every thread must
+// call it): out[g * D + e] = sum_s a_s[e] c_s / sum_s l_s c_s with c_s = 2^(m_s - max m), splits in ascending order.
+// part: the partial states of head 0 of the group (head g at + g * nsplit * (D + 2) floats); active <= 32.
+template <int G, int D>
+__device__ __forceinline__ void attn_combine_cta(const float* part, int nsplit, int active, uint16_t* out, AttnSmem<G, D>& sm) {
     constexpr int stride = D + 2;
-    float mm = -INFINITY;
-    for (int s = 0; s < active; ++s) mm = fmaxf(mm, __ldcg(p + s * stride + D));
-    float ll = 0.0f, av = 0.0f;
-    for (int s = 0; s < active; ++s) {
-        const float ms = __ldcg(p + s * stride + D);
-        const float c = ms == -INFINITY ? 0.0f : exp2f(ms - mm);
-        ll += __ldcg(p + s * stride + D + 1) * c;
-        av += __ldcg(p + s * stride + e) * c;
+    const int tid = threadIdx.x, nt = blockDim.x;
+    for (int i = tid; i < G * active; i += nt) {
+        const int g = i / active, s = i - g * active;
+        const float* p = part + ((size_t)g * nsplit + s) * stride;
+        sm.cml[g * 32 + s][0] = __ldcg(p + D);
+        sm.cml[g * 32 + s][1] = __ldcg(p + D + 1);
     }
-    return av / ll;
+    __syncthreads();
+    for (int g = tid; g < G; g += nt) {
+        float mm = -INFINITY;
+        for (int s = 0; s < active; ++s) mm = fmaxf(mm, sm.cml[g * 32 + s][0]);
+        float ll = 0.0f;
+        for (int s = 0; s < active; ++s) {
+            const float ms = sm.cml[g * 32 + s][0];
+            const float c = ms == -INFINITY ? 0.0f : exp2f(ms - mm);
+            ll += sm.cml[g * 32 + s][1] * c;
+            sm.coef[g][s] = c;
+        }
+        sm.coef[g][32] = ll;
+    }
+    __syncthreads();
+    for (int i = tid; i < G * D; i += nt) {
+        const int g = i / D, e = i - g * D;
+        const float* p = part + (size_t)g * nsplit * stride + e;
+        float v[32];
+#pragma unroll
+        for (int s = 0; s < 32; ++s) v[s] = s < active ? __ldcg(p + s * stride) : 0.0f;   // all loads in flight at once
+        float av = 0.0f;
+#pragma unroll
+        for (int s = 0; s < 32; ++s)
+            if (s < active) av += v[s] * sm.coef[g][s];
+        out[i] = f32_to_bf16(av / sm.coef[g][32]);
+    }
 }
 
 }  // namespace scmx

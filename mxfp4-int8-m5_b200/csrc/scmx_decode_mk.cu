@@ -2,15 +2,16 @@
 // step and the CTAs move through the phases of each layer together, separated by grid-wide barriers instead of kernel
 // boundaries.  A batch-1 step is a chain of ~10 tiny dependent kernels per layer; launched separately (even from a CUDA
 // graph, with programmatic dependent launch) each link costs a grid drain and a launch, about 5 us, while the weights it
-// reads would take 1 us at HBM speed.  Here a link costs one barrier, the activations are re-quantized redundantly by every
-// CTA in shared memory (instead of by a one-CTA kernel that everything waits for), and each warp issues the weight loads of
-// its first rows BEFORE it enters the barrier, because they do not depend on the activations.
+// reads would take 1 us at HBM speed.  Here a link costs one barrier and the activations are re-quantized redundantly by every
+// CTA in shared memory (instead of by a one-CTA kernel that everything waits for).  The phases are out-of-line functions with
+// short loops, one copy each: the kernel runs every phase once per layer, so straight-line unrolled code would be fetched
+// again from memory for every layer.
 //
 // Per layer (5 barriers):
 //   P1  RMSNorm + INT8 of h (each CTA, shared memory) -> q|k|v GEMV rows spread over all warps -> y (bf16)
 //   P3  per (kv head, split) CTA: q/k RMSNorm + rotary embedding of the new token, cache append, attention over its
-//       positions -> partial softmax states
-//   P4  every CTA combines the partials to o, INT8 of o -> o-projection GEMV + residual -> h
+//       positions -> partial softmax states; the last split of a kv head to finish combines them -> o
+//   P4  INT8 of o -> o-projection GEMV + residual -> h
 //   P5  RMSNorm + INT8 of h -> gate|up GEMV with SwiGLU -> act
 //   P6  INT8 of act -> down GEMV + residual -> h
 // Arithmetic: the device functions of the stand-alone kernels (row kernels, GEMV, q/k/v epilogue, decode attention), so the
@@ -44,13 +45,13 @@ struct MkArgs {
     uint16_t* y;          // bf16 [(hq + 2 hk) d]
     uint16_t* act;        // bf16 [F]
     float* part;          // f32 [hq, nsplit, d + 2]
+    uint16_t* o;          // bf16 [hq d] attention output
+    int32_t* counters;    // int32 [hk], zero at launch and left zero: arrivals of the splits of a kv head
     uint32_t* bar;        // [0] arrivals, [1] abort word; both zero at launch
     int32_t* status;
-};
-
-struct RowRegs {
-    uint4 w[MK_MAXSTEPS][4];
-    uint32_t bc[MK_MAXSTEPS];     // byte r = block-code byte of row r
+    unsigned long long* trace;   // diagnostic: null, or CTA 0 stores its cycle counter at every phase boundary
+    int n_trace;
+    int trace_barrier;           // diagnostic: every CTA stores its arrival time at this barrier (1-based) after the marks
 };
 
 struct MkSmem {
@@ -58,13 +59,13 @@ struct MkSmem {
     __align__(16) uint4 xn[MK_MAXK / 8];
     float red[33];
     double dred[33];
-    float coef[MK_MAXHQ][33];     // per head: weight of each split, [32] = 1 / sum
-    float ml[MK_MAXHQ * 32][2];
     int ok;
 };
 
+__shared__ MkSmem sm;     // one instance per CTA, used by the out-of-line phase functions below
+
 // ---- grid-wide barrier ------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ bool grid_barrier(const MkArgs& a, uint32_t target, int* ok) {
+__device__ __noinline__ bool grid_barrier(const MkArgs& a, uint32_t target) {
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
@@ -89,17 +90,21 @@ __device__ __forceinline__ bool grid_barrier(const MkArgs& a, uint32_t target, i
                 }
             }
         }
-        *ok = good;
+        sm.ok = good;
     }
     __syncthreads();
-    return *ok != 0;
+    return sm.ok != 0;
 }
 
+__device__ __forceinline__ void mk_mark(const MkArgs& a, int& ti) {
+    if (a.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0 && ti < a.n_trace) a.trace[ti] = (unsigned long long)clock64();
+    ++ti;
+}
 // ---- activation prologues: bf16 row -> INT8 row in shared memory, returns the scale ------------------------------------------
 __device__ __forceinline__ uint4 ldcg4(const uint4* p) { return __ldcg(p); }
 
 // INT8 of the bf16 row staged in sm.xn (nv vectors of 8), arithmetic of act_quant; amax is this thread's partial maximum.
-__device__ __forceinline__ float quantize_staged(MkSmem& sm, int nv, float amax) {
+__device__ __forceinline__ float quantize_staged(int nv, float amax) {
     amax = block_max(amax, sm.red);
     float s, qi;
     quant_scale(amax, s, qi);
@@ -126,7 +131,7 @@ __device__ __forceinline__ float amax8(const uint4& r) {
     return m;
 }
 
-__device__ __forceinline__ float pro_act(MkSmem& sm, const uint16_t* x, int K) {
+__device__ __noinline__ float pro_act(const uint16_t* x, int K) {
     const int nv = K / 8;
     float amax = 0.0f;
     for (int v = threadIdx.x; v < nv; v += MK_THREADS) {
@@ -134,10 +139,10 @@ __device__ __forceinline__ float pro_act(MkSmem& sm, const uint16_t* x, int K) {
         sm.xn[v] = r;
         amax = fmaxf(amax, amax8(r));
     }
-    return quantize_staged(sm, nv, amax);
+    return quantize_staged(nv, amax);
 }
 
-__device__ __forceinline__ float pro_norm(MkSmem& sm, const uint16_t* x, const uint16_t* nw, float eps, int K) {
+__device__ __noinline__ float pro_norm(const uint16_t* x, const uint16_t* nw, float eps, int K) {
     const int nv = K / 8;
     double ss = 0.0;
     for (int v = threadIdx.x; v < nv; v += MK_THREADS) {
@@ -167,77 +172,41 @@ __device__ __forceinline__ float pro_norm(MkSmem& sm, const uint16_t* x, const u
         }
         sm.xn[v] = make_uint4(o[0], o[1], o[2], o[3]);
     }
-    return quantize_staged(sm, nv, amax);
+    return quantize_staged(nv, amax);
 }
 
-// o = attention output from the partial states of all heads (the arithmetic of attn_combine), then its INT8.
-template <int HD>
-__device__ __forceinline__ float pro_attn(MkSmem& sm, const MkArgs& a, int active) {
-    constexpr int stride = HD + 2;
-    const int tid = threadIdx.x, hq = a.hq;
-    for (int i = tid; i < hq * active; i += MK_THREADS) {
-        const int head = i / active, s = i - head * active;
-        const float* p = a.part + ((size_t)head * a.nsplit + s) * stride;
-        sm.ml[head * 32 + s][0] = __ldcg(p + HD);
-        sm.ml[head * 32 + s][1] = __ldcg(p + HD + 1);
-    }
-    __syncthreads();
-    for (int head = tid; head < hq; head += MK_THREADS) {
-        float mm = -INFINITY;
-        for (int s = 0; s < active; ++s) mm = fmaxf(mm, sm.ml[head * 32 + s][0]);
-        float ll = 0.0f;
-        for (int s = 0; s < active; ++s) {
-            const float ms = sm.ml[head * 32 + s][0];
-            const float c = ms == -INFINITY ? 0.0f : exp2f(ms - mm);
-            ll += sm.ml[head * 32 + s][1] * c;
-            sm.coef[head][s] = c;
-        }
-        sm.coef[head][32] = ll;
-    }
-    __syncthreads();
-    const int n = hq * HD;
-    float amax = 0.0f;
-    uint16_t* stage = reinterpret_cast<uint16_t*>(sm.xn);
-    for (int e = tid; e < n; e += MK_THREADS) {
-        const int head = e / HD, dd = e - head * HD;
-        const float* p = a.part + (size_t)head * a.nsplit * stride + dd;
-        float av = 0.0f;
-        for (int s = 0; s < active; ++s) av += __ldcg(p + s * stride) * sm.coef[head][s];
-        const uint16_t ob = f32_to_bf16(av / sm.coef[head][32]);
-        stage[e] = ob;
-        amax = fmaxf(amax, fabsf(bf16_to_f32(ob)));
-    }
-    __syncthreads();
-    return quantize_staged(sm, n / 8, amax);
-}
+// ---- GEMV: a warp computes 4 consecutive output rows over the whole K, in chunks of MK_UNROLL steps of 1024 codes -----------
+// The chunks of a warp (row group after row group) form one sequence that is software-pipelined: the loads of chunk i + 1
+// are issued before chunk i is expanded and accumulated, and nothing consumes a loaded value before all loads of its chunk
+// are issued.  epi 1: out[n] = T(acc xs ws); 2: out[n] = T(res[n] + T(..)); 3: SwiGLU of rows [g0 g1 u0 u1].
+constexpr int MK_UNROLL = 3;
 
-// ---- GEMV rows: a warp computes 4 consecutive output rows over the whole K -------------------------------------------------
-__device__ __forceinline__ void load_rows(RowRegs& r, const uint32_t* codes, const uint8_t* bcodes, int K, int steps, int n0,
-                                          int lane) {
-    const int wpr = K / 8, bcr = K / 128;
+struct RowChunk {
+    uint4 w[MK_UNROLL][4];
+    uint32_t bc[MK_UNROLL];       // lane l: block-code byte (l >> 2) of the step, of row (l & 3)
+};
+
+__device__ __forceinline__ void load_chunk(RowChunk& c, const uint32_t* __restrict__ codes, const uint8_t* __restrict__ bcodes,
+                                           int n0, int s0, int steps, int wpr, int bcr, int lane) {
 #pragma unroll
-    for (int s = 0; s < MK_MAXSTEPS; ++s) {
-        if (s < steps) {
-            const int k0 = (s * 32 + lane) * 32;
-            uint32_t b = 0;
+    for (int u = 0; u < MK_UNROLL; ++u) {
+        if (s0 + u < steps) {
+            const int k0 = ((s0 + u) * 32 + lane) * 32;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                r.w[s][q] = ldg_stream(reinterpret_cast<const uint4*>(codes + (size_t)(n0 + q) * wpr + k0 / 8));
-                b |= (uint32_t)__ldg(bcodes + (size_t)(n0 + q) * bcr + (k0 >> 7)) << (8 * q);
-            }
-            r.bc[s] = b;
+            for (int q = 0; q < 4; ++q)
+                c.w[u][q] = ldg_stream(reinterpret_cast<const uint4*>(codes + (size_t)(n0 + q) * wpr + k0 / 8));
+            // the 32 lanes x 32 codes of a step span 8 block-code bytes per row: lane l fetches byte l >> 2 of row l & 3
+            c.bc[u] = __ldg(bcodes + (size_t)(n0 + (lane & 3)) * bcr + (s0 + u) * 8 + (lane >> 2));
         }
     }
 }
 
-__device__ __forceinline__ void compute_rows(const RowRegs& r, const int8_t* xq, int steps, int lane, int (&tot)[4]) {
+__device__ __forceinline__ void compute_chunk(const RowChunk& c, const int8_t* xq, int s0, int steps, int lane, int (&tot)[4]) {
     const uint32_t mlo = 0x03020100u, mhi = 0x0C080604u;      // 2 x E2M1 magnitudes 0 1 2 3 | 4 6 8 12
 #pragma unroll
-    for (int q = 0; q < 4; ++q) tot[q] = 0;
-#pragma unroll
-    for (int s = 0; s < MK_MAXSTEPS; ++s) {
-        if (s < steps) {
-            const int k0 = (s * 32 + lane) * 32;
+    for (int u = 0; u < MK_UNROLL; ++u) {
+        if (s0 + u < steps) {
+            const int k0 = ((s0 + u) * 32 + lane) * 32;
             const uint4 xa = *reinterpret_cast<const uint4*>(xq + k0);
             const uint4 xb = *reinterpret_cast<const uint4*>(xq + k0 + 16);
             const uint32_t x[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
@@ -247,8 +216,8 @@ __device__ __forceinline__ void compute_rows(const RowRegs& r, const int8_t* xq,
             const int sh = ((k0 >> 5) & 3) * 2;               // the lane's 32-block inside its block-code byte
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                const uint32_t ww[4] = {r.w[s][q].x, r.w[s][q].y, r.w[s][q].z, r.w[s][q].w};
-                const uint32_t code = (r.bc[s] >> (8 * q + sh)) & 3u;
+                const uint32_t ww[4] = {c.w[u][q].x, c.w[u][q].y, c.w[u][q].z, c.w[u][q].w};
+                const uint32_t code = (__shfl_sync(0xffffffffu, c.bc[u], (lane & ~3) | q) >> sh) & 3u;
                 int bs = 0;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -261,60 +230,55 @@ __device__ __forceinline__ void compute_rows(const RowRegs& r, const int8_t* xq,
             }
         }
     }
-#pragma unroll
-    for (int q = 0; q < 4; ++q) tot[q] = warp_sum(tot[q]);
 }
 
-// epi 1: out[n] = T(acc xs ws); 2: out[n] = T(res[n] + T(..)); 3: SwiGLU of rows [g0 g1 u0 u1] -> out[n0/2], out[n0/2 + 1]
-__device__ __forceinline__ void epilogue_rows(const int (&tot)[4], float xs, const float* wscale, int n0, int epi, const uint16_t* res,
-                                              uint16_t* out, int lane) {
-    if (epi == 3) {
-        if (lane < 2) {
-            const float g = scale_acc(tot[lane], xs, __ldg(wscale + n0 + lane));
-            const float u = scale_acc(tot[lane + 2], xs, __ldg(wscale + n0 + lane + 2));
-            out[n0 / 2 + lane] = f32_to_bf16(swiglu_bf16(g, u));
+__device__ __noinline__ void run_job(const uint32_t* __restrict__ codes, const uint8_t* __restrict__ bcodes,
+                                     const float* __restrict__ wscale, int N, int K, float xs, int epi, const uint16_t* res,
+                                     uint16_t* out) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // row groups are dealt warp-major, so that a job with fewer groups than warps still uses every SM
+    const int gw = warp * gridDim.x + blockIdx.x, nw = gridDim.x * MK_WARPS;
+    const int steps = K / 1024, wpr = K / 8, bcr = K / 128, groups = N / 4;
+    const int8_t* xq = sm.xq;
+    if (gw >= groups) return;
+    RowChunk cur, nxt;
+    int grp = gw, s0 = 0;
+    load_chunk(cur, codes, bcodes, grp * 4, 0, steps, wpr, bcr, lane);
+    int tot[4] = {0, 0, 0, 0};
+    for (;;) {
+        // the chunk after this one: the next steps of the same rows, or the first steps of the warp's next row group
+        int ngrp = grp, ns0 = s0 + MK_UNROLL;
+        if (ns0 >= steps) {
+            ngrp = grp + nw;
+            ns0 = 0;
         }
-        return;
-    }
-    if (lane < 4) {
-        float y = scale_acc(tot[lane], xs, __ldg(wscale + n0 + lane));
-        if (epi == 2) y = __fadd_rn(bf16_to_f32(__ldcg(res + n0 + lane)), y);
-        out[n0 + lane] = f32_to_bf16(y);
-    }
-}
-
-struct GemvJob {
-    const uint32_t* codes;
-    const uint8_t* bcodes;
-    const float* wscale;
-    int N, K, steps;
-};
-
-__device__ __forceinline__ GemvJob make_job(const scmx_decode_layer& L, int which, int N, int K) {
-    GemvJob j;
-    j.codes = L.codes[which];
-    j.bcodes = L.bcodes[which];
-    j.wscale = L.wscale[which];
-    j.N = N;
-    j.K = K;
-    j.steps = K / 1024;
-    return j;
-}
-
-// first row group of this warp: its weight loads go out before the barrier that the activations wait for
-__device__ __forceinline__ void prefetch_job(const GemvJob& j, RowRegs& r, int gw, int lane) {
-    if (gw * 4 < j.N) load_rows(r, j.codes, j.bcodes, j.K, j.steps, gw * 4, lane);
-}
-
-__device__ __forceinline__ void run_job(const GemvJob& j, RowRegs& r, const int8_t* xq, float xs, int epi, const uint16_t* res,
-                                        uint16_t* out, int gw, int nw, int lane) {
-    bool first = true;
-    for (int grp = gw; grp * 4 < j.N; grp += nw) {
-        if (!first) load_rows(r, j.codes, j.bcodes, j.K, j.steps, grp * 4, lane);
-        first = false;
-        int tot[4];
-        compute_rows(r, xq, j.steps, lane, tot);
-        epilogue_rows(tot, xs, j.wscale, grp * 4, epi, res, out, lane);
+        const bool more = ngrp < groups;
+        if (more) load_chunk(nxt, codes, bcodes, ngrp * 4, ns0, steps, wpr, bcr, lane);
+        compute_chunk(cur, xq, s0, steps, lane, tot);
+        if (ngrp != grp) {                                    // last chunk of the row group: reduce and write
+            const int n0 = grp * 4;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) tot[q] = warp_sum(tot[q]);
+            // every lane holds the four totals; lane r finishes row r (selects, not indexing: the totals stay in registers)
+            const int t_lo = (lane & 1) ? tot[1] : tot[0], t_hi = (lane & 1) ? tot[3] : tot[2];
+            if (epi == 3) {
+                if (lane < 2) {
+                    const float gg = scale_acc(t_lo, xs, __ldg(wscale + n0 + lane));
+                    const float uu = scale_acc(t_hi, xs, __ldg(wscale + n0 + lane + 2));
+                    out[n0 / 2 + lane] = f32_to_bf16(swiglu_bf16(gg, uu));
+                }
+            } else if (lane < 4) {
+                float y = scale_acc(lane < 2 ? t_lo : t_hi, xs, __ldg(wscale + n0 + lane));
+                if (epi == 2) y = __fadd_rn(bf16_to_f32(__ldcg(res + n0 + lane)), y);
+                out[n0 + lane] = f32_to_bf16(y);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) tot[q] = 0;
+        }
+        if (!more) break;
+        cur = nxt;
+        grp = ngrp;
+        s0 = ns0;
     }
 }
 
@@ -385,15 +349,11 @@ __device__ __forceinline__ void qkv_prepare(QkvSmem<G, HD>& qs, const MkArgs& a,
 // ---- the kernel ------------------------------------------------------------------------------------------------------------
 template <int G, int HD>
 __global__ void __launch_bounds__(MK_THREADS, 1) decode_step_kernel(const MkArgs a) {
-    __shared__ MkSmem sm;
     __shared__ QkvSmem<G, HD> qs;
     __shared__ AttnSmem<G, HD> as;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    // row groups are dealt warp-major, so that a job with fewer groups than warps still uses every SM
-    const int gw = warp * gridDim.x + blockIdx.x, nw = gridDim.x * MK_WARPS;
     const int D = a.D, F = a.F, QD = a.hq * HD, NQKV = (a.hq + 2 * a.hk) * HD;
     uint32_t target = 0;
-    RowRegs regs;
 
     int64_t pos = a.pos_dev[0];
     pos = pos < 0 ? 0 : pos;
@@ -404,20 +364,28 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_step_kernel(const MkArgs
     attn_chunking(T, a.nsplit, chunk, active);
     constexpr int stride = HD + 2;
 
+    int ti = 0;
+#define MK_MARK()                                                                                   \
+    do {                                                                                            \
+        mk_mark(a, ti);                                                                             \
+    } while (0)
 #define MK_BARRIER()                                          \
     do {                                                      \
+        MK_MARK();                                            \
         target += gridDim.x;                                  \
-        if (!grid_barrier(a, target, &sm.ok)) return;         \
+        if (a.trace != nullptr && tid == 0 && (int)(target / gridDim.x) == a.trace_barrier)                      \
+            a.trace[a.n_trace + blockIdx.x] = globaltimer_ns();                                             \
+        if (!grid_barrier(a, target)) return;         \
+        MK_MARK();                                            \
     } while (0)
 
     for (int li = 0; li < a.n_layers; ++li) {
-        const scmx_decode_layer& L = a.layers[li];
+        const scmx_decode_layer L = a.layers[li];             // by value: the pointers sit in registers for the whole layer
         // P1: input RMSNorm + INT8, q|k|v projection
-        GemvJob job = make_job(L, 0, NQKV, D);
-        prefetch_job(job, regs, gw, lane);
         if (li > 0) MK_BARRIER();                             // h of the previous layer complete
-        float xs = pro_norm(sm, a.h, L.ln_in, a.eps, D);
-        run_job(job, regs, sm.xq, xs, 1, nullptr, a.y, gw, nw, lane);
+        float xs = pro_norm(a.h, L.ln_in, a.eps, D);
+        MK_MARK();
+        run_job(L.codes[0], L.bcodes[0], L.wscale[0], NQKV, D, xs, 1, nullptr, a.y);
         // P3: attention of one (kv head, split) per CTA
         MK_BARRIER();
         {
@@ -433,39 +401,59 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_step_kernel(const MkArgs
                 const int64_t t0 = (int64_t)split * chunk, t1 = t0 + chunk < T ? t0 + chunk : T;
                 attn_split<G, HD>(qs.q, kc, vc, t0, t1, in_cache ? pos : -1, qs.k, qs.v, a.scale,
                                   a.part + ((size_t)kvh * G * a.nsplit + split) * stride, (size_t)a.nsplit * stride, as);
+                // the last split of this kv head to finish combines them (the arithmetic of attn_combine) into o
+                __syncthreads();
+                if (tid == 0) {                               // one fence orders the CTA's partials before the ticket
+                    __threadfence();
+                    sm.ok = atomicAdd(a.counters + kvh, 1);
+                    __threadfence();
+                }
+                __syncthreads();
+                if (sm.ok == active - 1) {
+                    attn_combine_cta<G, HD>(a.part + (size_t)kvh * G * a.nsplit * stride, a.nsplit, active,
+                                            a.o + (size_t)kvh * G * HD, as);
+                    if (tid == 0) a.counters[kvh] = 0;
+                }
             }
         }
         // P4: combine the splits, INT8 of o, o-projection + residual
-        job = make_job(L, 1, D, QD);
-        prefetch_job(job, regs, gw, lane);
         MK_BARRIER();
-        xs = pro_attn<HD>(sm, a, active);
-        run_job(job, regs, sm.xq, xs, 2, a.h, a.h, gw, nw, lane);
+        xs = pro_act(a.o, QD);
+        MK_MARK();
+        run_job(L.codes[1], L.bcodes[1], L.wscale[1], D, QD, xs, 2, a.h, a.h);
         // P5: post-attention RMSNorm + INT8, gate|up projection with SwiGLU
-        job = make_job(L, 2, 2 * F, D);
-        prefetch_job(job, regs, gw, lane);
         MK_BARRIER();
-        xs = pro_norm(sm, a.h, L.ln_post, a.eps, D);
-        run_job(job, regs, sm.xq, xs, 3, nullptr, a.act, gw, nw, lane);
+        xs = pro_norm(a.h, L.ln_post, a.eps, D);
+        MK_MARK();
+        run_job(L.codes[2], L.bcodes[2], L.wscale[2], 2 * F, D, xs, 3, nullptr, a.act);
         // P6: INT8 of act, down projection + residual
-        job = make_job(L, 3, D, F);
-        prefetch_job(job, regs, gw, lane);
         MK_BARRIER();
-        xs = pro_act(sm, a.act, F);
-        run_job(job, regs, sm.xq, xs, 2, a.h, a.h, gw, nw, lane);
+        xs = pro_act(a.act, F);
+        MK_MARK();
+        run_job(L.codes[3], L.bcodes[3], L.wscale[3], D, F, xs, 2, a.h, a.h);
     }
 #undef MK_BARRIER
+#undef MK_MARK
 }
 
 }  // namespace scmx
 
 using namespace scmx;
 
+static unsigned long long* g_trace = nullptr;
+static int g_n_trace = 0;
+extern "C" int scmx_set_decode_trace(unsigned long long* device_buf, int n) {
+    g_trace = n > 0 ? device_buf : nullptr;
+    g_n_trace = g_trace ? n : 0;
+    return SCMX_OK;
+}
+
 extern "C" int scmx_decode_step_dense(const scmx_decode_layer* layers, int n_layers, int D, int F, int hq, int hk, int d, float eps,
                                       float scale, const float* inv_freq, const float* rope_table, int64_t rope_rows,
                                       int64_t capacity, const int32_t* pos_dev, uint16_t* h, uint16_t* y, uint16_t* act,
-                                      float* partials, int nsplit, uint32_t* barrier, int32_t* status, void* stream) {
-    SCMX_REQUIRE(layers && pos_dev && h && y && act && partials && barrier && status && inv_freq, SCMX_EINVAL, "decode_step: null buffer");
+                                      uint16_t* o, float* partials, int nsplit, int32_t* counters, uint32_t* barrier,
+                                      int32_t* status, void* stream) {
+    SCMX_REQUIRE(layers && pos_dev && h && y && act && o && partials && counters && barrier && status && inv_freq, SCMX_EINVAL, "decode_step: null buffer");
     SCMX_REQUIRE(n_layers > 0 && hq > 0 && hk > 0 && hq % hk == 0 && hq <= MK_MAXHQ, SCMX_EINVAL, "decode_step: hq=%d hk=%d", hq, hk);
     SCMX_REQUIRE(d == 128, SCMX_ELIMIT, "decode_step: head size %d (128)", d);
     const int G = hq / hk;
@@ -485,7 +473,8 @@ extern "C" int scmx_decode_step_dense(const scmx_decode_layer* layers, int n_lay
     MkArgs a;
     a.layers = layers; a.n_layers = n_layers; a.D = D; a.F = F; a.hq = hq; a.hk = hk; a.nsplit = nsplit; a.eps = eps; a.scale = scale;
     a.inv_freq = inv_freq; a.rope_cs = rope_table; a.rope_rows = rope_table ? rope_rows : 0; a.cap = capacity; a.pos_dev = pos_dev;
-    a.h = h; a.y = y; a.act = act; a.part = partials; a.bar = barrier; a.status = status;
+    a.h = h; a.y = y; a.act = act; a.o = o; a.counters = counters; a.part = partials; a.bar = barrier; a.status = status;
+    a.trace = g_trace; a.n_trace = g_n_trace & 0xFFFF; a.trace_barrier = g_n_trace >> 16;
     cudaStream_t st = (cudaStream_t)stream;
     SCMX_CUDA_OK(cudaMemsetAsync(barrier, 0, 2 * sizeof(uint32_t), st));
     cudaLaunchConfig_t cfg = {};

@@ -131,6 +131,7 @@ class DecodeQwen3(_Decoder):
         self._mk = dict(cache=cache, table=torch.from_numpy(raw).to(dev),
                         y=torch.empty((hq + 2 * hk) * d, dtype=torch.bfloat16, device=dev),
                         act=torch.empty(a.intermediate_size, dtype=torch.bfloat16, device=dev),
+                        o=torch.empty(hq * d, dtype=torch.bfloat16, device=dev),
                         bar=torch.zeros(2, dtype=torch.int32, device=dev),
                         status=torch.zeros(1, dtype=torch.int32, device=dev),
                         pos=torch.zeros(1, dtype=torch.int32, device=dev))
@@ -154,7 +155,8 @@ class DecodeQwen3(_Decoder):
         _lib.call("scmx_decode_step_dense", _lib.ptr(mk["table"]), len(f.layers), a.hidden_size, a.intermediate_size, hq, hk, d,
                   float(f.eps), float(f.layers[0][0].self_attn.scale), _lib.ptr(f.inv_freq), _lib.ptr(f.rope_cs),
                   f.rope_cs.shape[0], cache[0].k.shape[1], _lib.ptr(pos_dev), _lib.ptr(h), _lib.ptr(mk["y"]), _lib.ptr(mk["act"]),
-                  _lib.ptr(self.attn.part), self.attn.nsplit, _lib.ptr(mk["bar"]), _lib.ptr(mk["status"]), _lib.stream())
+                  _lib.ptr(mk["o"]), _lib.ptr(self.attn.part), self.attn.nsplit, _lib.ptr(self.attn.counters), _lib.ptr(mk["bar"]),
+                  _lib.ptr(mk["status"]), _lib.stream())
         xn = S.rmsnorm_quant_n(h, self.model.model.norm.weight, f.eps, 1)[2]
         return self.head(xn[None])
 
