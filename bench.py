@@ -492,6 +492,12 @@ def run_ours(args):
         line["moe"] = bench_moe(pkg, torch, dist if world > 1 else None)
     except Exception as e:   # noqa: BLE001
         line["moe"] = dict(error=f"{type(e).__name__}: {e}")
+    if world == 1:
+        torch.cuda.empty_cache()
+        try:       # whole-model time to first token and decode tokens/s through the fused callers (attention included)
+            line["models"] = bench_models(pkg, torch, reps=3, lengths=(512, 2048))
+        except Exception as e:   # noqa: BLE001
+            line["models"] = dict(error=f"{type(e).__name__}: {e}")
     if rank == 0 and world == 1:
         dt, cops = cpu_dense_layer_sample()
         line["cpu_baseline"] = dict(value=cops / dt / 1e12, unit="TOPS", cores=os.cpu_count(), kind="port",
@@ -569,30 +575,35 @@ def bench_models(pkg, torch, reps=5, lengths=(512, 2048, 8192), kinds=("qwen3", 
                 del g
             except Exception as e:  # noqa: BLE001
                 res["ttft_graph_ms"][str(L)] = f"capture failed: {str(e)[:80]}"
-        # decode: 64 tokens after a 512-token prompt, eager step() calls and one CUDA graph replayed per token
-        dec = (DEC.DecodeQwen3 if kind == "qwen3" else DEC.DecodeOlmoe)(fused)
-        prefill(512)
-        torch.cuda.synchronize()
+        # decode: 64 tokens after a 512-token prompt.  Graph-replayed steps with (dense) the persistent one-kernel step and
+        # with the chain of stand-alone kernels, and eager step() calls
+        cls = DEC.DecodeQwen3 if kind == "qwen3" else DEC.DecodeOlmoe
         n_tok = 64
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        for rep in range(2):                                   # first pass warms up, second is timed
-            for c in cache:
-                c.offset = 512
+
+        def tok_s(fn):
+            for rep in range(2):                               # first pass warms up (and captures), second is timed
+                prefill(512)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+            return round(n_tok / (e0.elapsed_time(e1) / 1e3), 1)
+
+        def eager(dec):
             tok = ids_all[:, 512:513]
-            e0.record()
             for _ in range(n_tok):
                 tok = dec.step(tok, cache)[:, -1].argmax(-1, keepdim=True)
-            e1.record()
-            torch.cuda.synchronize()
-        res["decode_tok_s_eager"] = round(n_tok / (e0.elapsed_time(e1) / 1e3), 1)
-        for rep in range(2):
-            for c in cache:
-                c.offset = 512
-            e0.record()
-            dec.generate(ids_all[:, 512:513], cache, n_tok)
-            e1.record()
-            torch.cuda.synchronize()
-        res["decode_tok_s"] = round(n_tok / (e0.elapsed_time(e1) / 1e3), 1)
+
+        dec = cls(fused)
+        res["decode_tok_s"] = tok_s(lambda: dec.generate(ids_all[:, 512:513], cache, n_tok))
+        res["decode_tok_s_eager"] = tok_s(lambda: eager(dec))
+        if kind == "qwen3":
+            res["decode_persistent_kernel"] = bool(dec.persistent)
+            dec.check_status()
+            chain = cls(fused, persistent=False)
+            res["decode_tok_s_kernel_chain"] = tok_s(lambda: chain.generate(ids_all[:, 512:513], cache, n_tok))
+            del chain
         pkg._lib.check_status()
         out[kind] = res
         del fused, dec, cache, model
