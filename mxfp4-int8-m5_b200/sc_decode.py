@@ -1,8 +1,8 @@
 """Batch-1 decode GEMV that reads the packed SC-MXFP4 weights directly, with the call signature of the reference's
 e2e/sc_decode.py `gemv`.  The kernel accumulates exact INT32 totals (DP4A) and applies the GEMM's epilogues, so
 decode and prefill produce the same bits.  Prologues pro=1 / pro=2 (activation quantization / RMSNorm + quantization
-of a bf16 input row) run inside the GEMV kernel (scmx_gemv_pro) when K <= 8192 and the matrix is small enough for
-the register kernel; otherwise as the separate row kernel followed by the GEMV.  Both give the same bits."""
+of a bf16 input row) run as the separate row kernel followed by the GEMV, or - on request, see FUSE_PROLOGUE - inside the
+GEMV kernel (scmx_gemv_pro; K <= 8192, register kernel only).  Both give the same bits."""
 import torch
 
 from . import _lib
@@ -10,22 +10,27 @@ from . import sc_format as F
 from . import sc_kernels as S
 
 USE_PDL = True   # programmatic dependent launch: weight loads overlap the previous kernel's tail
-FUSE_PROLOGUE = (1, 2)   # which prologues run inside the GEMV kernel where it applies; () = always the separate row kernel
+# Which prologues run inside the GEMV kernel (scmx_gemv_pro) where it applies.  Empty by default: in a chain of programmatic
+# dependent launches the separate row kernel is faster (Qwen3-1.7B decode from a graph: 638 tokens/s with none fused, 628 /
+# 625 / 605 with pro 1 / pro 2 / both fused), because every CTA of the GEMV repeats the row reductions.
+FUSE_PROLOGUE = ()
 
 
 def gemv(xq, codes, bcodes, xscale, wscale, N, epi, dtype=torch.bfloat16, res=None, nsg=None, eidx=None, xstride=0,
-         pro=0, nw=None, eps=None, rows=None, vpl=None, shared=None, splitk=None):
+         pro=0, nw=None, eps=None, rows=None, vpl=None, shared=None, splitk=None, fuse=None):
     """W4A8 GEMV.  pro=0: xq int8 [K] (or [S, K] with xstride=1) and xscale; pro=1: xq is a bf16 row (or rows),
     quantized per token first; pro=2: RMSNorm(nw, eps) + INT8 first.  Output: EPI 1: bf16 [N]; 2: bf16 [N] = res + y;
     3: bf16 [N / 2] (interleaved gate/up rows); 0: int32 [N] exact totals.
     MoE (eidx int32 [S] given): codes [E, ...], bcodes [E, N, ...], wscale [E, N]; output row j uses expert eidx[j] and
     input row j if xstride = 1 (else the single input row) -> [S, N or N/2].  shared = e: one more slot uses expert e.
-    nsg / rows / vpl / splitk are Metal tile hints: accepted and ignored."""
+    nsg / rows / vpl / splitk are Metal tile hints: accepted and ignored.  fuse: None = FUSE_PROLOGUE, True / False / a tuple
+    of prologue numbers = run them inside the GEMV kernel."""
     xbf = None
     if pro:
         x2 = xq.reshape(-1, xq.shape[-1])
         Kp = x2.shape[-1]
-        fused = (pro in (FUSE_PROLOGUE if isinstance(FUSE_PROLOGUE, tuple) else ((1, 2) if FUSE_PROLOGUE else ())) and epi != 0 and Kp <= 8192 and x2.dtype == torch.bfloat16 and x2.is_contiguous()
+        sel = FUSE_PROLOGUE if fuse is None else fuse
+        fused = (pro in (sel if isinstance(sel, tuple) else ((1, 2) if sel else ())) and epi != 0 and Kp <= 8192 and x2.dtype == torch.bfloat16 and x2.is_contiguous()
                  and (eidx is not None or N * Kp // 2 < (16 << 20)))
         if fused:
             xbf = x2

@@ -376,13 +376,11 @@ def test_gemv_fused_prologue_equals_row_kernel_then_gemv(scmx, oracle, K):
         for epi in (1, 2, 3):
             outs = []
             for fuse in (True, False):
-                G.FUSE_PROLOGUE = fuse
-                outs.append(G.gemv(x, c, b, None, s, N, epi, res=res if epi == 2 else None, pro=pro, nw=nw, eps=1e-6))
-            G.FUSE_PROLOGUE = True
+                outs.append(G.gemv(x, c, b, None, s, N, epi, res=res if epi == 2 else None, pro=pro, nw=nw, eps=1e-6, fuse=fuse))
             assert torch.equal(outs[0], outs[1]), (pro, epi)
     # zero row: scale 0, all-zero codes, output exactly the residual
     z = torch.zeros_like(x)
-    y = G.gemv(z, c, b, None, s, N, 2, res=res, pro=1)
+    y = G.gemv(z, c, b, None, s, N, 2, res=res, pro=1, fuse=True)
     assert torch.equal(y, res)
     # expert form with one input row per slot
     E, Ne = 4, 256
@@ -392,7 +390,5 @@ def test_gemv_fused_prologue_equals_row_kernel_then_gemv(scmx, oracle, K):
     e = cuda(np.array([3, 0, 2], np.int32))
     outs = []
     for fuse in (True, False):
-        G.FUSE_PROLOGUE = fuse
-        outs.append(G.gemv(xr, cE, bE, None, sE, Ne, 1, eidx=e, xstride=1, pro=1))
-    G.FUSE_PROLOGUE = True
+        outs.append(G.gemv(xr, cE, bE, None, sE, Ne, 1, eidx=e, xstride=1, pro=1, fuse=fuse))
     assert torch.equal(outs[0], outs[1])
