@@ -299,11 +299,13 @@ def bench_moe(pkg, torch, dist=None, reps=5):
     if dist is not None:
         dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.profiler.start()            # a profiler given --profile-from-start off sees the timed passes only
     e0.record()
     for _ in range(reps):
         run()
     e1.record()
     torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
     ms = e0.elapsed_time(e1) / reps
     if dist is not None:
         t = torch.tensor([ms], device="cuda")

@@ -461,12 +461,23 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t* __rest
         if (live) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) a[j] = 0.0f;
-            for (int t = 0; t < topk; ++t) {
-                float v[8];
-                load8_bf16(y + (int64_t)s_pos[t] * K + k, v);
-                const float sc = s_sc[t];
+            for (int t0 = 0; t0 < topk; t0 += 8) {            // up to 8 expert rows in flight, summed in slot order
+                uint4 raw[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) a[j] = rbf(__fadd_rn(rbf(__fmul_rn(v[j], sc)), a[j]));
+                for (int u = 0; u < 8; ++u)
+                    if (t0 + u < topk) raw[u] = *reinterpret_cast<const uint4*>(y + (int64_t)s_pos[t0 + u] * K + k);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    if (t0 + u < topk) {
+                        const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+                        const float sc = s_sc[t0 + u];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            a[2 * j] = rbf(__fadd_rn(rbf(__fmul_rn(__uint_as_float(w[j] << 16), sc)), a[2 * j]));
+                            a[2 * j + 1] = rbf(__fadd_rn(rbf(__fmul_rn(__uint_as_float(w[j] & 0xFFFF0000u), sc)), a[2 * j + 1]));
+                        }
+                    }
+                }
             }
 #pragma unroll
             for (int j = 0; j < 8; ++j) r[j] = rbf(__fadd_rn(r[j], a[j]));
@@ -504,17 +515,33 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t* __rest
 }
 
 // ---- row gather --------------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(128) gather_rows_kernel(const int8_t* __restrict__ xq, const float* __restrict__ xs,
-                                                          const int32_t* __restrict__ tok, int64_t rows_s, int K,
+// One warp per destination row: its 16-byte loads are all issued before the first store (K <= 8192: 16 per lane).
+__global__ void __launch_bounds__(256) gather_rows_kernel(const int8_t* __restrict__ xq, const float* __restrict__ xs,
+                                                          const int32_t* __restrict__ tok, int64_t rows_q, int64_t rows_s, int K,
                                                           int8_t* __restrict__ dq, float* __restrict__ ds) {
     pdl_launch_dependents();
     pdl_wait();
-    const int64_t p = blockIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int64_t p = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (p >= rows_q) return;
     const int t = tok[p];
     const uint4* src = reinterpret_cast<const uint4*>(xq + (int64_t)t * K);
     uint4* dst = reinterpret_cast<uint4*>(dq + p * K);
-    for (int i = threadIdx.x; i < K / 16; i += blockDim.x) dst[i] = src[i];
-    if (threadIdx.x == 0 && p < rows_s) ds[p] = xs[t];
+    const int nv = K / 16;
+    for (int base = 0; base < nv; base += 32 * 8) {
+        uint4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int i = base + j * 32 + lane;
+            if (i < nv) v[j] = src[i];
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int i = base + j * 32 + lane;
+            if (i < nv) dst[i] = v[j];
+        }
+    }
+    if (lane == 0 && p < rows_s) ds[p] = xs[t];
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -623,7 +650,8 @@ extern "C" int scmx_gather_rows(const int8_t* xq, const float* xs, const int32_t
                  "gather_rows: need rows_s <= rows_q and K %% 16 == 0");
     SCMX_REQUIRE(aligned16(xq) && aligned16(dst_q), SCMX_EINVAL, "gather_rows: buffers must be 16-byte aligned");
     if (rows_q == 0) return SCMX_OK;
-    launch_pdl(gather_rows_kernel, dim3((unsigned)rows_q), dim3(128), 0, (cudaStream_t)stream, xq, xs, tok, rows_s, (int)K, dst_q, dst_s);
+    launch_pdl(gather_rows_kernel, dim3((unsigned)((rows_q + 7) / 8)), dim3(256), 0, (cudaStream_t)stream, xq, xs, tok, rows_q, rows_s, (int)K, dst_q,
+               dst_s);
     SCMX_LAUNCH_OK("gather_rows_kernel");
     return SCMX_OK;
 }

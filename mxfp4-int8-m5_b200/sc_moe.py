@@ -13,7 +13,7 @@ from . import sc_format as F
 from . import sc_kernels as S
 
 TM = 128
-EXPERTS_PER_PASS = 8     # experts decoded to INT8 per pass of moe_mm (two rotating scratch halves)
+EXPERTS_PER_PASS = 32    # experts decoded to INT8 per pass of moe_mm (two rotating scratch halves); 8 -> 32: -12 % on the half-block
 
 _scratch = {}
 

@@ -81,7 +81,7 @@ def test_res_epilogue_and_swiglu_quant(scmx, oracle):
     assert torch.equal(h2, h) and np.array_equal(q2.cpu().numpy(), oq2) and np.array_equal(s2.cpu().numpy(), os2)
 
 
-@pytest.mark.parametrize("E,M,k", [(8, 300, 2), (64, 1000, 8), (128, 257, 8), (3, 1, 1)])
+@pytest.mark.parametrize("E,M,k", [(8, 300, 2), (64, 1000, 8), (128, 257, 8), (3, 1, 1), (64, 4096, 8), (1000, 1025, 8), (16, 8191, 2)])
 def test_route_sort_contract(scmx, oracle, E, M, k):
     rng = np.random.default_rng(E + M)
     inds = np.stack([rng.permutation(E)[:k] for _ in range(M)]).astype(np.int32)
