@@ -8,26 +8,56 @@ from . import sc_moe as M_
 
 
 class MoeBlock:
-    def __init__(self, gu, dn, n_experts, topk, D, F, eps=1e-5, two_pass=False):
+    def __init__(self, gu, dn, n_experts, topk, D, F, eps=1e-5, two_pass=False, early_decode=True):
         """gu = (codes [E, 2F*D/8], bcodes [E, 2F, D/128], wscale [E, 2F]) with gate|up rows interleaved;
         dn = (codes [E, D*F/8], bcodes [E, D, F/128], wscale [E, D]).  two_pass: keep the experts decoded to INT8
-        (moe_mm_i8) instead of decoding per call (moe_mm)."""
+        (moe_mm_i8) instead of decoding per call.  early_decode (default, when the INT8 copies of all experts fit in
+        1 GiB): every step decodes all experts to INT8 on a side stream starting at the top of the step, under the
+        RMSNorm / router / sort / gather kernels and the first grouped GEMM, and the GEMMs run on that (moe_mm_i8);
+        otherwise moe_mm decodes groups of experts between its GEMM passes."""
         self.gu, self.dn, self.E, self.k, self.D, self.F, self.eps = gu, dn, n_experts, topk, D, F, eps
-        self.nw = torch.ones(D, dtype=torch.bfloat16, device=gu[0].device)
+        dev = gu[0].device
+        self.nw = torch.ones(D, dtype=torch.bfloat16, device=dev)
         self.two_pass = two_pass
+        self.early = bool(early_decode and not two_pass and n_experts * 3 * F * D <= (1 << 30))
         if two_pass:
             self.gu8 = M_.unpack_experts(gu[0], gu[1], 2 * F, D)
             self.dn8 = M_.unpack_experts(dn[0], dn[1], D, F)
+        elif self.early:
+            self.gu8 = torch.empty((n_experts * 2 * F, D), dtype=torch.int8, device=dev)
+            self.dn8 = torch.empty((n_experts * D, F), dtype=torch.int8, device=dev)
+            self.side = torch.cuda.Stream(device=dev)
 
-    def experts(self, xq_s, xs_s, R, off, ts, mt):
+    def _start_decode(self):
+        """Both expert sets -> INT8 on the side stream; returns the events the two GEMMs wait for."""
+        main = torch.cuda.current_stream()
+        self.side.wait_stream(main)                           # the previous step's GEMMs no longer read the buffers
+        E, D, F = self.E, self.D, self.F
+        with torch.cuda.stream(self.side):
+            S.unpack_i8(self.gu[0].reshape(-1), self.gu[1].reshape(E * 2 * F, -1), E * 2 * F, D, out=self.gu8)
+            e_gu = torch.cuda.Event()
+            e_gu.record(self.side)
+            S.unpack_i8(self.dn[0].reshape(-1), self.dn[1].reshape(E * D, -1), E * D, F, out=self.dn8)
+            e_dn = torch.cuda.Event()
+            e_dn.record(self.side)
+        return e_gu, e_dn
+
+    def experts(self, xq_s, xs_s, R, off, ts, mt, decoded=None):
         """Sorted INT8 rows [R + 128, D] -> bf16 expert outputs [R, D]."""
         D, F = self.D, self.F
-        if self.two_pass:
+        main = torch.cuda.current_stream()
+        if self.early and decoded is None:                    # called on its own: decode now (still on the side stream)
+            decoded = self._start_decode()
+        if self.two_pass or self.early:
+            if decoded is not None:
+                main.wait_event(decoded[0])
             act = M_.moe_mm_i8(xq_s, R, self.gu8, self.gu[2], off, ts, mt, 2 * F, 3, xs_s)
         else:
             act = M_.moe_mm(xq_s, R, *self.gu, off, ts, mt, 2 * F, 3, xs_s)
         xq2, xs2 = S.act_quant(act, R + M_.TM)
-        if self.two_pass:
+        if self.two_pass or self.early:
+            if decoded is not None:
+                main.wait_event(decoded[1])
             return M_.moe_mm_i8(xq2, R, self.dn8, self.dn[2], off, ts, mt, D, 1, xs2)
         return M_.moe_mm(xq2, R, *self.dn, off, ts, mt, D, 1, xs2)
 
@@ -35,10 +65,13 @@ class MoeBlock:
         """h bf16 [L, D] (L a multiple of 128), router logits f32 [L, E] -> new residual stream bf16 [L, D]."""
         L = h.shape[0]
         R = L * self.k
+        decoded = self._start_decode() if self.early else None
         xq, xs = S.rmsnorm_quant(h, self.nw, self.eps, L)
         inds, scores = M_.router_topk(logits, self.k)
         pos, tok, _, off, ts, mt = M_.route_sort(inds, self.E, M_.TM)
         xq_s, xs_s = M_.gather_rows(xq, xs, tok, R)
-        yd = self.experts(xq_s, xs_s, R, off, ts, mt)
+        yd = self.experts(xq_s, xs_s, R, off, ts, mt, decoded)
         hout, _, _ = M_.moe_combine(yd, pos, scores, h, self.nw, self.eps, L, quant=False)
+        if self.early:
+            torch.cuda.current_stream().wait_stream(self.side)
         return hout
