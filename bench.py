@@ -254,16 +254,21 @@ def build_moe_block(pkg, torch, cfg=OLMOE, shard=(0, 1), seed=0, two_pass=False)
             c, b, s_, _, _ = F.quantize_device(w.contiguous(), want_qw=False)
             cs.append(c); bs.append(b); ss.append(s_)
         return torch.stack(cs), torch.stack(bs), torch.stack(ss)
-    return pkg.fused_moe.MoeBlock(pack(2 * Fd, D, 1, perm), pack(D, Fd, 2), e1 - e0, cfg["topk"], D, Fd, two_pass=two_pass)
+    # with experts sharded over ranks the expert-parallel layer runs its own early decode of the local experts
+    return pkg.fused_moe.MoeBlock(pack(2 * Fd, D, 1, perm), pack(D, Fd, 2), e1 - e0, cfg["topk"], D, Fd, two_pass=two_pass,
+                                  early_decode=world == 1)
 
 
-def bench_moe(pkg, torch, dist=None, reps=5):
+def bench_moe(pkg, torch, dist=None, reps=5, weak=False, blk=None):
     """OLMoE-shaped MoE half-block at 4096 tokens: quant -> route -> (dispatch) -> two grouped GEMMs -> (return) -> combine.
-    With a process group: experts sharded by rank, tokens split by rank, NCCL all-to-all for dispatch and return."""
-    c = OLMOE
+    With a process group: experts sharded by rank, tokens split by rank, dispatch and return over NVLink.
+    weak: 4096 tokens PER RANK instead of in total."""
+    c = dict(OLMOE)
     world = dist.get_world_size() if dist is not None else 1
     rank = dist.get_rank() if dist is not None else 0
-    blk = build_moe_block(pkg, torch, shard=(rank, world))
+    if weak:
+        c["tokens"] = c["tokens"] * world
+    blk = blk if blk is not None else build_moe_block(pkg, torch, shard=(rank, world))
     Lr = c["tokens"] // world
     exchange = "none"
     if world > 1:
@@ -312,7 +317,7 @@ def bench_moe(pkg, torch, dist=None, reps=5):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     ops = 2 * c["tokens"] * c["topk"] * 3 * c["F"] * c["D"]
-    return dict(ms_per_half_block=ms, tokens_per_s_one_layer=c["tokens"] / ms * 1e3,
+    return dict(ms_per_half_block=ms, tokens=c["tokens"], tokens_per_s_one_layer=c["tokens"] / ms * 1e3,
                 tokens_per_s_16_layers=c["tokens"] / (ms * c["layers"]) * 1e3, tops=ops / ms / 1e9,
                 parallelism="single GPU" if world == 1 else f"ep{world}: {c['E'] // world} experts and {Lr} tokens per GPU, {exchange}")
 
@@ -494,6 +499,12 @@ def run_ours(args):
         line["moe"] = bench_moe(pkg, torch, dist if world > 1 else None)
     except Exception as e:   # noqa: BLE001
         line["moe"] = dict(error=f"{type(e).__name__}: {e}")
+    if world > 1:
+        torch.cuda.empty_cache()
+        try:       # the same half-block with 4096 tokens per GPU (weak scaling of the expert-parallel path)
+            line["moe_weak"] = bench_moe(pkg, torch, dist, weak=True)
+        except Exception as e:   # noqa: BLE001
+            line["moe_weak"] = dict(error=f"{type(e).__name__}: {e}")
     if world == 1:
         torch.cuda.empty_cache()
         try:       # whole-model time to first token and decode tokens/s through the fused callers (attention included)

@@ -92,6 +92,13 @@ int scmx_swiglu_quant(const int32_t* acc, const float* xscale, const float* wsca
  * gate-value check the reference runs in e2e/test_sc_kernels.py:80-93. */
 int scmx_swiglu(const uint16_t* g, const uint16_t* u, int64_t n, uint16_t* out, void* stream);
 
+/* Rotated-input quantization: every 32-wide block of a row times a +-1 sign vector (signs f32 [K]) and the 32-point
+ * Hadamard transform (float32 butterflies in the reference's order), scaled by 1/sqrt(32), rounded to bf16; then per-token
+ * INT8 as scmx_act_quant.  Rows M..Mp-1 come out as zero codes with scale 0.  Replaces sc_kernels.rot_quant
+ * (e2e/sc_kernels.py:234-275,572-582), the input side of weights packed in the rotated basis.  K % 32 == 0, K <= 8192. */
+int scmx_rot_quant(const uint16_t* x, const float* signs, int64_t M, int64_t K, int64_t Mp, int8_t* xq, float* xs,
+                   void* stream);
+
 /* q/k/v epilogue between the fused q|k|v projection and attention.  src is the bf16 GEMM output y [L, (hq+2hk)d]
  * (src_is_acc = 0) or its int32 accumulators with xscale [L] and wscale [(hq+2hk)d] (src_is_acc != 0).  q and k get
  * T(w * T(x * inv)): per head over d values with qn / kn bf16 [d] (full = 0), or over the whole hq*d-wide q and hk*d-wide

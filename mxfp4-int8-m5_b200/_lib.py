@@ -45,6 +45,7 @@ SIGNATURES = {
     "scmx_res_epilogue": [c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp],
     "scmx_swiglu_quant": [c_vp, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp, c_vp],
     "scmx_swiglu": [c_vp, c_vp, c_i64, c_vp, c_vp],
+    "scmx_rot_quant": [c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp],
     "scmx_qkv_norm": [c_vp, c_int, c_vp, c_vp, c_vp, c_vp, c_float, c_i64, c_int, c_int, c_int, c_int, c_vp, c_vp, c_i64, c_i64, c_vp, c_vp,
                       c_i64, c_vp, c_vp, c_i64, c_i64, c_vp],
     "scmx_attn_decode": [c_vp, c_vp, c_vp, c_i64, c_vp, c_i64, c_float, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp],

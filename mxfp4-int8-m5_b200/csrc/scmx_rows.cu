@@ -544,6 +544,63 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const int8_t* __restri
     if (lane == 0 && p < rows_s) ds[p] = xs[t];
 }
 
+// ---- rotated-input quantization --------------------------------------------------------------------------------------------
+// Every 32-wide block of the row is multiplied by a +-1 sign vector and by the 32-point Hadamard matrix, scaled by 1/sqrt(32),
+// rounded to bf16, then the row is quantized per token like act_quant.  The float32 butterflies run in the order of
+// e2e/sc_kernels.py:234-275 (two stages inside a thread's 4 values, three across the 8 threads of a block: the thread whose
+// index has bit h set computes partner - own, the other own + partner), so the sums round identically.
+constexpr float ROT_NORM = 0.17677669529663687f;
+
+__global__ void __launch_bounds__(256) rot_quant_kernel(const uint16_t* __restrict__ x, const float* __restrict__ signs, int64_t M,
+                                                        int K, int8_t* __restrict__ xq, float* __restrict__ xs) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float red[33];
+    constexpr int MAXJ = 8;                                   // K <= 8192
+    const int64_t row = blockIdx.x;
+    const int t = threadIdx.x;
+    float v[MAXJ][4];
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < MAXJ; ++j) {
+        const int p = 4 * (j * 256 + t);
+        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+        if (p < K && row < M) {
+            const uint2 r = *reinterpret_cast<const uint2*>(x + row * K + p);
+            const float4 sg = *reinterpret_cast<const float4*>(signs + p);
+            a0 = __fmul_rn(__uint_as_float(r.x << 16), sg.x);
+            a1 = __fmul_rn(__uint_as_float(r.x & 0xFFFF0000u), sg.y);
+            a2 = __fmul_rn(__uint_as_float(r.y << 16), sg.z);
+            a3 = __fmul_rn(__uint_as_float(r.y & 0xFFFF0000u), sg.w);
+        }
+        float b0 = __fadd_rn(a0, a1), b1 = __fsub_rn(a0, a1), b2 = __fadd_rn(a2, a3), b3 = __fsub_rn(a2, a3);
+        a0 = __fadd_rn(b0, b2); a1 = __fadd_rn(b1, b3); a2 = __fsub_rn(b0, b2); a3 = __fsub_rn(b1, b3);
+#pragma unroll
+        for (int h = 1; h < 8; h <<= 1) {                     // every lane takes part: the trip count is uniform
+            const float c0 = __shfl_xor_sync(0xffffffffu, a0, h), c1 = __shfl_xor_sync(0xffffffffu, a1, h);
+            const float c2 = __shfl_xor_sync(0xffffffffu, a2, h), c3 = __shfl_xor_sync(0xffffffffu, a3, h);
+            if (t & h) {
+                a0 = __fsub_rn(c0, a0); a1 = __fsub_rn(c1, a1); a2 = __fsub_rn(c2, a2); a3 = __fsub_rn(c3, a3);
+            } else {
+                a0 = __fadd_rn(a0, c0); a1 = __fadd_rn(a1, c1); a2 = __fadd_rn(a2, c2); a3 = __fadd_rn(a3, c3);
+            }
+        }
+        v[j][0] = rbf(__fmul_rn(a0, ROT_NORM)); v[j][1] = rbf(__fmul_rn(a1, ROT_NORM));
+        v[j][2] = rbf(__fmul_rn(a2, ROT_NORM)); v[j][3] = rbf(__fmul_rn(a3, ROT_NORM));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) amax = fmaxf(amax, fabsf(v[j][i]));
+    }
+    amax = block_max(amax, red);
+    float s, qi;
+    quant_scale(amax, s, qi);
+#pragma unroll
+    for (int j = 0; j < MAXJ; ++j) {
+        const int p = 4 * (j * 256 + t);
+        if (p < K) *reinterpret_cast<uint32_t*>(xq + row * K + p) = quant4(v[j][0], v[j][1], v[j][2], v[j][3], qi);
+    }
+    if (t == 0) xs[row] = s;
+}
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 }  // namespace scmx
@@ -690,3 +747,14 @@ extern "C" int scmx_rmsnorm_quant_seg(const uint16_t* x, const uint16_t* nw, flo
     return SCMX_OK;
 }
 
+
+extern "C" int scmx_rot_quant(const uint16_t* x, const float* signs, int64_t M, int64_t K, int64_t Mp, int8_t* xq, float* xs,
+                              void* stream) {
+    SCMX_REQUIRE(M >= 0 && Mp >= M && K > 0 && K % 32 == 0 && K <= 8192, SCMX_EINVAL,
+                 "rot_quant: need M <= Mp, K %% 32 == 0 and K <= 8192 (M=%lld Mp=%lld K=%lld)", (long long)M, (long long)Mp, (long long)K);
+    SCMX_REQUIRE(aligned16(x) && aligned16(signs) && aligned16(xq), SCMX_EINVAL, "rot_quant: buffers must be 16-byte aligned");
+    if (Mp == 0) return SCMX_OK;
+    launch_pdl(rot_quant_kernel, dim3((unsigned)Mp), dim3(256), 0, (cudaStream_t)stream, x, signs, M, (int)K, xq, xs);
+    SCMX_LAUNCH_OK("rot_quant_kernel");
+    return SCMX_OK;
+}

@@ -11,7 +11,7 @@
 
 epilogue="row" is the ablation that keeps INT32 GEMM outputs and applies scales, residuals, SwiGLU and the q/k norms in row
 kernels (e2e/fused_qwen3.py:237-288).  With overlap=True the 4-bit -> INT8 decode of the next weight runs on a side stream
-under the current GEMM.  Rotated inputs (rot=...) are not part of this path.
+under the current GEMM.  rot=True / "down" quantizes rotated inputs (rot_quant) for packs made in the rotated basis.
 """
 import numpy as np
 import torch
@@ -72,8 +72,10 @@ class FusedQwen3:
         """model: host_model.CausalLM on the GPU; packed: {"layers.{i}.{path}": (codes, bcodes, wscale)}.  resident keeps the
         INT8 operands decoded; fuse_rope=False applies the rotary embedding and the cache append with torch ops instead of
         inside the q/k/v kernel.  `compiled` is accepted for signature compatibility (there is no tracing compiler here)."""
-        if rot:
-            raise NotImplementedError("rotated-input packs are outside this path")
+        # rot: inputs rotated before INT8 (sc_kernels.rot_quant) for weights packed in the rotated basis; rot="down": only the
+        # down projection's input (e2e/fused_qwen3.py:88-90).  Producing such packs (GPTQ in the rotated basis) is not part
+        # of this library; they load through packed_io like any other pack.
+        self.rot, self._signs = rot, {}
         assert epilogue in ("gemm", "row")
         self.fmt = fmt if fmt is not None else F.Format()
         S.set_format(self.fmt)
@@ -103,11 +105,21 @@ class FusedQwen3:
     def weight_bytes(self):
         return sum(w.nbytes() for _, ws in self.layers for w in ws.values())
 
+    def signs(self, K):
+        if K not in self._signs:
+            self._signs[K] = S.rot_signs(K, self.inv_freq.device)
+        return self._signs[K]
+
     def rms_q(self, h, nw, Mp=None):
-        return S.rmsnorm_quant(h, nw, self.eps, Mp)
+        if self.rot is not True:
+            return S.rmsnorm_quant(h, nw, self.eps, Mp)
+        xn = S.rmsnorm_quant_n(h, nw, self.eps, Mp)[2]
+        return S.rot_quant(xn[:h.shape[0]], self.signs(h.shape[1]), Mp)
 
     def act_q(self, x, Mp=None, nt=256, down=False):
-        return S.act_quant(x, Mp)
+        if not (self.rot is True or (self.rot == "down" and down)):
+            return S.act_quant(x, Mp)
+        return S.rot_quant(x, self.signs(x.shape[1]), Mp)
 
     def _rec(self, i, g, x, xq, wq, acc):
         if self.record is not None and i in self.record_layers:

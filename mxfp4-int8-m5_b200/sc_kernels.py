@@ -174,6 +174,25 @@ def sc_swiglu(g, u):
     return out
 
 
+def rot_signs(K, device="cuda"):
+    """The +-1 sign vector for input width K: numpy.random.default_rng(0).choice([-1, 1], K), one per width so that q/k/v
+    and gate/up share a rotated input (e2e/sc_kernels.py:566-569)."""
+    return torch.from_numpy(np.random.default_rng(0).choice([-1.0, 1.0], size=K).astype(np.float32)).to(device)
+
+
+def rot_quant(x, signs, Mp=None, nt=512, deps=()):
+    """x bf16 [M, K] -> (xq int8 [Mp, K], xscale f32 [Mp]): sign flip and 32-point Hadamard rotation of each 32-wide block,
+    then per-token INT8."""
+    _lib.require_cuda(x, signs)
+    M, K = _bf16(x).shape
+    assert signs.shape == (K,) and signs.dtype == torch.float32
+    Mp = Mp or pad_rows(M)
+    xq = torch.empty((Mp, K), dtype=torch.int8, device=x.device)
+    xs = torch.empty(Mp, dtype=torch.float32, device=x.device)
+    _lib.call("scmx_rot_quant", _lib.ptr(x), _lib.ptr(signs), M, K, Mp, _lib.ptr(xq), _lib.ptr(xs), _lib.stream())
+    return xq, xs
+
+
 def rope_inv_freq(d, base, device="cuda"):
     """f32 [d/2]: base^(-2i/d), the frequencies of a half-split (non-interleaved) rotary embedding."""
     i = torch.arange(0, d, 2, dtype=torch.float64, device=device)   # device=None: torch's current default device

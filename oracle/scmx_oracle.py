@@ -370,6 +370,40 @@ def rmsnorm_quant(x, w, eps, Mp=None):
 
 
 # ---------------------------------------------------------------------------------------------------------------
+# rotated-input quantization, e2e/sc_kernels.py:234-275
+# ---------------------------------------------------------------------------------------------------------------
+
+def rot_signs(K):
+    """e2e/sc_kernels.py:566-569."""
+    return np.random.default_rng(0).choice([-1.0, 1.0], size=K).astype(np.float32)
+
+
+def rot_quant(x, signs, Mp=None):
+    """x (bf16 values) [M, K] -> (xq int8 [Mp, K], xs f32 [Mp]).  Per 32-wide block: y = H32 (x * signs) / sqrt(32) with the
+    float32 butterfly order of the reference's kernel (element 4t + i of a block belongs to thread t = 0..7: stages over
+    i with strides 1 and 2, then over t with strides 1, 2, 4; the side whose index bit is set computes partner - own),
+    rounded to bf16; then act_quant."""
+    x = np.asarray(x, np.float32)
+    M, K = x.shape
+    a = (x * np.asarray(signs, np.float32)[None, :]).astype(np.float32).reshape(M, K // 32, 8, 4)   # [.., t, i]
+    f = np.float32
+    b = np.empty_like(a)
+    b[..., 0], b[..., 1] = a[..., 0] + a[..., 1], a[..., 0] - a[..., 1]
+    b[..., 2], b[..., 3] = a[..., 2] + a[..., 3], a[..., 2] - a[..., 3]
+    a = np.empty_like(b)
+    a[..., 0], a[..., 1] = b[..., 0] + b[..., 2], b[..., 1] + b[..., 3]
+    a[..., 2], a[..., 3] = b[..., 0] - b[..., 2], b[..., 1] - b[..., 3]
+    a = a.astype(f)
+    t = np.arange(8)
+    for h in (1, 2, 4):
+        c = a[:, :, t ^ h, :]
+        hi = ((t & h) != 0)[None, None, :, None]
+        a = np.where(hi, c - a, a + c).astype(f)
+    y = bf16_round((a * f(0.17677669529663687)).astype(f)).reshape(M, K)
+    return act_quant(y, Mp)
+
+
+# ---------------------------------------------------------------------------------------------------------------
 # q/k/v epilogue before attention (the callers' glue), e2e/sc_kernels.py:333-423,597-637; rotary step as
 # mlx.nn.RoPE(traditional=False) which e2e/fused_qwen3.py:197-203 calls
 # ---------------------------------------------------------------------------------------------------------------

@@ -133,3 +133,19 @@ def test_gather_rows(scmx):
     tok = rng.integers(0, 50, 300 + 128).astype(np.int32)
     dq, ds = scmx.sc_moe.gather_rows(cuda(xq), cuda(xs), cuda(tok), 300)
     assert np.array_equal(dq.cpu().numpy(), xq[tok]) and np.array_equal(ds.cpu().numpy(), xs[tok[:300]])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,K", [(5, 96), (130, 2048), (3, 6144), (1, 8192)])
+def test_rot_quant_matches_oracle(scmx, oracle, M, K):
+    rng = np.random.default_rng(M + K)
+    x = oracle.bf16_round((rng.standard_normal((M, K)) * rng.lognormal(0, 1, (1, K))).astype(np.float32))
+    x[0, :32] = 0                                         # a zero block
+    signs = oracle.rot_signs(K)
+    Mp = M + 3
+    xq, xs = scmx.sc_kernels.rot_quant(to_bf16_cuda(x), scmx.sc_kernels.rot_signs(K), Mp)
+    oq, os_ = oracle.rot_quant(x, signs, Mp)
+    assert np.array_equal(xq.cpu().numpy(), oq) and np.array_equal(xs.cpu().numpy(), os_)
+    assert not xq[M:].any() and not xs[M:].any()
+    z, zs = scmx.sc_kernels.rot_quant(torch.zeros((2, K), dtype=torch.bfloat16, device="cuda"), scmx.sc_kernels.rot_signs(K), 2)
+    assert not z.any() and not zs.any()

@@ -108,3 +108,21 @@ def test_moe_combine_order(oracle):
     for j in range(k):
         acc = oracle.bf16_round(oracle.bf16_round(y[pos[t * k + j]] * sc[t, j]) + acc)
     assert np.array_equal(h[t], oracle.bf16_round(res[t] + acc)) and np.array_equal(h[M:], res[M:])
+
+
+def test_rot_quant_is_the_sign_flipped_block_hadamard_transform(oracle):
+    """The butterfly order restated from e2e/sc_kernels.py:234-275 against the definition: y = H32 (x * signs) / sqrt(32) per
+    32-wide block in float64, rounded to bf16, then per-token INT8 (a float32 rounding of a sum may move a code by one)."""
+    rng = np.random.default_rng(11)
+    M, K = 7, 256
+    x = oracle.bf16_round((rng.standard_normal((M, K)) * rng.lognormal(0, 1, (1, K))).astype(np.float32))
+    signs = oracle.rot_signs(K)
+    assert set(np.unique(signs)) == {-1.0, 1.0} and np.array_equal(signs[:8], np.random.default_rng(0).choice([-1.0, 1.0], size=K)[:8])
+    H = np.array([[1.0]])
+    while H.shape[0] < 32:
+        H = np.block([[H, H], [H, -H]])
+    y = ((x.astype(np.float64) * signs).reshape(M, K // 32, 32) @ H.T / np.sqrt(32)).reshape(M, K)
+    want_q, want_s = oracle.act_quant(oracle.bf16_round(y.astype(np.float32)), M)
+    got_q, got_s = oracle.rot_quant(x, signs, M)
+    assert np.abs(got_q.astype(int) - want_q.astype(int)).max() <= 1
+    assert (got_q != want_q).mean() < 0.01 and np.allclose(got_s, want_s, rtol=1e-2)
