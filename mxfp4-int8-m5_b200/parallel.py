@@ -207,7 +207,7 @@ class PeerExpertParallelMoe:
         # With few experts per rank the whole rank's expert weights decode to a modest INT8 buffer: the decode is started on a
         # side stream at the top of every step and overlaps routing, dispatch and the barrier (weights do not depend on them).
         F = block_local.F
-        self.early_decode = El * 3 * F * D <= (96 << 20)
+        self.early_decode = El * 3 * F * D <= (1 << 30)
         if self.early_decode:
             self.side = torch.cuda.Stream(device=dev)
             self.gu8 = torch.empty((El * 2 * F, D), dtype=torch.int8, device=dev)
