@@ -8,7 +8,8 @@
 // again from memory for every layer.
 //
 // Per layer (5 barriers):
-//   P1  RMSNorm + INT8 of h (each CTA, shared memory) -> q|k|v GEMV rows spread over all warps -> y (bf16)
+//   P1  RMSNorm + INT8 of h (each CTA, shared memory; the first weight loads of every warp are already in flight) ->
+//       q|k|v GEMV rows spread over all warps -> y (bf16)
 //   P3  per (kv head, split) CTA: q/k RMSNorm + rotary embedding of the new token, cache append, attention over its
 //       positions -> partial softmax states; the last split of a kv head to finish combines them -> o
 //   P4  INT8 of o -> o-projection GEMV + residual -> h
@@ -131,7 +132,7 @@ __device__ __forceinline__ float amax8(const uint4& r) {
     return m;
 }
 
-__device__ __noinline__ float pro_act(const uint16_t* x, int K) {
+__device__ __forceinline__ float pro_act(const uint16_t* x, int K) {
     const int nv = K / 8;
     float amax = 0.0f;
     for (int v = threadIdx.x; v < nv; v += MK_THREADS) {
@@ -142,7 +143,7 @@ __device__ __noinline__ float pro_act(const uint16_t* x, int K) {
     return quantize_staged(nv, amax);
 }
 
-__device__ __noinline__ float pro_norm(const uint16_t* x, const uint16_t* nw, float eps, int K) {
+__device__ __forceinline__ float pro_norm(const uint16_t* x, const uint16_t* nw, float eps, int K) {
     const int nv = K / 8;
     double ss = 0.0;
     for (int v = threadIdx.x; v < nv; v += MK_THREADS) {
@@ -232,24 +233,30 @@ __device__ __forceinline__ void compute_chunk(const RowChunk& c, const int8_t* x
     }
 }
 
-__device__ __noinline__ void run_job(const uint32_t* __restrict__ codes, const uint8_t* __restrict__ bcodes,
-                                     const float* __restrict__ wscale, int N, int K, float xs, int epi, const uint16_t* res,
-                                     uint16_t* out) {
+// One GEMV phase: the warp's first chunk of weights is requested, then the CTA computes the INT8 input row in shared memory
+// (NORM: RMSNorm with weights nw first), then the chunks are consumed.  The weights do not depend on the activations, so
+// their first round trip to memory runs under the prologue.
+template <bool NORM>
+__device__ __noinline__ void run_phase(const uint32_t* __restrict__ codes, const uint8_t* __restrict__ bcodes,
+                                       const float* __restrict__ wscale, int N, int K, const uint16_t* x, const uint16_t* nw,
+                                       float eps, int epi, const uint16_t* res, uint16_t* out) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     // row groups are dealt warp-major, so that a job with fewer groups than warps still uses every SM
-    const int gw = warp * gridDim.x + blockIdx.x, nw = gridDim.x * MK_WARPS;
+    const int gw = warp * gridDim.x + blockIdx.x, nw_ = gridDim.x * MK_WARPS;
     const int steps = K / 1024, wpr = K / 8, bcr = K / 128, groups = N / 4;
     const int8_t* xq = sm.xq;
-    if (gw >= groups) return;
+    const bool work = gw < groups;
     RowChunk cur, nxt;
     int grp = gw, s0 = 0;
-    load_chunk(cur, codes, bcodes, grp * 4, 0, steps, wpr, bcr, lane);
+    if (work) load_chunk(cur, codes, bcodes, grp * 4, 0, steps, wpr, bcr, lane);
+    const float xs = NORM ? pro_norm(x, nw, eps, K) : pro_act(x, K);     // every thread: contains CTA barriers
+    if (!work) return;
     int tot[4] = {0, 0, 0, 0};
     for (;;) {
         // the chunk after this one: the next steps of the same rows, or the first steps of the warp's next row group
         int ngrp = grp, ns0 = s0 + MK_UNROLL;
         if (ns0 >= steps) {
-            ngrp = grp + nw;
+            ngrp = grp + nw_;
             ns0 = 0;
         }
         const bool more = ngrp < groups;
@@ -383,9 +390,7 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_step_kernel(const MkArgs
         const scmx_decode_layer L = a.layers[li];             // by value: the pointers sit in registers for the whole layer
         // P1: input RMSNorm + INT8, q|k|v projection
         if (li > 0) MK_BARRIER();                             // h of the previous layer complete
-        float xs = pro_norm(a.h, L.ln_in, a.eps, D);
-        MK_MARK();
-        run_job(L.codes[0], L.bcodes[0], L.wscale[0], NQKV, D, xs, 1, nullptr, a.y);
+        run_phase<true>(L.codes[0], L.bcodes[0], L.wscale[0], NQKV, D, a.h, L.ln_in, a.eps, 1, nullptr, a.y);
         // P3: attention of one (kv head, split) per CTA
         MK_BARRIER();
         {
@@ -418,19 +423,13 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_step_kernel(const MkArgs
         }
         // P4: combine the splits, INT8 of o, o-projection + residual
         MK_BARRIER();
-        xs = pro_act(a.o, QD);
-        MK_MARK();
-        run_job(L.codes[1], L.bcodes[1], L.wscale[1], D, QD, xs, 2, a.h, a.h);
+        run_phase<false>(L.codes[1], L.bcodes[1], L.wscale[1], D, QD, a.o, nullptr, 0.0f, 2, a.h, a.h);
         // P5: post-attention RMSNorm + INT8, gate|up projection with SwiGLU
         MK_BARRIER();
-        xs = pro_norm(a.h, L.ln_post, a.eps, D);
-        MK_MARK();
-        run_job(L.codes[2], L.bcodes[2], L.wscale[2], 2 * F, D, xs, 3, nullptr, a.act);
+        run_phase<true>(L.codes[2], L.bcodes[2], L.wscale[2], 2 * F, D, a.h, L.ln_post, a.eps, 3, nullptr, a.act);
         // P6: INT8 of act, down projection + residual
         MK_BARRIER();
-        xs = pro_act(a.act, F);
-        MK_MARK();
-        run_job(L.codes[3], L.bcodes[3], L.wscale[3], D, F, xs, 2, a.h, a.h);
+        run_phase<false>(L.codes[3], L.bcodes[3], L.wscale[3], D, F, a.act, nullptr, 0.0f, 2, a.h, a.h);
     }
 #undef MK_BARRIER
 #undef MK_MARK

@@ -94,6 +94,15 @@ class FusedOlmoe:
             for path in ATTN:
                 setattr(layer.self_attn, path.split(".")[1], None)
             layer.mlp.switch_mlp = None
+        # Expert weights of the NEXT layer are decoded to INT8 on a side stream while the current layer runs (two rotating
+        # buffer pairs), when the INT8 copy of one layer's experts is at most 1 GiB; the grouped GEMMs then read those
+        # (moe_mm_i8).  Otherwise moe_mm decodes groups of experts between its own GEMM passes.
+        F2, D = 2 * Fi, a.hidden_size
+        self.prefetch = E * (F2 * D + D * Fi) <= (1 << 30)
+        if self.prefetch:
+            self.ring = [(torch.empty((E * F2, D), dtype=torch.int8, device=dev),
+                          torch.empty((E * D, Fi), dtype=torch.int8, device=dev)) for _ in range(2)]
+            self.side = torch.cuda.Stream(device=dev)
         self.inv_freq = S.rope_inv_freq(a.head_dim, a.rope_theta, dev)
         self.rope_cs = S.rope_table(self.inv_freq, 16384)          # cos / sin of the first positions, read by the q/k/v kernel
         self.record, self.record_layers = None, ()
@@ -111,8 +120,23 @@ class FusedOlmoe:
         logits = torch.nn.functional.linear(xn[:M], layer.mlp.gate.weight)
         return M_.router_topk(logits.float(), self.args.num_experts_per_tok)
 
-    def experts(self, ex, xq, xs, inds, L):
-        """INT8 rows + routing -> (sorted expert outputs yd bf16 [R, D], pos)."""
+    def _decode_experts(self, i):
+        """Layer i's experts -> INT8 in ring[i % 2] on the side stream; waits for the GEMMs that last read that pair."""
+        a = self.args
+        E, F2, D = a.num_experts, 2 * a.intermediate_size, a.hidden_size
+        (cg, bg, _), (cd, bd, _) = self.layers[i][2]["gu"], self.layers[i][2]["down"]
+        gu8, dn8 = self.ring[i % 2]
+        with torch.cuda.stream(self.side):
+            if i >= 2:
+                self.side.wait_event(self._done[i - 2])
+            S.unpack_i8(cg.reshape(-1), bg.reshape(E * F2, -1), E * F2, D, out=gu8)
+            S.unpack_i8(cd.reshape(-1), bd.reshape(E * D, -1), E * D, F2 // 2, out=dn8)
+            self._ready[i] = torch.cuda.Event()
+            self._ready[i].record(self.side)
+
+    def experts(self, ex, xq, xs, inds, L, decoded=None):
+        """INT8 rows + routing -> (sorted expert outputs yd bf16 [R, D], pos).  decoded: (gu8, dn8) INT8 copies of this
+        layer's experts when they were decoded ahead."""
         a = self.args
         k, E, F2, D = a.num_experts_per_tok, a.num_experts, 2 * a.intermediate_size, a.hidden_size
         R = L * k
@@ -120,6 +144,11 @@ class FusedOlmoe:
         pos, tok_p, e_sorted, off, tstart, maxt = M_.route_sort(inds, E, M_.TM)
         xq_s, xs_s = M_.gather_rows(xq, xs, tok_p, R)
         (cg, bg, sg), (cd, bd, sd) = ex["gu"], ex["down"]
+        if decoded is not None:
+            act = M_.moe_mm_i8(xq_s, R, decoded[0], sg, off, tstart, maxt, F2, 3, xs_s)
+            xq2, xs2 = S.act_quant(act, R + M_.TM)
+            yd = M_.moe_mm_i8(xq2, R, decoded[1], sd, off, tstart, maxt, D, 1, xs2)
+            return yd, pos, (xq_s, xs_s, act, xq2, xs2, e_sorted)
         if two_pass:
             act = M_.moe_mm_i8(xq_s, R, M_.unpack_experts(cg, bg, F2, D), sg, off, tstart, maxt, F2, 3, xs_s)
         else:
@@ -142,9 +171,16 @@ class FusedOlmoe:
             h = torch.nn.functional.pad(h, (0, 0, 0, Mp - L))
         h = h.contiguous()
         nl = len(self.layers)
+        main = torch.cuda.current_stream()
+        if self.prefetch:
+            self._ready, self._done = [None] * nl, [None] * nl
+            self.side.wait_stream(main)
+            self._decode_experts(0)
         xq, xs = S.rmsnorm_quant(h, self.layers[0][0].input_layernorm.weight, self.eps, Mp)
         for i, (layer, ws, ex) in enumerate(self.layers):
             at, c = layer.self_attn, cache[i]
+            if self.prefetch and i + 1 < nl:
+                self._decode_experts(i + 1)                    # under this layer's attention and GEMMs
             wq, wo = ws["qkv"], ws["o"]
             y = S.mm_epi(xq, wq.unpack(), xs, wq.wscale, 1)
             q, kk, v = S.qkv_fullnorm_y(y, at.q_norm.weight, at.k_norm.weight, self.eps, L, H, d,
@@ -155,12 +191,19 @@ class FusedOlmoe:
             h = S.mm_epi(xq, wo.unpack(), xs, wo.wscale, 2, res=h)
             xq, xs, xn = S.rmsnorm_quant_n(h, layer.post_attention_layernorm.weight, self.eps)
             inds, scores = self.route(layer, xn, L)
-            yd, pos, rec = self.experts(ex, xq, xs, inds, L)
+            if self.prefetch:
+                main.wait_event(self._ready[i])
+            yd, pos, rec = self.experts(ex, xq, xs, inds, L, self.ring[i % 2] if self.prefetch else None)
+            if self.prefetch:
+                self._done[i] = torch.cuda.Event()
+                self._done[i].record(main)
             nn = self.layers[i + 1][0].input_layernorm.weight if i + 1 < nl else self.model.model.norm.weight
             h_in = h
             h, xq, xs = M_.moe_combine(yd, pos, scores, h, nn, self.eps, L)
             if self.record is not None and i in self.record_layers:
                 self.record[(i, "experts")] = (h_in, xn, inds, scores, yd, pos, *rec)
+        if self.prefetch:
+            main.wait_stream(self.side)
         xn = S.rmsnorm_quant_n(h, self.model.model.norm.weight, self.eps, Mp)[2]
         return xn[:L][None]
 
