@@ -91,6 +91,37 @@ def from_shift_layout(codes_u32, shifts, wscale, fmt=DEFAULT):
     return np.asarray(codes_u32, np.uint32).reshape(-1), bc.astype(np.uint8), np.asarray(wscale, np.float32)
 
 
+def pack_values(v, e, fmt=DEFAULT):
+    """Packing from E2M1 values v [N, K/32, 32] (levels 0, 0.5, 1, 1.5, 2, 3, 4, 6 with sign) and block exponents
+    e [N, K/32] instead of from weights - for roundings other than round-to-nearest that keep the exponents of the
+    unquantized weights, as the reference's GPTQ pack does (pack_ve, e2e/gptq_pack.py:29-47).  Host-side NumPy like the
+    other layout helpers.  Returns (codes uint32 [N*K/8], bcodes uint8 [N, K/128], wscale f32 [N], qw int8 [N, K]).
+    A non-finite exponent marks an all-zero block."""
+    assert fmt.block == 32 and tuple(fmt.mult) == (1, 2, 4, 8) and fmt.bc_bits == 2
+    v = np.asarray(v, np.float64)
+    e = np.asarray(e, np.float64)
+    n, nb, blk = v.shape
+    assert blk == 32 and e.shape == (n, nb) and nb % fmt.per_byte == 0
+    fin = np.isfinite(e)
+    hi = np.where(fin, e, -np.inf).max(-1, keepdims=True)
+    hi = np.where(np.isfinite(hi), hi, 0.0)
+    lo = np.where(fin, e, hi).min(-1, keepdims=True)
+    spread = np.where(fin, e, lo) - lo
+    if spread.max() > 3:
+        raise ValueError(f"block exponent spread {int(spread.max())} > 3: not INT8-embeddable")
+    levels = np.asarray(fmt.code_mag, np.float64) / 2
+    a = np.abs(v)
+    idx = np.searchsorted(levels, a)
+    if idx.max() > 7 or not np.array_equal(levels[np.minimum(idx, 7)], a):
+        raise ValueError("values are not E2M1 levels")
+    if np.any(a[~fin] != 0):
+        raise ValueError("a block without an exponent holds non-zero values")
+    code4 = (idx | ((v < 0) << 3)).astype(np.uint8).reshape(n, nb * 32)
+    shifts = spread.astype(np.uint8)
+    codes, bc, ws = pack_rows(code4, shifts, np.exp2(lo[:, 0] - 1).astype(np.float32), fmt)
+    return codes, bc, ws, decode_numpy(codes, bc, n, nb * 32, fmt).astype(np.int8)
+
+
 _DTYPE_CODE = {torch.float32: 0, torch.float64: 1, torch.bfloat16: 2}
 
 

@@ -188,6 +188,34 @@ def decode(codes, bc, n, k, fmt=DEFAULT):
     return np.where(c & 8, -mag, mag).astype(np.int8)
 
 
+def pack_values(v, e):
+    """Packing from E2M1 values v [N, K/32, 32] and block exponents e [N, K/32] instead of from weights: what a rounding
+    other than round-to-nearest (GPTQ) produces while keeping the exponents (e2e/gptq_pack.py:29-47, with
+    sim/mx_int8.py:92-109 for the INT8 embedding).  Returns (codes uint32 [N*K/8], shifts uint8 [N, K/32] one byte per block,
+    wscale f32 [N], qw int8 [N, K]).  A non-finite exponent marks an all-zero block (shift 0); the row exponent is the
+    minimum finite one (0 for a row without any)."""
+    v = np.asarray(v, np.float64)
+    e = np.asarray(e, np.float64)
+    n, nb, _ = v.shape
+    k = nb * BLOCK
+    fin = np.isfinite(e)
+    hi = np.where(fin, e, -np.inf).max(-1, keepdims=True)
+    hi = np.where(np.isfinite(hi), hi, 0.0)
+    lo = np.where(fin, e, hi).min(-1, keepdims=True)
+    shift_q = (np.where(fin, e, hi) - lo)                       # the embedding's shift (zero blocks: value 0 anyway)
+    q = 2 * v * np.exp2(shift_q)[..., None]
+    assert np.abs(q).max() <= 127 and np.all(q == np.round(q)), "not INT8-embeddable"
+    shifts = (np.where(fin, e, lo) - lo).astype(np.uint8)       # the stored block codes
+    a = np.abs(v.reshape(n, k))
+    lv = np.array(E2M1_X2, np.float64) / 2
+    idx = np.searchsorted(lv, a).astype(np.uint8)
+    assert idx.max() <= 7 and np.array_equal(lv[idx], a), "values are not E2M1 levels"
+    code4 = idx | ((v.reshape(n, k) < 0).astype(np.uint8) << 3)
+    c = code4.astype(np.uint32).reshape(n, k // 8, 8)
+    codes = np.bitwise_or.reduce(c << (4 * np.arange(8, dtype=np.uint32)), axis=-1).astype(np.uint32).reshape(-1)
+    return codes, shifts, np.exp2(lo[:, 0] - 1).astype(np.float32), q.reshape(n, k).astype(np.int8)
+
+
 def quantize(w, fmt=DEFAULT):
     """(N,K) float weights -> (codes, bcodes, wscale, qw) in the published SC-MXFP4 layout
     (e2e/sc_format.py:105-111: make_testcase.pack then from_shift_layout)."""

@@ -10,6 +10,8 @@ What is recorded (all inputs are stored as float32/int arrays so that no RNG str
   actq_*        quant_ref, the float32 activation-quant recipe (e2e/test_sc_kernels.py:21-26; the function's source
                 is extracted from the file because the module imports MLX at the top)
   perm_*        interleave_gate_up (e2e/sc_kernels.py:520-524; extracted the same way)
+  packve_*      gptq_pack.pack_ve: packing from (E2M1 values, block exponents) instead of weights, on values moved to
+                neighbouring levels the way a GPTQ rounding would (e2e/gptq_pack.py:29-47)
   config1       sha256 digests of the full 6144x2048 / 512x2048 case of the headline single-layer configuration
 """
 import ast
@@ -111,6 +113,24 @@ def main(ref):
 
     perm = _extract(os.path.join(ref, "e2e", "sc_kernels.py"), "interleave_gate_up")
     g["perm_768"] = perm(768).astype(np.int32)
+
+    # ---- packing from values and exponents (GPTQ-rounded tensors keep the exponents of the unquantized weights)
+    import gptq_pack
+    r2 = np.random.default_rng(77)
+    w = (r2.standard_normal((8, 256)) * 0.02 * r2.lognormal(0, 1.0, (1, 256))).astype(np.float64)
+    w[1, 32:64] = 0
+    e = mx_int8.constrain_spread(w, mx_int8.block_exponents(w, "search"))
+    v = mx_int8.blocks(mx_int8.dequant_mx(w, e)[0]) / 2.0 ** e[..., None]          # round-to-nearest E2M1 values
+    lv = mx_int8.E2M1
+    idx = np.searchsorted(lv, np.abs(v))
+    move = r2.random(v.shape) < 0.15                                                 # some weights go to a neighbouring level
+    idx2 = np.clip(idx + np.where(move, r2.choice([-1, 1], size=v.shape), 0), 0, 7)
+    sgn = np.where(v < 0, -1.0, np.where(v > 0, 1.0, r2.choice([-1.0, 1.0], size=v.shape)))
+    v2 = sgn * lv[idx2]
+    packed, shifts, wscale, qw = gptq_pack.pack_ve(v2, e)
+    g["packve_v"], g["packve_e"] = v2, e
+    g["packve_codes"], g["packve_shifts"] = packed.reshape(-1).view(np.uint32).copy(), shifts
+    g["packve_wscale"], g["packve_qw"] = wscale, qw
 
     np.savez_compressed(os.path.join(OUT, "reference_vectors.npz"), **g)
 

@@ -126,3 +126,31 @@ def test_rot_quant_is_the_sign_flipped_block_hadamard_transform(oracle):
     got_q, got_s = oracle.rot_quant(x, signs, M)
     assert np.abs(got_q.astype(int) - want_q.astype(int)).max() <= 1
     assert (got_q != want_q).mean() < 0.01 and np.allclose(got_s, want_s, rtol=1e-2)
+
+
+def test_pack_from_values_and_exponents(oracle, golden, scmx):
+    """pack_ve of the reference (e2e/gptq_pack.py:29-47) on values moved to neighbouring levels: the oracle's restatement and
+    the product's host-side helper reproduce its codes, shifts, row scales and INT8 values."""
+    v, e = golden["packve_v"], golden["packve_e"]
+    codes, shifts, ws, qw = oracle.pack_values(v, e)
+    assert np.array_equal(codes, golden["packve_codes"]) and np.array_equal(shifts, golden["packve_shifts"])
+    assert np.array_equal(ws, golden["packve_wscale"]) and np.array_equal(qw, golden["packve_qw"])
+    F = scmx.sc_format
+    c2, b2, w2, q2 = F.pack_values(v, e)
+    want = F.from_shift_layout(golden["packve_codes"], golden["packve_shifts"], golden["packve_wscale"])
+    assert np.array_equal(c2, want[0]) and np.array_equal(b2, want[1]) and np.array_equal(w2, want[2])
+    assert np.array_equal(q2, golden["packve_qw"])
+    # an all-zero block may carry no exponent; anything else there, or an off-grid value, is refused
+    e2 = e.copy()
+    v2 = v.copy()
+    v2[0, 0] = 0
+    e2[0, 0] = -np.inf
+    c3, b3, w3, q3 = F.pack_values(v2, e2)
+    assert not q3[0, :32].any() and np.array_equal(q3[1:], golden["packve_qw"][1:])
+    v2[0, 0, 0] = 1.0
+    with pytest.raises(ValueError):
+        F.pack_values(v2, e2)
+    v4 = v.copy()
+    v4[0, 0, 0] = 0.75
+    with pytest.raises(ValueError):
+        F.pack_values(v4, e)
