@@ -322,3 +322,23 @@ def test_persistent_decode_kernel_equals_kernel_chain(scmx):
     assert chain.generate(t1, c1, n).tolist() == mk.generate(t2, c2, n).tolist()
     mk.check_status()
     assert torch.equal(c1[1].k[:, :40 + n], c2[1].k[:, :40 + n])
+
+
+def test_fused_qwen3_rotated_inputs_path(scmx):
+    """rot=True / "down" route the INT8 quantization of the GEMM inputs through rot_quant (for packs made in the rotated
+    basis); with ordinary packs the outputs are simply different, finite numbers - this checks the wiring only."""
+    FQ, S = _mod("fused_qwen3"), _mod("sc_kernels")
+    model, a = _tiny("qwen3")
+    packed = FQ.pack_model(model)
+    ids = _ids(70, a.vocab_size, 19)
+    base = FQ.FusedQwen3(copy.deepcopy(model), packed)(ids)
+    for rot in (True, "down"):
+        f = FQ.FusedQwen3(copy.deepcopy(model), packed, rot=rot)
+        x = torch.randn((128, a.intermediate_size), device="cuda").to(torch.bfloat16)
+        q1, s1 = f.act_q(x, 128, down=True)
+        q2, s2 = S.rot_quant(x, S.rot_signs(a.intermediate_size), 128)
+        assert torch.equal(q1, q2) and torch.equal(s1, s2)
+        q3, _ = f.act_q(x, 128)
+        assert torch.equal(q3, q2) == (rot is True)
+        out = f(ids)
+        assert torch.isfinite(out.float()).all() and not torch.equal(out, base)
