@@ -57,6 +57,19 @@ class ClockSampler:
                                          stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
+        # nvidia-smi needs up to a second to start (longer on an 8-GPU node): wait for its first line, so that the timed
+        # region that follows is sampled from its start; lines written before it are not counted
+        self.skip = 0
+        if self.proc:
+            t0 = time.time()
+            while time.time() - t0 < 6.0:
+                try:
+                    self.skip = sum(1 for _ in open(self.path))
+                except OSError:
+                    self.skip = 0
+                if self.skip:
+                    break
+                time.sleep(0.02)
         return self
 
     def __exit__(self, *a):
@@ -69,7 +82,10 @@ class ClockSampler:
         if not self.path or not os.path.exists(self.path):
             return out
         sm, mx, reasons = [], [], set()
-        for line in open(self.path):
+        lines = open(self.path).read().splitlines()
+        if len(lines) > self.skip:             # the samples taken since the timed region began
+            lines = lines[self.skip:]
+        for line in lines:
             f = [c.strip() for c in line.split(",")]
             if len(f) < 9:
                 continue
@@ -432,6 +448,8 @@ def run_ours(args):
     # (126 MB), so every step streams its weights from HBM (no explicit flush needed).
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as cs:
+        for _ in range(2):                   # the sampler's start-up left the GPU idle for a moment: two more untimed steps
+            run()
         barrier()
         e0.record()
         for _ in range(args.steps):
