@@ -165,22 +165,38 @@ __global__ void __launch_bounds__(128) ep_return_kernel(const uint16_t* __restri
 
 // Row gather and activation quantization over a row count that lives on the device (rows beyond it are skipped; the tm rows
 // right after it are zero-filled so that the last M tile of the grouped GEMM reads defined data).
-__global__ void __launch_bounds__(128) gather_rows_dyn_kernel(const int8_t* __restrict__ xq, const float* __restrict__ xs,
+// The grids of the two kernels below are bounded (a few CTAs per SM) and stride over the rows that exist: the capacity
+// they are launched for is a worst case (every token of every rank routed here), the row count is known on the device only.
+__global__ void __launch_bounds__(256) gather_rows_dyn_kernel(const int8_t* __restrict__ xq, const float* __restrict__ xs,
                                                               const int32_t* __restrict__ tok, const int32_t* __restrict__ n_rows, int pad,
                                                               int K, int8_t* __restrict__ dq, float* __restrict__ ds) {
     pdl_launch_dependents();
     pdl_wait();
-    const int p = blockIdx.x, n = n_rows[0];
-    if (p >= n + pad) return;
-    uint4* dst = reinterpret_cast<uint4*>(dq + (size_t)p * K);
-    if (p >= n) {
-        for (int i = threadIdx.x; i < K / 16; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
-        return;
+    const int lane = threadIdx.x & 31, n = n_rows[0], nv = K / 16;
+    const int stride = gridDim.x * (blockDim.x >> 5);
+    for (int p = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); p < n + pad; p += stride) {   // a warp per row
+        uint4* dst = reinterpret_cast<uint4*>(dq + (size_t)p * K);
+        if (p >= n) {
+            for (int i = lane; i < nv; i += 32) dst[i] = make_uint4(0, 0, 0, 0);
+            continue;
+        }
+        const int t = tok[p];
+        const uint4* src = reinterpret_cast<const uint4*>(xq + (size_t)t * K);
+        for (int base = 0; base < nv; base += 32 * 8) {
+            uint4 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int i = base + j * 32 + lane;
+                if (i < nv) v[j] = src[i];
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int i = base + j * 32 + lane;
+                if (i < nv) dst[i] = v[j];
+            }
+        }
+        if (lane == 0) ds[p] = xs[t];
     }
-    const int t = tok[p];
-    const uint4* src = reinterpret_cast<const uint4*>(xq + (size_t)t * K);
-    for (int i = threadIdx.x; i < K / 16; i += blockDim.x) dst[i] = src[i];
-    if (threadIdx.x == 0) ds[p] = xs[t];
 }
 
 __global__ void __launch_bounds__(256) act_quant_dyn_kernel(const uint16_t* __restrict__ x, const int32_t* __restrict__ n_rows, int pad,
@@ -188,13 +204,13 @@ __global__ void __launch_bounds__(256) act_quant_dyn_kernel(const uint16_t* __re
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float red[33];
-    const int row = blockIdx.x, n = n_rows[0];
-    if (row >= n + pad) return;
+    const int n = n_rows[0];
+    for (int row = blockIdx.x; row < n + pad; row += gridDim.x) {     // uniform over the CTA: the barriers below are safe
     uint2* qrow = reinterpret_cast<uint2*>(xq + (size_t)row * K);
     if (row >= n) {
         for (int v = threadIdx.x; v < K / 8; v += blockDim.x) qrow[v] = make_uint2(0, 0);
         if (threadIdx.x == 0) xs[row] = 0.0f;
-        return;
+        continue;
     }
     const uint4* xrow = reinterpret_cast<const uint4*>(x + (size_t)row * K);
     float amax = 0.0f;
@@ -217,6 +233,7 @@ __global__ void __launch_bounds__(256) act_quant_dyn_kernel(const uint16_t* __re
         qrow[v] = make_uint2(quant4(f[0], f[1], f[2], f[3], qi), quant4(f[4], f[5], f[6], f[7], qi));
     }
     if (threadIdx.x == 0) xs[row] = s;
+    }
 }
 
 // All-gather by stores: this rank's contiguous block is written at the same offset into every rank's buffer (its own
@@ -310,8 +327,9 @@ extern "C" int scmx_ep_return(const uint16_t* y, const int32_t* ret_rank, const 
 extern "C" int scmx_gather_rows_dyn(const int8_t* xq, const float* xs, const int32_t* tok, const int32_t* n_rows, int64_t r_cap, int pad,
                                     int64_t K, int8_t* dst_q, float* dst_s, void* stream) {
     SCMX_REQUIRE(r_cap >= 0 && pad >= 0 && K > 0 && K % 16 == 0, SCMX_EINVAL, "gather_rows_dyn: K %% 16 != 0");
-    launch_pdl(gather_rows_dyn_kernel, dim3((unsigned)(r_cap + pad)), dim3(128), 0, (cudaStream_t)stream, xq, xs, tok, n_rows, pad, (int)K,
-               dst_q, dst_s);
+    const int64_t g_ctas = (r_cap + pad + 7) / 8;
+    launch_pdl(gather_rows_dyn_kernel, dim3((unsigned)(g_ctas < 148 * 8 ? g_ctas : 148 * 8)), dim3(256), 0, (cudaStream_t)stream, xq, xs, tok,
+               n_rows, pad, (int)K, dst_q, dst_s);
     SCMX_LAUNCH_OK("gather_rows_dyn_kernel");
     return SCMX_OK;
 }
@@ -319,7 +337,9 @@ extern "C" int scmx_gather_rows_dyn(const int8_t* xq, const float* xs, const int
 extern "C" int scmx_act_quant_dyn(const uint16_t* x, const int32_t* n_rows, int64_t r_cap, int pad, int64_t K, int8_t* xq, float* xs,
                                   void* stream) {
     SCMX_REQUIRE(r_cap >= 0 && pad >= 0 && K > 0 && K % 8 == 0, SCMX_EINVAL, "act_quant_dyn: K %% 8 != 0");
-    launch_pdl(act_quant_dyn_kernel, dim3((unsigned)(r_cap + pad)), dim3(256), 0, (cudaStream_t)stream, x, n_rows, pad, (int)K, xq, xs);
+    const int64_t a_ctas = r_cap + pad;
+    launch_pdl(act_quant_dyn_kernel, dim3((unsigned)(a_ctas < 148 * 8 ? a_ctas : 148 * 8)), dim3(256), 0, (cudaStream_t)stream, x, n_rows, pad,
+               (int)K, xq, xs);
     SCMX_LAUNCH_OK("act_quant_dyn_kernel");
     return SCMX_OK;
 }
