@@ -217,6 +217,15 @@ int scmx_ep_plan(const int32_t* rx_meta, int world, int El, int64_t cap, int tm,
 /* Stores expert output row p (bf16 [D]) into rank ret_rank[p]'s y_back at row ret_row[p], for p < n_rows[0]. */
 int scmx_ep_return(const uint16_t* y, const int32_t* ret_rank, const int32_t* ret_row, const int32_t* n_rows, int64_t r_cap,
                    int64_t D, int world, const void* const* y_back_peers, void* stream);
+/* scmx_moe_mm_i8 with EPI 1 whose epilogue IS the return exchange of expert parallelism: bf16 output row r of the grouped
+ * GEMM is stored at row ret_row[r] of out_peers[ret_rank[r]] (bf16 [*, N] buffers of the `world` GPUs, this GPU's own
+ * included; peer buffers are device pointers of peer-mapped memory), straight from the TMEM accumulators, instead of being
+ * written locally and moved by scmx_ep_return afterwards.  ret_rank / ret_row as produced by scmx_ep_plan; rows outside the
+ * expert segments (off) are not stored.  Follow with scmx_peer_barrier before the peers read.  No counterpart in the
+ * single-device reference. */
+int scmx_moe_mm_i8_ret(const int8_t* xq, int64_t R, const int8_t* wq, const float* wscale, const int32_t* off,
+                       const int32_t* tstart, int E, int64_t N, int64_t K, const float* xscale, const int32_t* ret_rank,
+                       const int32_t* ret_row, int world, void* const* out_peers, int tm, int32_t* status, void* stream);
 /* gather_rows / act_quant over a device-side row count: rows >= n_rows[0] + pad are skipped, the pad rows after
  * n_rows[0] are zero-filled. */
 int scmx_gather_rows_dyn(const int8_t* xq, const float* xs, const int32_t* tok, const int32_t* n_rows, int64_t r_cap, int pad,

@@ -42,6 +42,11 @@ struct GemmArgs {
     int e_begin, e_end;          // grouped: experts handled by this launch; B rows are relative to e_begin
     int32_t* status;
     const uint16_t* silu_lut;    // 65536-entry bf16 table of silu(g) indexed by the bf16 bits of g (EPI 3)
+    // EPI 1 with a return map (expert parallelism): output row r is stored at row ret_row[r] of peer_out[ret_rank[r]], the
+    // buffer of the GPU the token came from, instead of row r of `out`: the GEMM's epilogue is the return exchange.
+    const int32_t* ret_rank;
+    const int32_t* ret_row;
+    uint16_t* peer_out[8];
 };
 
 // Barrier among the epilogue threads only (named barrier 1).
@@ -212,7 +217,13 @@ __device__ __forceinline__ void epilogue_chunk(const GemmArgs& a, const uint32_t
                 pk[j] = pack_bf16x2(scale2(r[2 * j], xs, w2.x), scale2(r[2 * j + 1], xs, w2.y));
             }
         }
-        uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(a.out) + (size_t)row * a.N + n);
+        uint16_t* orow = reinterpret_cast<uint16_t*>(a.out) + (size_t)row * a.N;
+        if (a.ret_rank != nullptr) {                          // the row's home: a peer GPU's (or this GPU's) return buffer
+            const int rr = a.ret_rank[row], r2 = a.ret_row[row];
+            if (rr < 0 || rr >= 8 || r2 < 0 || a.peer_out[rr] == nullptr) return;     // inconsistent tables: store nothing
+            orow = a.peer_out[rr] + (size_t)r2 * a.N;
+        }
+        uint4* o = reinterpret_cast<uint4*>(orow + n);
 #pragma unroll
         for (int j = 0; j < 4; ++j) o[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
     }
@@ -574,6 +585,29 @@ extern "C" int scmx_moe_mm_i8(const int8_t* xq, int64_t R, const int8_t* wq, con
     GemmArgs a = {};
     a.M = (int)R; a.N = (int)N; a.K = (int)K; a.epi = epi; a.xscale = xscale; a.wscale = wscale; a.out = out;
     a.off = off; a.tstart = tstart; a.E = E; a.e_begin = 0; a.e_end = E; a.status = status;
+    return run_gemm(xq, R, wq, (int64_t)E * N, a, (cudaStream_t)stream);
+}
+
+extern "C" int scmx_moe_mm_i8_ret(const int8_t* xq, int64_t R, const int8_t* wq, const float* wscale, const int32_t* off,
+                                  const int32_t* tstart, int E, int64_t N, int64_t K, const float* xscale, const int32_t* ret_rank,
+                                  const int32_t* ret_row, int world, void* const* out_peers, int tm, int32_t* status,
+                                  void* stream) {
+    int rc = check_common("moe_mm_i8_ret", N, K, 1, xscale, wscale, out_peers, status);
+    if (rc) return rc;
+    SCMX_REQUIRE(tm == BM, SCMX_EINVAL, "moe_mm_i8_ret: tm=%d, the kernel's M tile is %d", tm, BM);
+    SCMX_REQUIRE(E >= 1 && E <= 65536 && R >= 0 && R < (1ll << 30) && off && tstart, SCMX_EINVAL, "moe_mm_i8_ret: bad E / R / offsets");
+    SCMX_REQUIRE((int64_t)E * N < (1ll << 31), SCMX_ELIMIT, "moe_mm_i8_ret: E*N too large");
+    SCMX_REQUIRE(ret_rank && ret_row && world >= 1 && world <= 8, SCMX_EINVAL, "moe_mm_i8_ret: return map / world (1..8)");
+    if (R == 0) return SCMX_OK;
+    GemmArgs a = {};
+    a.M = (int)R; a.N = (int)N; a.K = (int)K; a.epi = 1; a.xscale = xscale; a.wscale = wscale; a.out = out_peers[0];
+    a.off = off; a.tstart = tstart; a.E = E; a.e_begin = 0; a.e_end = E; a.status = status;
+    a.ret_rank = ret_rank; a.ret_row = ret_row;
+    for (int g = 0; g < 8; ++g) {
+        a.peer_out[g] = g < world ? static_cast<uint16_t*>(out_peers[g]) : nullptr;
+        SCMX_REQUIRE(g >= world || (a.peer_out[g] != nullptr && (reinterpret_cast<uintptr_t>(a.peer_out[g]) & 15) == 0), SCMX_EINVAL,
+                     "moe_mm_i8_ret: return buffer of rank %d is NULL or not 16-byte aligned", g);
+    }
     return run_gemm(xq, R, wq, (int64_t)E * N, a, (cudaStream_t)stream);
 }
 

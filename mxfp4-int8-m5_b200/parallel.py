@@ -208,6 +208,7 @@ class PeerExpertParallelMoe:
         # side stream at the top of every step and overlaps routing, dispatch and the barrier (weights do not depend on them).
         F = block_local.F
         self.early_decode = El * 3 * F * D <= (1 << 30)
+        self.fused_return = True      # the down GEMM stores its rows straight into the senders' buffers (scmx_moe_mm_i8_ret)
         if self.early_decode:
             self.side = torch.cuda.Stream(device=dev)
             self.gu8 = torch.empty((El * 2 * F, D), dtype=torch.int8, device=dev)
@@ -260,12 +261,18 @@ class PeerExpertParallelMoe:
         xq2 = torch.empty((self.r_cap + TM, F), dtype=torch.int8, device=h.device)
         xs2 = torch.empty(self.r_cap + TM, dtype=torch.float32, device=h.device)
         L_.call("scmx_act_quant_dyn", L_.ptr(act), L_.ptr(self.n_rows), self.r_cap, TM, F, L_.ptr(xq2), L_.ptr(xs2), L_.stream())
-        if self.early_decode:
-            yd = M_.moe_mm_i8(xq2, self.r_cap, self.dn8, blk.dn[2], self.off2, self.ts2, mt, D, 1, xs2)
+        if self.early_decode and self.fused_return:
+            # the down GEMM's epilogue stores every output row into the buffer of the GPU its token came from
+            L_.call("scmx_moe_mm_i8_ret", L_.ptr(xq2), self.r_cap, L_.ptr(self.dn8), L_.ptr(blk.dn[2]), L_.ptr(self.off2),
+                    L_.ptr(self.ts2), blk.E, D, F, L_.ptr(xs2), L_.ptr(self.ret_rank), L_.ptr(self.ret_row), G,
+                    self._peers["y_back"], TM, L_.ptr(L_.status_buffer()), L_.stream())
         else:
-            yd = M_.moe_mm(xq2, self.r_cap, *blk.dn, self.off2, self.ts2, mt, D, 1, xs2)
-        L_.call("scmx_ep_return", L_.ptr(yd), L_.ptr(self.ret_rank), L_.ptr(self.ret_row), L_.ptr(self.n_rows), self.r_cap, D, G,
-                self._peers["y_back"], L_.stream())
+            if self.early_decode:
+                yd = M_.moe_mm_i8(xq2, self.r_cap, self.dn8, blk.dn[2], self.off2, self.ts2, mt, D, 1, xs2)
+            else:
+                yd = M_.moe_mm(xq2, self.r_cap, *blk.dn, self.off2, self.ts2, mt, D, 1, xs2)
+            L_.call("scmx_ep_return", L_.ptr(yd), L_.ptr(self.ret_rank), L_.ptr(self.ret_row), L_.ptr(self.n_rows), self.r_cap, D, G,
+                    self._peers["y_back"], L_.stream())
         self._barrier()
         hout, _, _ = M_.moe_combine(self.y_back, pos, scores, h, blk.nw, blk.eps, Lr, quant=False)
         return hout

@@ -119,6 +119,15 @@ def _worker_body(rank, world, port, q):
         o2 = pep.step(hl, ll)
         torch.cuda.synchronize()
         ok["peer_ep"] = bool(torch.equal(o1, refm[rank * Lr:(rank + 1) * Lr])) and bool(torch.equal(o2, o1))
+        # the return exchange as a separate kernel (the default stores from the down GEMM's epilogue) and the per-pass decode
+        assert pep.early_decode and pep.fused_return
+        pep.fused_return = False
+        o4 = pep.step(hl, ll)
+        pep.early_decode = False
+        o5 = pep.step(hl, ll)
+        pep.early_decode, pep.fused_return = True, True
+        torch.cuda.synchronize()
+        ok["peer_ep_variants"] = bool(torch.equal(o4, o1)) and bool(torch.equal(o5, o1))
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             o3 = pep.step(hl, ll)
@@ -151,7 +160,7 @@ def test_tensor_and_expert_parallel_match_single_gpu():
         p.join(20)
         if p.is_alive():
             p.kill()
-    want = dict(tp=True, peer_tp=True, ep=True, peer_ep=True, peer_ep_graph=True, two_pass=True)
+    want = dict(tp=True, peer_tp=True, ep=True, peer_ep=True, peer_ep_variants=True, peer_ep_graph=True, two_pass=True)
     assert res == {0: want, 1: want}
 
 
