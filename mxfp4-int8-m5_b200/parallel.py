@@ -208,7 +208,11 @@ class PeerExpertParallelMoe:
         # side stream at the top of every step and overlaps routing, dispatch and the barrier (weights do not depend on them).
         F = block_local.F
         self.early_decode = El * 3 * F * D <= (1 << 30)
-        self.fused_return = True      # the down GEMM stores its rows straight into the senders' buffers (scmx_moe_mm_i8_ret)
+        # fused_return: the down GEMM stores its rows straight into the senders' buffers (scmx_moe_mm_i8_ret) instead of a
+        # separate return kernel.  Off by default: measured slower on 2 GPUs (half-block 0.534 vs 0.390 ms) - an epilogue thread
+        # owns one row, so a warp's stores are 32 separate 64-byte pieces per instruction, which NVLink carries poorly, and the
+        # stalled epilogue holds the TMEM accumulators; the return kernel writes whole 4 KB rows.
+        self.fused_return = False
         if self.early_decode:
             self.side = torch.cuda.Stream(device=dev)
             self.gu8 = torch.empty((El * 2 * F, D), dtype=torch.int8, device=dev)

@@ -119,13 +119,14 @@ def _worker_body(rank, world, port, q):
         o2 = pep.step(hl, ll)
         torch.cuda.synchronize()
         ok["peer_ep"] = bool(torch.equal(o1, refm[rank * Lr:(rank + 1) * Lr])) and bool(torch.equal(o2, o1))
-        # the return exchange as a separate kernel (the default stores from the down GEMM's epilogue) and the per-pass decode
-        assert pep.early_decode and pep.fused_return
-        pep.fused_return = False
+        # variants: the return exchange from the down GEMM's epilogue (scmx_moe_mm_i8_ret); the per-pass expert decode
+        assert pep.early_decode and not pep.fused_return
+        pep.fused_return = True
         o4 = pep.step(hl, ll)
+        pep.fused_return = False
         pep.early_decode = False
         o5 = pep.step(hl, ll)
-        pep.early_decode, pep.fused_return = True, True
+        pep.early_decode = True
         torch.cuda.synchronize()
         ok["peer_ep_variants"] = bool(torch.equal(o4, o1)) and bool(torch.equal(o5, o1))
         graph = torch.cuda.CUDAGraph()
