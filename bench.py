@@ -706,19 +706,28 @@ def run_case(args):
         xs = torch.full((1,), 1e-2, device="cuda")
         for _ in range(3):
             G.gemv(xq, c, b, xs, w_, 151936, 1)
-    elif args.case == "decodestep":   # Qwen3-1.7B-shaped model, 512 positions in the cache, three one-kernel decode steps
+    elif args.case in ("decodestep", "decodechain"):   # Qwen3-1.7B-shaped model, 512 positions in the cache: three one-kernel
+        # decode steps, or two graph-replayed steps of the chain of stand-alone kernels
         HM, FQ, DEC = pkg.host_model, pkg.fused_qwen3, pkg.decode
         with torch.device("cuda"):
             model = HM.CausalLM(HM.QWEN3_1_7B)
         model.init_random(0)
         fused = FQ.FusedQwen3(model, FQ.pack_model(model, on_device=True))
-        dec = DEC.DecodeQwen3(fused)
+        dec = DEC.DecodeQwen3(fused, persistent=args.case == "decodestep")
         ids = torch.randint(0, HM.QWEN3_1_7B.vocab_size, (1, 513), device="cuda", generator=g)
         cache = fused.make_cache(1024)
         fused.logits(fused.hidden(ids[:, :512], cache)[:, -1:])
         tok = ids[:, 512:513]
-        for _ in range(3):
-            tok = dec.step(tok, cache)[:, -1].argmax(-1, keepdim=True)
+        if args.case == "decodestep":
+            for _ in range(3):
+                tok = dec.step(tok, cache)[:, -1].argmax(-1, keepdim=True)
+        else:       # the chain of stand-alone kernels: capture the step, then replay two tokens inside the profiler range
+            dec.generate(tok, cache, 1)
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
+            dec.generate(tok, cache, 2)
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
         torch.cuda.synchronize()
         dec.check_status()
     elif args.case == "models":
@@ -741,7 +750,7 @@ def main():
     ap.add_argument("--no-overlap", action="store_true", help="decode weights on the main stream instead of a side stream")
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic stream serialization")
     ap.add_argument("--dense-only", action="store_true", help="skip the roofline / decode / MoE / CPU sections")
-    ap.add_argument("--case", choices=["gemm", "gemv", "gemvbig", "moe", "models", "decodestep"], help="run one small kernel case (for profiler captures) and exit")
+    ap.add_argument("--case", choices=["gemm", "gemv", "gemvbig", "moe", "models", "decodestep", "decodechain"], help="run one small kernel case (for profiler captures) and exit")
     args = ap.parse_args()
     if args.case:
         run_case(args)
