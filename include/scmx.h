@@ -294,7 +294,8 @@ int scmx_decode_step_dense(const scmx_decode_layer* layers, int n_layers, int D,
                            const int32_t* pos_dev, uint16_t* h, uint16_t* y, uint16_t* act, uint16_t* o, float* partials,
                            int nsplit, int32_t* counters, uint32_t* barrier, int32_t* status, void* stream);
 /* Diagnostic: while device_buf is set, CTA 0 of scmx_decode_step_dense stores its SM cycle counter in device_buf[0 .. n)
- * at every phase boundary (barrier entry / exit, end of each activation prologue), layer after layer; with
+ * at every barrier entry and exit and, in the attention phase, after the q/k/v preparation and after the split's positions,
+ * layer after layer; with
  * n_and_barrier = n | (b << 16), b > 0, every CTA also stores the global nanosecond timer at its arrival at barrier b
  * (1-based) in device_buf[n + CTA index].  device_buf: uint64 [n + number of SMs].  0 switches it off.  Process-wide; no
  * counterpart in the reference. */

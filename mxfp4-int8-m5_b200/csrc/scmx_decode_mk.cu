@@ -397,6 +397,7 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_step_kernel(const MkArgs
             const int kvh = blockIdx.x % a.hk, split = blockIdx.x / a.hk;
             if (split < active) {                             // uniform over the CTA
                 qkv_prepare<G, HD>(qs, a, L, kvh, pos);
+                MK_MARK();
                 uint16_t* kc = L.k_cache + (size_t)kvh * a.cap * HD;
                 uint16_t* vc = L.v_cache + (size_t)kvh * a.cap * HD;
                 if (split == 0 && in_cache && tid < HD / 8) {
@@ -406,6 +407,7 @@ __global__ void __launch_bounds__(MK_THREADS, 1) decode_step_kernel(const MkArgs
                 const int64_t t0 = (int64_t)split * chunk, t1 = t0 + chunk < T ? t0 + chunk : T;
                 attn_split<G, HD>(qs.q, kc, vc, t0, t1, in_cache ? pos : -1, qs.k, qs.v, a.scale,
                                   a.part + ((size_t)kvh * G * a.nsplit + split) * stride, (size_t)a.nsplit * stride, as);
+                MK_MARK();
                 // the last split of this kv head to finish combines them (the arithmetic of attn_combine) into o
                 __syncthreads();
                 if (tid == 0) {                               // one fence orders the CTA's partials before the ticket
