@@ -226,6 +226,16 @@ int scmx_ep_return(const uint16_t* y, const int32_t* ret_rank, const int32_t* re
 int scmx_moe_mm_i8_ret(const int8_t* xq, int64_t R, const int8_t* wq, const float* wscale, const int32_t* off,
                        const int32_t* tstart, int E, int64_t N, int64_t K, const float* xscale, const int32_t* ret_rank,
                        const int32_t* ret_row, int world, void* const* out_peers, int tm, int32_t* status, void* stream);
+/* scmx_moe_combine whose expert rows are READ from the GPUs that computed them (expert parallelism, "pull" form): y_peers[d]
+ * is rank d's output buffer bf16 [world * cap, K] ordered by receive slot (source rank * cap + position among the rows that
+ * source sent), as written by scmx_moe_mm_i8_ret with ret_row = the gather list of scmx_ep_plan.  Sorted position p of this
+ * rank (pos, esorted, off from scmx_route_sort over the GLOBAL expert ids) lives at y_peers[esorted[p] / El][rank * cap +
+ * p - off[(esorted[p] / El) * El]].  Same arithmetic as scmx_moe_combine; replaces scmx_ep_return + the barrier-separated
+ * local combine by one kernel that loads over peer memory.  Run scmx_peer_barrier first.  No counterpart in the reference. */
+int scmx_moe_combine_pull(const void* const* y_peers, int world, int rank, int El, int64_t cap, const int32_t* esorted,
+                          const int32_t* off, const int32_t* pos, const uint16_t* scores, const uint16_t* res,
+                          const uint16_t* nw, float eps, int64_t M, int64_t Mp, int64_t K, int topk, int quant, uint16_t* h,
+                          int8_t* xq, float* xs, void* stream);
 /* gather_rows / act_quant over a device-side row count: rows >= n_rows[0] + pad are skipped, the pad rows after
  * n_rows[0] are zero-filled. */
 int scmx_gather_rows_dyn(const int8_t* xq, const float* xs, const int32_t* tok, const int32_t* n_rows, int64_t r_cap, int pad,

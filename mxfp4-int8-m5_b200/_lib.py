@@ -71,6 +71,8 @@ SIGNATURES = {
     "scmx_enable_peer_access": [c_int],
     "scmx_moe_mm_i8_ret": [c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, c_vp, c_vp, c_vp, c_int, c_vp, c_int, c_vp,
                            c_vp],
+    "scmx_moe_combine_pull": [c_vp, c_int, c_int, c_int, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_float, c_i64, c_i64, c_i64,
+                              c_int, c_int, c_vp, c_vp, c_vp, c_vp],
     "scmx_moe_combine": [c_vp, c_vp, c_vp, c_vp, c_vp, c_float, c_i64, c_i64, c_i64, c_int, c_int, c_vp, c_vp, c_vp,
                          c_vp],
     "scmx_decode_step_dense": [c_vp, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_vp, c_vp, c_i64, c_i64, c_vp,

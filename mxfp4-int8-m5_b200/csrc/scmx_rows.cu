@@ -435,23 +435,42 @@ __global__ void swiglu_kernel(const uint16_t* __restrict__ g, const uint16_t* __
 
 // ---- MoE combine ------------------------------------------------------------------------------------------------------
 // acc_j = rbf(rbf(y[pos[t*k+j]] * sc_j) + acc_{j-1}), h = T(res + acc); then (QUANT) RMSNorm + INT8 of h.
+// Expert-parallel "pull" form: the expert outputs stay on the GPUs that computed them, stored by receive slot
+// [source rank * cap + position among the rows that source sent]; the combine of the GPU that owns the token reads them
+// over peer memory.  Sorted position p of this rank went to rank d = es[p] / El at slot rank * cap + (p - off[d * El]).
+struct CombinePull {
+    const int32_t* es;            // expert of every sorted position; null = local form (rows of y at pos)
+    const int32_t* off;           // this rank's segment offsets per global expert
+    const uint16_t* peer[8];      // every rank's slot-ordered output buffer
+    int El, cap, rank, world;
+};
+
 template <int TOPK_MAX>
 __global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t* __restrict__ y, const int32_t* __restrict__ pos,
                                                           const uint16_t* __restrict__ scores,
                                                           const uint16_t* __restrict__ res, const uint16_t* __restrict__ nw,
                                                           float eps, int64_t M, int K, int topk, int quant,
                                                           uint16_t* __restrict__ h, int8_t* __restrict__ xq,
-                                                          float* __restrict__ xs) {
+                                                          float* __restrict__ xs, const CombinePull pl) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float red[33];
     __shared__ double dred[33];
-    __shared__ int s_pos[TOPK_MAX];
+    __shared__ const uint16_t* s_ptr[TOPK_MAX];
     __shared__ float s_sc[TOPK_MAX];
     const int64_t row = blockIdx.x;
     const bool live = row < M;
     if (live && threadIdx.x < topk) {
-        s_pos[threadIdx.x] = pos[row * topk + threadIdx.x];
+        const int p = pos[row * topk + threadIdx.x];
+        const uint16_t* base = y + (int64_t)p * K;
+        if (pl.es != nullptr) {
+            const int e = pl.es[p];
+            const int d = e / pl.El;
+            const int idx = (d >= 0 && d < pl.world) ? p - pl.off[d * pl.El] : -1;
+            // inconsistent routing tables: contribute zeros instead of reading somewhere
+            base = (idx >= 0 && idx < pl.cap && pl.peer[d] != nullptr) ? pl.peer[d] + ((int64_t)pl.rank * pl.cap + idx) * K : nullptr;
+        }
+        s_ptr[threadIdx.x] = base;
         s_sc[threadIdx.x] = bf16_to_f32(scores[row * topk + threadIdx.x]);
     }
     __syncthreads();
@@ -468,7 +487,8 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t* __rest
                 uint4 raw[8];
 #pragma unroll
                 for (int u = 0; u < 8; ++u)
-                    if (t0 + u < topk) raw[u] = *reinterpret_cast<const uint4*>(y + (int64_t)s_pos[t0 + u] * K + k);
+                    if (t0 + u < topk)
+                        raw[u] = s_ptr[t0 + u] ? *reinterpret_cast<const uint4*>(s_ptr[t0 + u] + k) : make_uint4(0, 0, 0, 0);
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
                     if (t0 + u < topk) {
@@ -698,8 +718,32 @@ extern "C" int scmx_moe_combine(const uint16_t* y, const int32_t* pos, const uin
     SCMX_REQUIRE(aligned16(y) && aligned16(res) && aligned16(h) && (!quant || (aligned16(xq) && aligned16(nw))),
                  SCMX_EINVAL, "moe_combine: buffers must be 16-byte aligned");
     if (Mp == 0) return SCMX_OK;
+    CombinePull pl = {};
     launch_pdl(moe_combine_kernel<32>, dim3((unsigned)Mp), dim3(256), 0, (cudaStream_t)stream, y, pos, scores, res, nw, eps, M, (int)K, topk,
-                                                                             quant, h, xq, xs);
+               quant, h, xq, xs, pl);
+    SCMX_LAUNCH_OK("moe_combine_kernel");
+    return SCMX_OK;
+}
+
+extern "C" int scmx_moe_combine_pull(const void* const* y_peers, int world, int rank, int El, int64_t cap, const int32_t* esorted,
+                                     const int32_t* off, const int32_t* pos, const uint16_t* scores, const uint16_t* res,
+                                     const uint16_t* nw, float eps, int64_t M, int64_t Mp, int64_t K, int topk, int quant,
+                                     uint16_t* h, int8_t* xq, float* xs, void* stream) {
+    SCMX_REQUIRE(M >= 0 && Mp >= M && K > 0 && K % 8 == 0, SCMX_EINVAL, "moe_combine_pull: need M <= Mp and K %% 8 == 0");
+    SCMX_REQUIRE(topk >= 1 && topk <= 32, SCMX_ELIMIT, "moe_combine_pull: topk=%d outside 1..32", topk);
+    SCMX_REQUIRE(y_peers && world >= 1 && world <= 8 && rank >= 0 && rank < world && El >= 1 && cap >= 1 && cap < (1ll << 31) && esorted && off,
+                 SCMX_EINVAL, "moe_combine_pull: bad peers / world / rank / El / cap / tables");
+    SCMX_REQUIRE(aligned16(res) && aligned16(h) && (!quant || (aligned16(xq) && aligned16(nw))), SCMX_EINVAL,
+                 "moe_combine_pull: buffers must be 16-byte aligned");
+    if (Mp == 0) return SCMX_OK;
+    CombinePull pl = {};
+    pl.es = esorted; pl.off = off; pl.El = El; pl.cap = (int)cap; pl.rank = rank; pl.world = world;
+    for (int g = 0; g < world; ++g) {
+        pl.peer[g] = static_cast<const uint16_t*>(y_peers[g]);
+        SCMX_REQUIRE(pl.peer[g] != nullptr && aligned16(pl.peer[g]), SCMX_EINVAL, "moe_combine_pull: buffer of rank %d is NULL or unaligned", g);
+    }
+    launch_pdl(moe_combine_kernel<32>, dim3((unsigned)Mp), dim3(256), 0, (cudaStream_t)stream, pl.peer[rank], pos, scores, res, nw, eps, M,
+               (int)K, topk, quant, h, xq, xs, pl);
     SCMX_LAUNCH_OK("moe_combine_kernel");
     return SCMX_OK;
 }

@@ -14,6 +14,8 @@ uses for row concatenation (e2e/fused_qwen3.py:36,44-46) and for order independe
 (e2e/sc_moe.py:110-113).  The bookkeeping in this file is device-agnostic so that it also runs on CPU tensors with the
 gloo backend.
 """
+import ctypes
+
 import torch
 import torch.distributed as dist
 
@@ -199,7 +201,10 @@ class PeerExpertParallelMoe:
         torch.cuda.synchronize()
         self._views = {}
         self._peers = {}
-        for name in ("rx_q", "rx_s", "rx_meta", "y_back", "flags"):
+        # "pull" return: expert outputs stay here, ordered by receive slot; the token's owner reads them in its combine
+        self.y_slot = torch.empty((G * self.cap, D), dtype=torch.bfloat16, device=dev)
+        self.zero_rank = torch.zeros(G * self.cap + TM, **i32)
+        for name in ("rx_q", "rx_s", "rx_meta", "y_back", "flags", "y_slot"):
             views = share_tensor(getattr(self, name), group)
             self._views[name] = views                      # keep the mappings alive
             self._peers[name] = (ctypes.c_void_p * 8)(*[v.data_ptr() for v in views], *([None] * (8 - G)))
@@ -213,6 +218,9 @@ class PeerExpertParallelMoe:
         # owns one row, so a warp's stores are 32 separate 64-byte pieces per instruction, which NVLink carries poorly, and the
         # stalled epilogue holds the TMEM accumulators; the return kernel writes whole 4 KB rows.
         self.fused_return = False
+        # pull_combine: the down GEMM stores its rows by receive slot in a local buffer (the same epilogue scatter, local) and
+        # after one barrier every rank's combine loads the rows of its tokens from the owners over peer memory: no return kernel
+        self.pull_combine = True
         if self.early_decode:
             self.side = torch.cuda.Stream(device=dev)
             self.gu8 = torch.empty((El * 2 * F, D), dtype=torch.int8, device=dev)
@@ -265,6 +273,16 @@ class PeerExpertParallelMoe:
         xq2 = torch.empty((self.r_cap + TM, F), dtype=torch.int8, device=h.device)
         xs2 = torch.empty(self.r_cap + TM, dtype=torch.float32, device=h.device)
         L_.call("scmx_act_quant_dyn", L_.ptr(act), L_.ptr(self.n_rows), self.r_cap, TM, F, L_.ptr(xq2), L_.ptr(xs2), L_.stream())
+        if self.early_decode and self.pull_combine:
+            own = (ctypes.c_void_p * 8)(self.y_slot.data_ptr(), *([None] * 7))
+            L_.call("scmx_moe_mm_i8_ret", L_.ptr(xq2), self.r_cap, L_.ptr(self.dn8), L_.ptr(blk.dn[2]), L_.ptr(self.off2),
+                    L_.ptr(self.ts2), blk.E, D, F, L_.ptr(xs2), L_.ptr(self.zero_rank), L_.ptr(self.tok2), 1, own, TM,
+                    L_.ptr(L_.status_buffer()), L_.stream())
+            self._barrier()
+            hout = torch.empty((Lr, D), dtype=torch.bfloat16, device=h.device)
+            L_.call("scmx_moe_combine_pull", self._peers["y_slot"], G, self.rank, blk.E, self.cap, L_.ptr(es), L_.ptr(off), L_.ptr(pos),
+                    L_.ptr(scores), L_.ptr(h), L_.ptr(blk.nw), float(blk.eps), Lr, Lr, D, k, 0, L_.ptr(hout), None, None, L_.stream())
+            return hout
         if self.early_decode and self.fused_return:
             # the down GEMM's epilogue stores every output row into the buffer of the GPU its token came from
             L_.call("scmx_moe_mm_i8_ret", L_.ptr(xq2), self.r_cap, L_.ptr(self.dn8), L_.ptr(blk.dn[2]), L_.ptr(self.off2),

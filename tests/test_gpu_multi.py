@@ -119,14 +119,18 @@ def _worker_body(rank, world, port, q):
         o2 = pep.step(hl, ll)
         torch.cuda.synchronize()
         ok["peer_ep"] = bool(torch.equal(o1, refm[rank * Lr:(rank + 1) * Lr])) and bool(torch.equal(o2, o1))
-        # variants: the return exchange from the down GEMM's epilogue (scmx_moe_mm_i8_ret); the per-pass expert decode
-        assert pep.early_decode and not pep.fused_return
-        pep.fused_return = True
+        # variants of the return path: the default keeps the expert outputs on their GPU and the combine pulls them over
+        # peer memory; a separate return kernel; the return stores from the down GEMM's epilogue; the per-pass expert decode
+        assert pep.early_decode and pep.pull_combine and not pep.fused_return
+        pep.pull_combine = False
         o4 = pep.step(hl, ll)
+        pep.fused_return = True
+        o6 = pep.step(hl, ll)
         pep.fused_return = False
         pep.early_decode = False
         o5 = pep.step(hl, ll)
-        pep.early_decode = True
+        pep.early_decode, pep.pull_combine = True, True
+        o4 = o4 if torch.equal(o4, o6) else o6 * float("nan")
         torch.cuda.synchronize()
         ok["peer_ep_variants"] = bool(torch.equal(o4, o1)) and bool(torch.equal(o5, o1))
         graph = torch.cuda.CUDAGraph()
