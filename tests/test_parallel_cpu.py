@@ -111,3 +111,56 @@ def test_segment_layout_of_column_gather_gloo():
     for p in procs:
         p.join(60)
     assert res == {0: True, 1: True}
+
+
+def test_peer_exchange_slot_algebra():
+    """The index arithmetic of the kernel-side expert-parallel exchange, restated in NumPy for 3 ranks: dispatch slots
+    (source rank * cap + position among the rows that source sends there), the receiver's regrouping list, the scatter of
+    the expert outputs back to slot order, and the addresses the pull-form combine reads.  Every token must get, for each
+    of its top-k slots, the output of exactly its own (token, expert) assignment."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import scmx_oracle as O
+    G, E, k, tm = 3, 12, 2, 128
+    El = E // G
+    L = [19, 7, 30]
+    cap = max(L) * k
+    rng = np.random.default_rng(5)
+    sent = []
+    rx = [[None] * (G * cap) for _ in range(G)]           # rx[d][slot] = payload (source rank, token, expert)
+    meta = [np.zeros((G, El + 1), np.int64) for _ in range(G)]
+    for r in range(G):
+        inds = np.stack([rng.permutation(E)[:k] for _ in range(L[r])]).astype(np.int32)
+        inds[inds == 7] = 6                                # an expert nobody routes to
+        pos, tok, es, off, _, _ = O.route_sort(inds, E, tm)
+        sent.append((inds, pos, es, off))
+        for p in range(L[r] * k):                          # ep_dispatch
+            d = es[p] // El
+            rx[d][r * cap + (p - off[d * El])] = (r, int(tok[p]), int(es[p]))
+        for d in range(G):
+            meta[d][r, :El] = np.diff(off[d * El:(d + 1) * El + 1])
+            meta[d][r, El] = off[d * El]
+    y_slot = []
+    for d in range(G):                                     # ep_plan + grouped GEMM with the slot scatter
+        cnt = meta[d][:, :El]
+        tok2 = []
+        for le in range(El):
+            for s in range(G):
+                a = s * cap + int(cnt[s, :le].sum())
+                tok2 += list(range(a, a + int(cnt[s, le])))
+        ys = [None] * (G * cap)
+        seen_experts = []
+        for p2, slot in enumerate(tok2):
+            src, t, e = rx[d][slot]
+            assert e // El == d
+            seen_experts.append(e)
+            ys[slot] = ("out", src, t, e)                  # what the expert GEMM computes for regrouped row p2
+        assert seen_experts == sorted(seen_experts)        # regrouped rows are expert-major
+        y_slot.append(ys)
+    for r in range(G):                                     # the pull-form combine of rank r
+        inds, pos, es, off = sent[r]
+        for t in range(L[r]):
+            for j in range(k):
+                p = pos[t * k + j]
+                d = es[p] // El
+                got = y_slot[d][r * cap + (p - off[d * El])]
+                assert got == ("out", r, t, int(inds[t, j]))
