@@ -13,8 +13,8 @@
 //               T((float(acc) * xscale[m]) * wscale[n]) (+ residual, or SwiGLU on interleaved gate/up columns) and
 //               stores; then releases the accumulator ("tmem_empty") so the next tile's MMAs overlap this epilogue.
 //
-// Tiles are visited m-fastest so that concurrently running CTAs share B tiles through L2.  No cluster launch, no
-// multicast: every CTA fetches its own tiles.  Every mbarrier wait is bounded by a wall-clock limit; when it runs
+// Tiles are visited m-fastest so that concurrently running CTAs share B tiles through L2.  No cluster launch: every CTA
+// fetches its own tiles with its own TMA loads.  Every mbarrier wait is bounded by a wall-clock limit; when it runs
 // out the kernel records where in `status`, lets in-flight copies land, frees its TMEM and returns.
 #include <cuda.h>
 #include "scmx_common.cuh"
