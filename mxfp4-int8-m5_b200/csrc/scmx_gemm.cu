@@ -142,7 +142,8 @@ __device__ __forceinline__ Tile get_tile(const GemmArgs& a, int t, int tiles_m, 
     // columns have used them; with plain m-fastest order over thousands of sorted rows every column sweep re-read A from
     // DRAM (grouped gate|up GEMM: 689 MB read for 335 MB of operands).  Two waves of CTAs per band.
     const int tiles_n = (a.N + BN - 1) / BN;
-    const int gm_full = max(1, (2 * (int)gridDim.x + tiles_n - 1) / tiles_n);
+    // (dense launches have at most a few dozen M tiles and L2-resident operands: one band)
+    const int gm_full = a.E == 0 ? tiles_m : max(1, (2 * (int)gridDim.x + tiles_n - 1) / tiles_n);
     const int band = t / (gm_full * tiles_n), r = t - band * gm_full * tiles_n;
     const int gm = min(gm_full, tiles_m - band * gm_full);
     const int nt = r / gm, mt = band * gm_full + r - nt * gm;
