@@ -155,6 +155,16 @@ template <int G, int D>
 __device__ __forceinline__ void attn_combine_cta(const float* part, int nsplit, int active, uint16_t* out, AttnSmem<G, D>& sm) {
     constexpr int stride = D + 2;
     const int tid = threadIdx.x, nt = blockDim.x;
+    // the partial outputs of this thread's first element do not depend on the weights: request them before anything else, so
+    // that their round trip overlaps the one of the running maxima / sums
+    float v0[32];
+    const bool first = tid < G * D;
+    {
+        const int g = tid / D, e = tid - g * D;
+        const float* p = part + (size_t)g * nsplit * stride + e;
+#pragma unroll
+        for (int s = 0; s < 32; ++s) v0[s] = (first && s < active) ? __ldcg(p + s * stride) : 0.0f;
+    }
     for (int i = tid; i < G * active; i += nt) {
         const int g = i / active, s = i - g * active;
         const float* p = part + ((size_t)g * nsplit + s) * stride;
@@ -177,14 +187,20 @@ __device__ __forceinline__ void attn_combine_cta(const float* part, int nsplit, 
     __syncthreads();
     for (int i = tid; i < G * D; i += nt) {
         const int g = i / D, e = i - g * D;
-        const float* p = part + (size_t)g * nsplit * stride + e;
-        float v[32];
-#pragma unroll
-        for (int s = 0; s < 32; ++s) v[s] = s < active ? __ldcg(p + s * stride) : 0.0f;   // all loads in flight at once
         float av = 0.0f;
+        if (i == tid) {
 #pragma unroll
-        for (int s = 0; s < 32; ++s)
-            if (s < active) av += v[s] * sm.coef[g][s];
+            for (int s = 0; s < 32; ++s)
+                if (s < active) av += v0[s] * sm.coef[g][s];
+        } else {
+            const float* p = part + (size_t)g * nsplit * stride + e;
+            float v[32];
+#pragma unroll
+            for (int s = 0; s < 32; ++s) v[s] = s < active ? __ldcg(p + s * stride) : 0.0f;   // all loads in flight at once
+#pragma unroll
+            for (int s = 0; s < 32; ++s)
+                if (s < active) av += v[s] * sm.coef[g][s];
+        }
         out[i] = f32_to_bf16(av / sm.coef[g][32]);
     }
 }
