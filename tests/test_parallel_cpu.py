@@ -1,4 +1,4 @@
-"""CPU, world_size 2, gloo: the host-side bookkeeping of tensor-parallel sharding and of the expert-parallel exchange
+"""CPU, world_size 2 and 4, gloo: the host-side bookkeeping of tensor-parallel sharding and of the expert-parallel exchange
 (counts, variable all-to-all, regrouping by local expert, return to the sender in the original order)."""
 import importlib
 import os
@@ -58,16 +58,21 @@ def _ep_worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def test_expert_parallel_exchange_gloo():
+def _run_ranks(worker, world, port):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_ep_worker, args=(r, 2, 29613, q)) for r in range(2)]
+    procs = [ctx.Process(target=worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    res = dict(q.get(timeout=120) for _ in procs)
+    res = dict(q.get(timeout=180) for _ in procs)
     for p in procs:
         p.join(60)
-    assert res == {0: True, 1: True}
+    assert res == {r: True for r in range(world)}
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_exchange_gloo(world):
+    _run_ranks(_ep_worker, world, 29613 + 10 * world)
 
 
 def test_shard_rows_and_packed(scmx, oracle, golden):
@@ -101,16 +106,9 @@ def _seg_worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def test_segment_layout_of_column_gather_gloo():
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    procs = [ctx.Process(target=_seg_worker, args=(r, 2, 29614, q)) for r in range(2)]
-    for p in procs:
-        p.start()
-    res = dict(q.get(timeout=120) for _ in procs)
-    for p in procs:
-        p.join(60)
-    assert res == {0: True, 1: True}
+@pytest.mark.parametrize("world", [2, 4])
+def test_segment_layout_of_column_gather_gloo(world):
+    _run_ranks(_seg_worker, world, 29614 + 10 * world)
 
 
 def test_peer_exchange_slot_algebra():
