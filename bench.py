@@ -188,7 +188,7 @@ def build_dense_layers(pkg, torch, layers, shard=(0, 1), seed=0):
     return out
 
 
-def bench_decode(pkg, torch, model, reps=3):
+def bench_decode(pkg, torch, model, reps=10):
     """Batch-1 decode GEMVs over every packed weight set of the stack (nothing L2-resident across a pass)."""
     G = pkg.sc_decode
     xq = {k: torch.randint(-127, 128, (k,), dtype=torch.int8, device="cuda") for k in (2048, 6144)}
@@ -209,7 +209,7 @@ def bench_decode(pkg, torch, model, reps=3):
         run = g.replay
     except Exception:
         run = one_pass
-    for _ in range(2):
+    for _ in range(3):
         run()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -236,15 +236,16 @@ def bench_decode(pkg, torch, model, reps=3):
     def big_pass():
         for c, b, w_ in big:
             G.gemv(xq[K], c, b, xs, w_, N, 1)
-    for _ in range(2):
+    big_reps = 2 * reps            # ~50 us per launch: a timed region of a few ms
+    for _ in range(4):
         big_pass()
     torch.cuda.synchronize()
     e0.record()
-    for _ in range(reps):
+    for _ in range(big_reps):
         big_pass()
     e1.record()
     torch.cuda.synchronize()
-    us = e0.elapsed_time(e1) / reps / len(big) * 1e3
+    us = e0.elapsed_time(e1) / big_reps / len(big) * 1e3
     out["kernel_roofline"] = dict(kernel="gemv_stream_kernel", workload="151936 x 2048 SC-MXFP4 GEMV", bound="hbm",
                                   algorithmic_bytes_per_launch=gemv_bytes(N, K), us_per_launch=us,
                                   achieved=gemv_bytes(N, K) / us / 1e3, unit="GB/s")
