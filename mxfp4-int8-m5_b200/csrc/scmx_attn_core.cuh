@@ -8,6 +8,7 @@ namespace scmx {
 
 constexpr int AD_THREADS = 128;        // 4 warps x 4 position slots x 8 lanes per position
 constexpr int AD_MIN_CHUNK = 32;       // positions per split at least: short sequences use the first few splits only
+constexpr int AD_UNROLL = 2;           // groups of 16 positions whose loads are in flight together
 constexpr float LOG2E = 1.4426950408889634f;
 
 template <int G, int D>
@@ -61,44 +62,60 @@ __device__ __forceinline__ void attn_split(const uint16_t* q, const uint16_t* kb
             m[g] = -INFINITY;
             l[g] = 0.0f;
         }
-        // the trip count is uniform over the warp (the shuffles below need every lane); slots past the end are masked
-        for (int64_t tb = t0 + warp * 4; tb < t1; tb += 16) {
-            const int64_t t = tb + slot;
-            const bool valid = t < t1;
-            const uint16_t* kp = (t == t_new) ? knew + l8 * E : kb + t * D + l8 * E;
-            const uint16_t* vp = (t == t_new) ? vnew + l8 * E : vb + t * D + l8 * E;
-            float kf[E], vf[E];
+        // the trip count is uniform over the warp (the shuffles below need every lane); slots past the end are masked.
+        // AD_UNROLL groups of 16 positions per trip: the loads of all groups are issued before the first one is consumed,
+        // so that a CTA keeps AD_UNROLL x 16 KB in flight; the positions of a thread are consumed in ascending order.
+        for (int64_t tb = t0 + warp * 4; tb < t1; tb += 16 * AD_UNROLL) {
+            uint4 kw[AD_UNROLL][E / 8], vw[AD_UNROLL][E / 8];
 #pragma unroll
-            for (int c = 0; c < E / 8; ++c) {
-                uint4 kw = make_uint4(0, 0, 0, 0), vw = make_uint4(0, 0, 0, 0);
-                if (valid) {
-                    kw = *reinterpret_cast<const uint4*>(kp + 8 * c);
-                    vw = *reinterpret_cast<const uint4*>(vp + 8 * c);
-                }
-                const uint32_t ku[4] = {kw.x, kw.y, kw.z, kw.w}, vu[4] = {vw.x, vw.y, vw.z, vw.w};
+            for (int u = 0; u < AD_UNROLL; ++u) {
+                const int64_t t = tb + 16 * u + slot;
+                const uint16_t* kp = (t == t_new) ? knew + l8 * E : kb + t * D + l8 * E;
+                const uint16_t* vp = (t == t_new) ? vnew + l8 * E : vb + t * D + l8 * E;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    kf[8 * c + 2 * i] = __uint_as_float(ku[i] << 16);
-                    kf[8 * c + 2 * i + 1] = __uint_as_float(ku[i] & 0xFFFF0000u);
-                    vf[8 * c + 2 * i] = __uint_as_float(vu[i] << 16);
-                    vf[8 * c + 2 * i + 1] = __uint_as_float(vu[i] & 0xFFFF0000u);
+                for (int c = 0; c < E / 8; ++c) {
+                    kw[u][c] = make_uint4(0, 0, 0, 0);
+                    vw[u][c] = make_uint4(0, 0, 0, 0);
+                    if (t < t1) {
+                        kw[u][c] = *reinterpret_cast<const uint4*>(kp + 8 * c);
+                        vw[u][c] = *reinterpret_cast<const uint4*>(vp + 8 * c);
+                    }
                 }
             }
 #pragma unroll
-            for (int g = 0; g < G; ++g) {
-                float s = 0.0f;
+            for (int u = 0; u < AD_UNROLL; ++u) {
+                if (tb + 16 * u < t1) {               // uniform over the warp
+                    const bool valid = tb + 16 * u + slot < t1;
+                    float kf[E], vf[E];
 #pragma unroll
-                for (int i = 0; i < E; ++i) s = fmaf(qf[g][i], kf[i], s);
-                s += __shfl_xor_sync(0xffffffffu, s, 1);
-                s += __shfl_xor_sync(0xffffffffu, s, 2);
-                s += __shfl_xor_sync(0xffffffffu, s, 4);
-                if (valid) {
-                    const float mn = fmaxf(m[g], s);
-                    const float corr = exp2f(m[g] - mn), p = exp2f(s - mn);
-                    l[g] = l[g] * corr + p;
+                    for (int c = 0; c < E / 8; ++c) {
+                        const uint32_t ku[4] = {kw[u][c].x, kw[u][c].y, kw[u][c].z, kw[u][c].w};
+                        const uint32_t vu[4] = {vw[u][c].x, vw[u][c].y, vw[u][c].z, vw[u][c].w};
 #pragma unroll
-                    for (int i = 0; i < E; ++i) acc[g][i] = acc[g][i] * corr + p * vf[i];
-                    m[g] = mn;
+                        for (int i = 0; i < 4; ++i) {
+                            kf[8 * c + 2 * i] = __uint_as_float(ku[i] << 16);
+                            kf[8 * c + 2 * i + 1] = __uint_as_float(ku[i] & 0xFFFF0000u);
+                            vf[8 * c + 2 * i] = __uint_as_float(vu[i] << 16);
+                            vf[8 * c + 2 * i + 1] = __uint_as_float(vu[i] & 0xFFFF0000u);
+                        }
+                    }
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        float s = 0.0f;
+#pragma unroll
+                        for (int i = 0; i < E; ++i) s = fmaf(qf[g][i], kf[i], s);
+                        s += __shfl_xor_sync(0xffffffffu, s, 1);
+                        s += __shfl_xor_sync(0xffffffffu, s, 2);
+                        s += __shfl_xor_sync(0xffffffffu, s, 4);
+                        if (valid) {
+                            const float mn = fmaxf(m[g], s);
+                            const float corr = exp2f(m[g] - mn), p = exp2f(s - mn);
+                            l[g] = l[g] * corr + p;
+#pragma unroll
+                            for (int i = 0; i < E; ++i) acc[g][i] = acc[g][i] * corr + p * vf[i];
+                            m[g] = mn;
+                        }
+                    }
                 }
             }
         }
