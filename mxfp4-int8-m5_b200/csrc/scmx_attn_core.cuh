@@ -6,15 +6,17 @@
 
 namespace scmx {
 
-constexpr int AD_THREADS = 128;        // 4 warps x 4 position slots x 8 lanes per position
+constexpr int AD_THREADS = 256;        // 8 warps x 4 position slots x 8 lanes per position
+constexpr int AD_WARPS = AD_THREADS / 32;
+constexpr int AD_GROUP = AD_WARPS * 4;  // positions the CTA consumes together
 constexpr int AD_MIN_CHUNK = 32;       // positions per split at least: short sequences use the first few splits only
-constexpr int AD_UNROLL = 2;           // groups of 16 positions whose loads are in flight together
+constexpr int AD_UNROLL = 2;           // groups of positions whose loads are in flight together
 constexpr float LOG2E = 1.4426950408889634f;
 
 template <int G, int D>
 struct AttnSmem {
-    float acc[4][G][D];
-    float ml[4][G][2];
+    float acc[AD_WARPS][G][D];
+    float ml[AD_WARPS][G][2];
     float cml[G * 32][2];     // combination: running maximum and sum of every (head, split)
     float coef[G][33];        // weight of every split, [32] = the normalizer
 };
@@ -63,13 +65,13 @@ __device__ __forceinline__ void attn_split(const uint16_t* q, const uint16_t* kb
             l[g] = 0.0f;
         }
         // the trip count is uniform over the warp (the shuffles below need every lane); slots past the end are masked.
-        // AD_UNROLL groups of 16 positions per trip: the loads of all groups are issued before the first one is consumed,
-        // so that a CTA keeps AD_UNROLL x 16 KB in flight; the positions of a thread are consumed in ascending order.
-        for (int64_t tb = t0 + warp * 4; tb < t1; tb += 16 * AD_UNROLL) {
+        // AD_UNROLL groups of AD_GROUP positions per trip: the loads of all groups are issued before the first one is consumed,
+        // so that a CTA keeps AD_UNROLL x AD_GROUP x 2 rows in flight; the positions of a thread are consumed in ascending order.
+        for (int64_t tb = t0 + warp * 4; tb < t1; tb += AD_GROUP * AD_UNROLL) {
             uint4 kw[AD_UNROLL][E / 8], vw[AD_UNROLL][E / 8];
 #pragma unroll
             for (int u = 0; u < AD_UNROLL; ++u) {
-                const int64_t t = tb + 16 * u + slot;
+                const int64_t t = tb + AD_GROUP * u + slot;
                 const uint16_t* kp = (t == t_new) ? knew + l8 * E : kb + t * D + l8 * E;
                 const uint16_t* vp = (t == t_new) ? vnew + l8 * E : vb + t * D + l8 * E;
 #pragma unroll
@@ -84,8 +86,8 @@ __device__ __forceinline__ void attn_split(const uint16_t* q, const uint16_t* kb
             }
 #pragma unroll
             for (int u = 0; u < AD_UNROLL; ++u) {
-                if (tb + 16 * u < t1) {               // uniform over the warp
-                    const bool valid = tb + 16 * u + slot < t1;
+                if (tb + AD_GROUP * u < t1) {         // uniform over the warp
+                    const bool valid = tb + AD_GROUP * u + slot < t1;
                     float kf[E], vf[E];
 #pragma unroll
                     for (int c = 0; c < E / 8; ++c) {
@@ -144,13 +146,13 @@ __device__ __forceinline__ void attn_split(const uint16_t* q, const uint16_t* kb
         }
     }
     __syncthreads();
-    // merge the 4 warps; thread e < D owns output element e of every q head of this kv head
+    // merge the warps; thread e < D owns output element e of every q head of this kv head
     if (tid < AD_THREADS) {
         for (int g = 0; g < G; ++g) {
             float mm = -INFINITY;
-            for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sm.ml[w][g][0]);
+            for (int w = 0; w < AD_WARPS; ++w) mm = fmaxf(mm, sm.ml[w][g][0]);
             float ll = 0.0f, av = 0.0f;
-            for (int w = 0; w < 4; ++w) {
+            for (int w = 0; w < AD_WARPS; ++w) {
                 const float c = mm == -INFINITY ? 0.0f : exp2f(sm.ml[w][g][0] - mm);
                 ll += sm.ml[w][g][1] * c;
                 if (tid < D) av += sm.acc[w][g][tid] * c;
