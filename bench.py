@@ -141,11 +141,65 @@ def cpu_dense_layer_sample(seed=0, M=QWEN["M"]):
     return dt, qwen_ops(M, 1)
 
 
+def blas_threads(want=None):
+    """Sets the BLAS pool NumPy uses to `want` threads (all host cores by default; a launcher may have exported
+    OMP_NUM_THREADS=1) and returns the number the pool then reports."""
+    want = want or os.cpu_count() or 1
+    try:
+        import threadpoolctl
+        threadpoolctl.threadpool_limits(limits=want, user_api="blas")
+        got = [p.get("num_threads") for p in threadpoolctl.threadpool_info() if p.get("user_api") == "blas"]
+        return max(got) if got else 1
+    except Exception:   # noqa: BLE001
+        return int(os.environ.get("OMP_NUM_THREADS", "0")) or want
+
+
+def cpu_gemv_sample(seed=0):
+    """The reference's CPU check of the decode GEMV (e2e/sc_decode.py:253): qw.astype(int64) @ xq plus the scaling epilogue
+    for the four projection groups of ONE layer (25.6 MB of packed weights when stored 4-bit).  Returns (seconds, bytes)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import scmx_oracle as O
+    rng = np.random.default_rng(seed)
+    ws = {g: (rng.integers(-96, 97, nk).astype(np.int8), np.full(nk[0], 2.0 ** -9, np.float32)) for g, nk in QWEN["groups"].items()}
+    xq = {k: rng.integers(-127, 128, k).astype(np.int8) for k in (2048, 6144)}
+    t0 = time.perf_counter()
+    for g, (wq, wsc) in ws.items():
+        O.gemv(xq[wq.shape[1]], np.float32(0.01), wq, wsc, 1)
+    dt = time.perf_counter() - t0
+    return dt, sum(gemv_bytes(n, k) for n, k in QWEN["groups"].values())
+
+
+def cpu_moe_sample(seed=0, tokens=512):
+    """The reference's CPU check of the grouped GEMM (e2e/sc_moe.py:224-226): a per-expert loop of float64 BLAS products
+    over the sorted rows, for gate|up (SwiGLU) and down of an OLMoE-shaped block on `tokens` tokens (top-8 of 64 experts).
+    Returns (seconds, tokens)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import scmx_oracle as O
+    c = OLMOE
+    rng = np.random.default_rng(seed)
+    E, D, Fd, k = c["E"], c["D"], c["F"], c["topk"]
+    R = tokens * k
+    ex = np.sort(rng.integers(0, E, R))
+    off = np.concatenate([[0], np.cumsum(np.bincount(ex, minlength=E))]).astype(np.int32)
+    gu = [rng.integers(-96, 97, (2 * Fd, D)).astype(np.int8) for _ in range(E)]
+    dn = [rng.integers(-96, 97, (D, Fd)).astype(np.int8) for _ in range(E)]
+    wsg = [np.full(2 * Fd, 2.0 ** -9, np.float32)] * E
+    wsd = [np.full(D, 2.0 ** -9, np.float32)] * E
+    x = O.bf16_round(rng.standard_normal((R, D)).astype(np.float32))
+    t0 = time.perf_counter()
+    xq, xs = O.act_quant(x)
+    act = O.moe_mm(xq, R, gu, off, 3, xs, wsg)
+    xq2, xs2 = O.act_quant(act)
+    O.moe_mm(xq2, R, dn, off, 1, xs2, wsd)
+    dt = time.perf_counter() - t0
+    return dt, tokens
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cores = os.cpu_count()
+    cores = blas_threads()
     times = []
     for i in range(args.warmup + args.steps):
         dt, ops = cpu_dense_layer_sample(seed=i)
@@ -188,18 +242,57 @@ def build_dense_layers(pkg, torch, layers, shard=(0, 1), seed=0):
     return out
 
 
-def bench_decode(pkg, torch, model, reps=10):
-    """Batch-1 decode GEMVs over every packed weight set of the stack (nothing L2-resident across a pass)."""
+def bench_decode(pkg, torch, model, pk, reps=10):
+    """Batch-1 decode GEMVs over every packed weight set of the stack, 112 independent GEMVs per pass (717.9 MB, nothing
+    L2-resident across a pass).  Headline: the whole pass as ONE persistent launch (sc_decode.GemvList); beside it the same
+    pass as 112 launches from a CUDA graph, and per projection group (the reference's table, e2e/tune_07.py:63-66) the
+    latency per GEMV and GB/s over the 28 layers' weights of that group."""
     G = pkg.sc_decode
     xq = {k: torch.randint(-127, 128, (k,), dtype=torch.int8, device="cuda") for k in (2048, 6144)}
     xs = torch.full((1,), 0.01, device="cuda")
     res = torch.zeros(2048, dtype=torch.bfloat16, device="cuda")
+    EPI = dict(qkv=1, o=2, gu=3, down=2)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
+    def timed(run, n):
+        for _ in range(3):
+            run()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(n):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    def jobs_of(names):
+        return [(xq[lw[n][4]], lw[n][0], lw[n][1], xs, lw[n][2], lw[n][3], EPI[n], res if EPI[n] == 2 else None)
+                for lw in model.layers for n in names]
+
+    nbytes = sum(gemv_bytes(n, k) for lw in model.layers for (_, _, _, n, k) in lw.values())
+    n_gemv = 4 * len(model.layers)
+    whole = G.GemvList(jobs_of(("qkv", "o", "gu", "down")))
+    ms = timed(whole.run, reps)
+    out = dict(ms_per_step=ms, gemv_per_step=n_gemv, bytes_per_step=nbytes, gbs=nbytes / ms / 1e6, us_per_gemv=ms * 1e3 / n_gemv,
+               hbm_frac=nbytes / ms / 1e6 / pk["hbm_gbs"], launches_per_step=1,
+               form="one persistent launch over the list of 112 independent GEMVs (gemv_multi_kernel)")
+    groups = {}
+    for name in ("qkv", "o", "gu", "down"):
+        gl = G.GemvList(jobs_of((name,)))
+        gms = timed(gl.run, reps)
+        n, k = model.layers[0][name][3], model.layers[0][name][4]
+        gb = gemv_bytes(n, k) * len(model.layers)
+        groups[name] = dict(N=n, K=k, us_per_gemv=gms * 1e3 / len(model.layers), gbs=gb / gms / 1e6,
+                            hbm_frac=gb / gms / 1e6 / pk["hbm_gbs"])
+        del gl
+    out["groups"] = groups
+
+    # the same pass as one launch per GEMV (programmatic dependent launches replayed from a CUDA graph)
     def one_pass():
         for lw in model.layers:
-            for name, epi in (("qkv", 1), ("o", 2), ("gu", 3), ("down", 2)):
+            for name in ("qkv", "o", "gu", "down"):
                 codes, bc, ws, n, k = lw[name]
-                G.gemv(xq[k], codes, bc, xs, ws, n, epi, res=res if epi == 2 else None)
+                G.gemv(xq[k], codes, bc, xs, ws, n, EPI[name], res=res if EPI[name] == 2 else None)
     one_pass()
     torch.cuda.synchronize()
     g = torch.cuda.CUDAGraph()
@@ -209,46 +302,12 @@ def bench_decode(pkg, torch, model, reps=10):
         run = g.replay
     except Exception:
         run = one_pass
-    for _ in range(3):
-        run()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(reps):
-        run()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / reps
-    nbytes = sum(gemv_bytes(n, k) for lw in model.layers for (_, _, _, n, k) in lw.values())
-    out = dict(ms_per_step=ms, gemv_per_step=4 * len(model.layers), bytes_per_step=nbytes, gbs=nbytes / ms / 1e6,
-               us_per_gemv=ms * 1e3 / (4 * len(model.layers)))
-    # the GEMV kernel on a matrix large enough that launch latency does not matter: LM-head shaped, 151936 x 2048
-    # (vocabulary of the model family), 160 MB of packed weights per launch, three distinct launches per pass
-    F = pkg.sc_format
-    N, K = 151936, 2048
-    g = torch.Generator(device="cuda").manual_seed(5)
-    big = []
-    for _ in range(3):
-        w = torch.randn((N, K), generator=g, device="cuda") * 0.02
-        big.append(F.quantize_device(w, want_qw=False)[:3])
-        del w
-
-    def big_pass():
-        for c, b, w_ in big:
-            G.gemv(xq[K], c, b, xs, w_, N, 1)
-    big_reps = 2 * reps            # ~50 us per launch: a timed region of a few ms
-    for _ in range(4):
-        big_pass()
-    torch.cuda.synchronize()
-    e0.record()
-    for _ in range(big_reps):
-        big_pass()
-    e1.record()
-    torch.cuda.synchronize()
-    us = e0.elapsed_time(e1) / big_reps / len(big) * 1e3
-    out["kernel_roofline"] = dict(kernel="gemv_stream_kernel", workload="151936 x 2048 SC-MXFP4 GEMV", bound="hbm",
-                                  algorithmic_bytes_per_launch=gemv_bytes(N, K), us_per_launch=us,
-                                  achieved=gemv_bytes(N, K) / us / 1e3, unit="GB/s")
+    cms = timed(run, reps)
+    out["per_call_launches"] = dict(ms_per_step=cms, gbs=nbytes / cms / 1e6, us_per_gemv=cms * 1e3 / n_gemv,
+                                    hbm_frac=nbytes / cms / 1e6 / pk["hbm_gbs"], launches_per_step=n_gemv)
+    out["kernel_roofline"] = dict(kernel="gemv_multi_kernel", workload="the 112-GEMV pass above", bound="hbm",
+                                  algorithmic_bytes_per_launch=nbytes, us_per_launch=ms * 1e3, achieved=nbytes / ms / 1e6,
+                                  peak=pk["hbm_gbs"], frac=nbytes / ms / 1e6 / pk["hbm_gbs"], unit="GB/s")
     return out
 
 
@@ -339,6 +398,78 @@ def bench_moe(pkg, torch, dist=None, reps=5, weak=False, blk=None):
                 parallelism="single GPU" if world == 1 else f"ep{world}: {c['E'] // world} experts and {Lr} tokens per GPU, {exchange}")
 
 
+def parity_multi(pkg, torch, dist):
+    """Correctness evidence at world > 1, before any timing: a small tensor-parallel dense stack and a small
+    expert-parallel MoE block, each compared bit for bit with the single-GPU result computed on every rank (row sharding
+    and expert grouping are exact).  Returns {"tp": bool, "ep": bool}, true only if every rank agrees."""
+    F, S, P = pkg.sc_format, pkg.sc_kernels, pkg.parallel
+    rank, world = dist.get_rank(), dist.get_world_size()
+    ok = {}
+    M, hidden, Fd, layers = 256, 1024, 1536, 2
+    shapes = dict(qkv=(2048, hidden), o=(hidden, hidden), gu=(2 * Fd, hidden), down=(hidden, Fd))
+    g = torch.Generator(device="cuda").manual_seed(0)
+    full, local = [], []
+    for _ in range(layers):
+        lf, ll = {}, {}
+        for name, (n, k) in shapes.items():
+            wt = torch.randn((n, k), generator=g, device="cuda") * 0.02
+            if name == "gu":
+                wt = wt[torch.from_numpy(S.interleave_gate_up(n // 2)).cuda()]
+            c, b, s_, _, _ = F.quantize_device(wt.contiguous(), want_qw=False)
+            lf[name] = (c, b, s_, n, k)
+            ll[name] = P.shard_packed(c, b, s_, n, k, rank, world, 4)
+        full.append(lf)
+        local.append(ll)
+    h = torch.randn((M, hidden), generator=g, device="cuda").to(torch.bfloat16)
+    o = torch.randn((M, hidden), generator=g, device="cuda").to(torch.bfloat16)
+    ref = pkg.fused_dense.DenseStack(full, M, hidden, overlap=False).step(h, o)
+    w = hidden // world
+    hs, ol = h.view(M, world, w).permute(1, 0, 2).contiguous(), o[:, rank * w:(rank + 1) * w].contiguous()
+    try:
+        tp = P.PeerTensorParallelDense(pkg, local, M, hidden, Fd)
+    except Exception:   # noqa: BLE001
+        tp = P.TensorParallelDense(pkg, local, M, hidden)
+    out = tp.step(hs, ol)
+    ok["tp"] = bool(torch.equal(out.permute(1, 0, 2).reshape(M, hidden), ref))
+    E, k, D, Fm, L = 8 * max(1, world // 8), 2, 512, 256, 128 * world
+    perm = torch.from_numpy(S.interleave_gate_up(Fm)).cuda()
+
+    def pack(n, kk, tag, e0, e1, p=None):
+        cs, bs, ss = [], [], []
+        for e in range(e0, e1):
+            ge = torch.Generator(device="cuda").manual_seed(1000 * tag + e)
+            wt = torch.randn((n, kk), generator=ge, device="cuda") * 0.02
+            if p is not None:
+                wt = wt[p]
+            c, b, s_, _, _ = F.quantize_device(wt.contiguous(), want_qw=False)
+            cs.append(c); bs.append(b); ss.append(s_)
+        return torch.stack(cs), torch.stack(bs), torch.stack(ss)
+    blk_full = pkg.fused_moe.MoeBlock(pack(2 * Fm, D, 1, 0, E, perm), pack(D, Fm, 2, 0, E), E, k, D, Fm)
+    El = E // world
+    blk_loc = pkg.fused_moe.MoeBlock(pack(2 * Fm, D, 1, rank * El, (rank + 1) * El, perm),
+                                     pack(D, Fm, 2, rank * El, (rank + 1) * El), El, k, D, Fm)
+    hm = torch.randn((L, D), generator=g, device="cuda").to(torch.bfloat16)
+    lg = torch.randn((L, E), generator=g, device="cuda")
+    lg[:, E - 3] = -30.0                                           # an expert nobody routes to
+    refm = blk_full.step(hm, lg)
+    Lr = L // world
+    try:
+        ep = P.PeerExpertParallelMoe(pkg, blk_loc, E, k, Lr)
+    except Exception:   # noqa: BLE001
+        ep = P.ExpertParallelMoe(pkg, blk_loc, E, k)
+    sl = slice(rank * Lr, (rank + 1) * Lr)
+    o1 = ep.step(hm[sl].contiguous(), lg[sl].contiguous())
+    o2 = ep.step(hm[sl].contiguous(), lg[sl].contiguous())
+    ok["ep"] = bool(torch.equal(o1, refm[sl])) and bool(torch.equal(o2, o1))
+    torch.cuda.synchronize()
+    pkg._lib.check_status()
+    t = torch.tensor([int(ok["tp"]), int(ok["ep"])], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    del tp, ep
+    torch.cuda.empty_cache()
+    return dict(tp=bool(t[0].item()), ep=bool(t[1].item()), world=world)
+
+
 def gemm_only_roofline(pkg, torch, stack, pk, reps=3):
     """Average duration of the tcgen05 GEMM launches of one step, timed alone: every packed matrix is decoded to INT8
     beforehand (1.4 GB, far beyond L2), then the 112 GEMMs (with their real epilogues) are replayed back to back from a
@@ -372,18 +503,21 @@ def gemm_only_roofline(pkg, torch, stack, pk, reps=3):
     ms = e0.elapsed_time(e1) / reps
     n_launch = 4 * len(stack.layers)
     ops = qwen_ops(M, len(stack.layers))
-    peak = 2 * pk["bf16_tflops_sustained"]
+    peak = 2 * pk["bf16_tflops"]          # the replay lasts ~10 ms at full clock: the burst figure applies
     ach = ops / ms / 1e9
     return dict(kernel="gemm_i8_kernel (tcgen05 kind::i8)", bound="tensor", achieved=ach, peak=peak, unit="TOP/s", frac=ach / peak,
-                traffic=GEMM_TRAFFIC_BYTES, launches=n_launch, avg_launch_us=ms * 1e3 / n_launch,
-                algorithmic_ops_per_launch=ops / n_launch,
-                peak_note=f"2 x bf16_tflops_sustained of {pk['source']} peaks (MEASURED_PEAKS.json has no INT8 figure; the INT8 dense "
-                          f"rate is twice bf16); of nominal 4500 TOP/s: {ach / 4500:.3f}",
-                traffic_note="dram read+write of the gate|up launch from profiles/gemm_i8_kernel_gateup_2048x12288x2048.md; "
-                             "algorithmic operand bytes of that launch are 29.4 MB")
+                frac_of_nominal_4500=ach / 4500.0, traffic=NCU_GATEUP["dram_bytes"], launches=n_launch,
+                avg_launch_us=ms * 1e3 / n_launch, algorithmic_ops_per_launch=ops / n_launch,
+                peak_note=f"2 x bf16_tflops (burst) of {pk['source']} peaks: the file has no INT8 figure and the dense INT8 rate "
+                          "is twice bf16",
+                traffic_note=NCU_GATEUP["what"])
 
 
-GEMM_TRAFFIC_BYTES = 29.5e6 + 0.12e6
+# DRAM traffic of the dominant launch as one ncu capture recorded it (dram__bytes_read.sum + dram__bytes_write.sum); bench.py
+# cannot run the profiler itself, so the figure is carried here with what it was measured on.
+NCU_GATEUP = dict(dram_bytes=29.5e6 + 0.12e6,
+                  what="ncu --set full capture of one gate|up launch (2048 x 12288 x 2048, SwiGLU epilogue, `--case gemm`); "
+                       "algorithmic operand bytes of that launch: 29.4 MB")
 
 
 def run_ours(args):
@@ -400,6 +534,12 @@ def run_ours(args):
     if args.no_pdl:
         pkg._lib.call("scmx_set_pdl", 0)
     pk = peaks()
+    parity = None
+    if world > 1:
+        try:
+            parity = parity_multi(pkg, torch, dist)
+        except Exception as e:   # noqa: BLE001
+            parity = dict(tp=False, ep=False, error=f"{type(e).__name__}: {e}"[:200])
     M, layers, hidden = QWEN["M"], QWEN["layers"], 2048
     lw = build_dense_layers(pkg, torch, layers, shard=(rank, world))
     g = torch.Generator(device="cuda").manual_seed(123)
@@ -534,16 +674,15 @@ def run_ours(args):
                                         f"4 all-gathers per layer ({collectives})",
                             l2="inputs larger than L2: 718 MB of packed weights per step", cuda_graph=graph is not None),
                 clocks=clocks, e2e=e2e, gpu_launches=stack.launches_per_layer * layers * args.steps)
+    if parity is not None:
+        line["parity_multi"] = parity
     if args.dense_only:
         if rank == 0:
             print(json.dumps(line))
         return
     if world == 1:
         line["roofline"] = gemm_only_roofline(pkg, torch, stack, pk)
-        line["decode"] = bench_decode(pkg, torch, stack)
-        line["decode"]["hbm_frac"] = line["decode"]["gbs"] / pk["hbm_gbs"]
-        kr = line["decode"]["kernel_roofline"]
-        kr.update(peak=pk["hbm_gbs"], frac=kr["achieved"] / pk["hbm_gbs"])
+        line["decode"] = bench_decode(pkg, torch, stack, pk)
     del stack, lw, graph
     torch.cuda.empty_cache()
     try:
@@ -563,9 +702,18 @@ def run_ours(args):
         except Exception as e:   # noqa: BLE001
             line["models"] = dict(error=f"{type(e).__name__}: {e}")
     if rank == 0 and world == 1:
+        threads = blas_threads()
         dt, cops = cpu_dense_layer_sample()
-        line["cpu_baseline"] = dict(value=cops / dt / 1e12, unit="TOPS", cores=os.cpu_count(), kind="port",
+        line["cpu_baseline"] = dict(value=cops / dt / 1e12, unit="TOPS", cores=threads, kind="port",
                                     sample="1 of 28 layers at M=2048: act-quant + f64-BLAS INT32 GEMM + epilogue (NumPy oracle)")
+        gdt, gbytes = cpu_gemv_sample()
+        line["cpu_baseline"]["gemv"] = dict(value=gbytes / gdt / 1e9, unit="GB/s (of 4-bit packed bytes)", cores=1,
+                                            us_per_gemv=gdt / 4 * 1e6,
+                                            sample="the 4 GEMVs of one layer: int64 matrix-vector product (NumPy, no BLAS) + epilogue")
+        mdt, mtok = cpu_moe_sample()
+        line["cpu_baseline"]["moe"] = dict(value=mtok / mdt, unit="tokens/s (one half-block)", cores=threads,
+                                           sample=f"{mtok} tokens (4096 sorted rows): act-quant, per-expert f64-BLAS loop for "
+                                                  "gate|up + SwiGLU, act-quant, per-expert loop for down")
     if rank == 0:
         print(json.dumps(line))
     if world > 1:

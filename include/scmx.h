@@ -141,9 +141,20 @@ int scmx_mm_i8(const int8_t* xq, const int8_t* wq, int64_t M, int64_t N, int64_t
 int scmx_set_gemm_tile(int bn);
 
 /* Process-wide switches with no counterpart in the reference: programmatic dependent launch for the kernels of the chains
- * (default on) and the streaming (bulk-copy, persistent) form of the dense GEMV (default on).  For A/B measurements. */
+ * (default on) and the streaming (bulk-copy, persistent) form of the dense GEMV: mode 0 = never, 1 = for matrices of
+ * 16 MB of packed codes and more (default), 2 = whenever the shape allows it; other values are refused.  For A/B
+ * measurements and for tests of the streaming kernel on small shapes. */
 int scmx_set_pdl(int enable);
-int scmx_set_gemv_stream(int enable);
+int scmx_set_gemv_stream(int mode);
+
+/* Limit, in nanoseconds, of every bounded device-side wait of kernels launched afterwards (mbarrier waits of the GEMM
+ * and the streaming GEMV, the flag wait of scmx_peer_barrier); default 2 s, accepted range 1 us .. 60 s.  A wait that
+ * runs out stores a code in the kernel's status word (1..5 GEMM roles, 11 / 12 streaming GEMV, 20 peer barrier) and the
+ * kernel returns early.  Process-wide; no counterpart in the reference (failure detection, outside its scope). */
+int scmx_set_wait_limit_ns(unsigned long long ns);
+/* Registers, for the current device, the int32[4] status word used by kernels whose entry point takes no status
+ * argument (scmx_gemv's streaming kernel).  NULL (the default) = such kernels give up silently. */
+int scmx_set_status_word(int32_t* status);
 
 /* ---- grouped MoE GEMM ------------------------------------------------------------------------------------------- */
 
@@ -187,7 +198,9 @@ int scmx_moe_mm(const int8_t* xq, int64_t R, const uint32_t* codes, const uint8_
  * (two 8 MiB halves), held by every GPU that loads the library until the process exits.  The call allocates nothing.
  * Limit: one decoded expert matrix must fit one half, N * K <= 8 MiB (8388608); larger shapes return SCMX_ELIMIT.
  * The first call on a device looks up the array's device address (and, for epi 3, builds the SiLU table and
- * synchronises the stream once): make that first call before any stream capture.  All calls share the one array:
+ * synchronises the stream once): make that first call before any stream capture (during capture it is refused with
+ * SCMX_EINVAL).  The array comes into being when the library's code is first loaded on a device, so a host that
+ * reserves all remaining device memory for itself should make one warm-up call per device before doing so.  All calls share the one array:
  * every byte read from it is rewritten by the same call first, so contents left by an earlier call are never used,
  * but two calls whose kernels overlap on the GPU (different streams, or different threads on the same device) race. */
 int scmx_moe_mm_static(const int8_t* xq, int64_t R, const uint32_t* codes, const uint8_t* bcodes, const float* wscale,
@@ -263,6 +276,32 @@ int scmx_gemv(const int8_t* xq, const float* xscale, const uint32_t* codes, cons
               int64_t N, int64_t K, const scmx_format* fmt, int epi, const uint16_t* res, const int32_t* eidx,
               int n_routed, int shared, int xstride, void* out, int pdl, void* stream);
 
+/* Many independent dense GEMVs in one persistent launch.  A job is one y = epilogue(W x) as in scmx_gemv (no expert
+ * gather, no prologue); all jobs share the weight format.  The kernel streams the packed weights of all jobs through one
+ * shared-memory ring without pausing at matrix boundaries, so a list of small GEMVs runs at streaming bandwidth instead of
+ * paying a launch and a pipeline fill each.  Counterpart of issuing sc_decode.gemv once per weight set
+ * (e2e/sc_decode.py:208-238), batched the way the reference times it: a list of calls evaluated as one graph
+ * (e2e/tune_07.py:19-28).  Inputs of every job must be complete when the launch starts (jobs cannot feed each other).
+ * Limits: K % 128 == 0, K <= 8192, N % 4 == 0, K*bc_bits/(8*block) % 4 == 0, block 8, 16 or a multiple of 32, at most 512
+ * jobs; codes, bcodes, wscale and xq 16-byte aligned. */
+typedef struct scmx_gemv_job {
+    const uint32_t* codes;   /* u32 [N*K/8] */
+    const uint8_t* bcodes;   /* u8 [N, K*bc_bits/(8*block)] */
+    const float* wscale;     /* f32 [N] */
+    const int8_t* xq;        /* int8 [K] */
+    const float* xscale;     /* f32 [1] (unused for epi 0) */
+    const uint16_t* res;     /* bf16 [N], epi 2 only */
+    void* out;               /* epi 0: int32 [N]; 1, 2: bf16 [N]; 3: bf16 [N/2] */
+    int32_t N, K, epi;
+    int32_t plan[15];        /* filled by scmx_gemv_multi_plan; opaque */
+} scmx_gemv_job;
+/* Validates a HOST array of n jobs and fills their plan fields (tile shapes and the position of each job in the launch). */
+int scmx_gemv_multi_plan(scmx_gemv_job* jobs_host, int n, const scmx_format* fmt);
+/* Launches the planned list.  jobs_host: the planned host array; jobs_dev: a device copy of the same n records made by the
+ * caller after planning (ignored for n = 1).  status as in scmx_mm_i8 (codes 11 / 12). */
+int scmx_gemv_multi(const scmx_gemv_job* jobs_host, const scmx_gemv_job* jobs_dev, int n, const scmx_format* fmt,
+                    int32_t* status, int pdl, void* stream);
+
 /* scmx_gemv on a bf16 input row (or rows, xstride = 1) quantized inside the kernel: pro = 1 per-token INT8
  * (scmx_act_quant's arithmetic), pro = 2 RMSNorm with weights nw bf16 [K] and eps first (scmx_rmsnorm_quant's).
  * Every CTA computes the INT8 row in shared memory after its weight loads are in flight; results are bit-identical to
@@ -296,7 +335,7 @@ typedef struct scmx_decode_layer {
  * between the steps instead of kernel boundaries.  Same bits as scmx_rmsnorm_quant / scmx_gemv / scmx_qkv_norm /
  * scmx_attn_decode (with the same nsplit) / scmx_act_quant called in that order.
  * layers: device array; y bf16 [(hq + 2 hk) d], act bf16 [F], o bf16 [hq d], partials f32 [hq, nsplit, d + 2], barrier
- * uint32 [2] are scratch; counters int32 [hk] must be zero before the first call and is left zero; status int32 [1] receives 100 + k if barrier k timed out (0.5 s), after which the step's outputs are invalid.
+ * uint32 [2] are scratch; counters int32 [hk] is scratch too (zeroed by every call on its stream); status int32 [1] receives 100 + k if barrier k timed out (0.5 s), after which the step's outputs are invalid.
  * Limits: d = 128; D, F and hq*d multiples of 1024 up to 6144; hq/hk in {1, 2, 4}; hk * nsplit <= number of SMs.
  * Not to be run concurrently with other work on the same device: the launch needs every SM. */
 int scmx_decode_step_dense(const scmx_decode_layer* layers, int n_layers, int D, int F, int hq, int hk, int d, float eps,

@@ -26,6 +26,13 @@ class ScmxDecodeLayer(ctypes.Structure):
                 ("k_norm", ctypes.c_void_p), ("k_cache", ctypes.c_void_p), ("v_cache", ctypes.c_void_p)]
 
 
+class ScmxGemvJob(ctypes.Structure):
+    """Mirror of `scmx_gemv_job` in include/scmx.h (128 bytes)."""
+    _fields_ = [("codes", ctypes.c_void_p), ("bcodes", ctypes.c_void_p), ("wscale", ctypes.c_void_p), ("xq", ctypes.c_void_p),
+                ("xscale", ctypes.c_void_p), ("res", ctypes.c_void_p), ("out", ctypes.c_void_p), ("N", ctypes.c_int32),
+                ("K", ctypes.c_int32), ("epi", ctypes.c_int32), ("plan", ctypes.c_int32 * 15)]
+
+
 class ScmxError(RuntimeError):
     """A libscmx entry point returned a non-zero status."""
 
@@ -52,6 +59,8 @@ SIGNATURES = {
     "scmx_mm_i8": [c_vp, c_vp, c_i64, c_i64, c_i64, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp],
     "scmx_set_gemm_tile": [c_int],
     "scmx_set_pdl": [c_int],
+    "scmx_set_wait_limit_ns": [ctypes.c_uint64],
+    "scmx_set_status_word": [c_vp],
     "scmx_set_gemv_stream": [c_int],
     "scmx_route_sort": [c_vp, c_i64, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp],
     "scmx_router_topk": [c_vp, c_i64, c_int, c_int, c_vp, c_vp, c_vp, c_vp],
@@ -80,6 +89,8 @@ SIGNATURES = {
     "scmx_set_decode_trace": [c_vp, c_int],
     "scmx_gemv_pro": [c_vp, c_int, c_vp, c_float, c_vp, c_vp, c_vp, c_i64, c_i64, _FMT_P, c_int, c_vp, c_vp, c_int, c_int, c_int,
                       c_vp, c_int, c_vp],
+    "scmx_gemv_multi_plan": [c_vp, c_int, _FMT_P],
+    "scmx_gemv_multi": [c_vp, c_vp, c_int, _FMT_P, c_vp, c_int, c_vp],
     "scmx_gemv": [c_vp, c_vp, c_vp, c_vp, c_vp, c_i64, c_i64, _FMT_P, c_int, c_vp, c_vp, c_int, c_int, c_int, c_vp,
                   c_int, c_vp],
 }
@@ -136,6 +147,8 @@ def status_buffer():
     dev = torch.cuda.current_device()
     if dev not in _status:
         _status[dev] = torch.zeros(4, dtype=torch.int32, device=f"cuda:{dev}")
+        with torch.cuda.device(dev):      # kernels whose entry point takes no status argument report here too
+            call("scmx_set_status_word", c_vp(_status[dev].data_ptr()))
     return _status[dev]
 
 
@@ -145,5 +158,18 @@ def check_status():
     v = st.cpu().tolist()
     if v[0] != 0:
         st.zero_()
-        raise ScmxError(f"device-side wait ran out: role {v[0]} in CTA {v[1]} thread {v[2]} "
-                        "(1 producer/free stage, 2 MMA/free accumulator, 3 MMA/operands, 4 epilogue/accumulator)")
+        raise ScmxError(f"device-side wait ran out: {describe_status(v[0])} (CTA or rank {v[1]}, thread {v[2]})")
+
+
+_GEMM_ROLES = {1: "GEMM producer waiting for a free stage", 2: "GEMM MMA warp waiting for a free accumulator",
+               3: "GEMM MMA warp waiting for operands", 4: "GEMM epilogue waiting for an accumulator",
+               5: "GEMM CTA pair waiting for its peer", 11: "streaming GEMV producer waiting for a free stage",
+               12: "streaming GEMV consumer waiting for a tile", 20: "peer barrier waiting for another rank's flag"}
+
+
+def describe_status(code):
+    """Text for a status-word code: 1..5 GEMM roles, 11 / 12 streaming GEMV, 20 peer barrier, 100 + k = grid barrier k of
+    the one-kernel decode step."""
+    if code >= 100:
+        return f"decode step: grid barrier {code - 100} timed out"
+    return _GEMM_ROLES.get(code, f"code {code}")

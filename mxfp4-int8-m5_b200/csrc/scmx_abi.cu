@@ -7,6 +7,28 @@ namespace scmx {
 
 static thread_local char g_err[512] = "no error";
 int g_use_pdl = 1;
+unsigned long long g_wait_limit_ns = 2000000000ull;
+static int32_t* g_status_word[64] = {};
+
+int current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+    return dev;
+}
+int sm_count() {
+    static int n[64] = {};
+    const int dev = current_device();
+    if (dev < 0) return 148;
+    if (!n[dev]) {
+        if (cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n[dev] <= 0) n[dev] = 148;
+    }
+    return n[dev];
+}
+int32_t* device_status_word() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    return g_status_word[dev];
+}
 
 void set_error(const char* fmt, ...) {
     va_list ap;
@@ -61,6 +83,18 @@ int make_dev_format(const scmx_format* fmt, DevFormat* out) {
 
 extern "C" const char* scmx_last_error_string(void) { return scmx::g_err; }
 extern "C" int scmx_abi_version(void) { return 1; }
+extern "C" int scmx_set_wait_limit_ns(unsigned long long ns) {
+    SCMX_REQUIRE(ns >= 1000ull && ns <= 60000000000ull, SCMX_EINVAL, "set_wait_limit_ns: %llu outside 1 us .. 60 s", ns);
+    scmx::g_wait_limit_ns = ns;
+    return SCMX_OK;
+}
+extern "C" int scmx_set_status_word(int32_t* status) {
+    int dev = 0;
+    SCMX_CUDA_OK(cudaGetDevice(&dev));
+    SCMX_REQUIRE(dev >= 0 && dev < 64, SCMX_ELIMIT, "device ordinal %d out of range", dev);
+    scmx::g_status_word[dev] = status;
+    return SCMX_OK;
+}
 extern "C" int scmx_set_pdl(int enable) {
     scmx::g_use_pdl = enable ? 1 : 0;
     return SCMX_OK;

@@ -16,6 +16,13 @@ void set_error(const char* fmt, ...);
 // kernel performs all its reads of activations and all its writes after pdl_wait(), so by induction along the stream
 // nothing earlier is still running when a kernel touches memory.
 extern int g_use_pdl;
+// Limit of every bounded device-side wait in nanoseconds (scmx_set_wait_limit_ns; default 2 s), handed to the kernels as an
+// argument, and the per-device status word registered with scmx_set_status_word for kernels whose entry point takes none.
+extern unsigned long long g_wait_limit_ns;
+int32_t* device_status_word();
+// Ordinal of the current device (0..63; -1 on error) and its SM count, cached per device: one process may drive several GPUs.
+int current_device();
+int sm_count();
 
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }

@@ -462,13 +462,15 @@ extern "C" int scmx_decode_step_dense(const scmx_decode_layer* layers, int n_lay
     SCMX_REQUIRE(D % 1024 == 0 && F % 1024 == 0 && (hq * d) % 1024 == 0 && D <= MK_MAXK && F <= MK_MAXK && hq * d <= MK_MAXK,
                  SCMX_ELIMIT, "decode_step: widths D=%d F=%d hq*d=%d must be multiples of 1024 up to %d", D, F, hq * d, MK_MAXK);
     SCMX_REQUIRE(capacity >= 1 && nsplit >= 1 && nsplit <= 32, SCMX_EINVAL, "decode_step: capacity=%lld nsplit=%d", (long long)capacity, nsplit);
-    static int n_sm = 0, coop = 0;
-    if (!n_sm) {
-        int dev = 0;
-        SCMX_CUDA_OK(cudaGetDevice(&dev));
-        SCMX_CUDA_OK(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
-        SCMX_CUDA_OK(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+    static int coop_dev[64] = {};            // 0 unknown, 1 supported, -1 not: per device
+    const int dev = current_device();
+    SCMX_REQUIRE(dev >= 0, SCMX_ECUDA, "decode_step: no current CUDA device (ordinal 0..63)");
+    if (!coop_dev[dev]) {
+        int c = 0;
+        SCMX_CUDA_OK(cudaDeviceGetAttribute(&c, cudaDevAttrCooperativeLaunch, dev));
+        coop_dev[dev] = c ? 1 : -1;
     }
+    const int coop = coop_dev[dev] > 0, n_sm = sm_count();
     SCMX_REQUIRE(coop, SCMX_EDEVICE, "decode_step: the device does not support cooperative launches");
     SCMX_REQUIRE(hk * nsplit <= n_sm, SCMX_EINVAL, "decode_step: hk * nsplit = %d exceeds the %d CTAs of the grid", hk * nsplit, n_sm);
     MkArgs a;
@@ -478,6 +480,8 @@ extern "C" int scmx_decode_step_dense(const scmx_decode_layer* layers, int n_lay
     a.trace = g_trace; a.n_trace = g_n_trace & 0xFFFF; a.trace_barrier = g_n_trace >> 16;
     cudaStream_t st = (cudaStream_t)stream;
     SCMX_CUDA_OK(cudaMemsetAsync(barrier, 0, 2 * sizeof(uint32_t), st));
+    // tickets taken by a step that gave up on a barrier are not returned: start every step from zero
+    SCMX_CUDA_OK(cudaMemsetAsync(counters, 0, (size_t)hk * sizeof(int32_t), st));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)n_sm);
     cfg.blockDim = dim3(MK_THREADS);

@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(128) ep_dispatch_kernel(const int8_t* __restri
 }
 
 // flags: int32 [world] on every GPU; slot r of GPU g's array is written by rank r.  epoch lives on the local GPU.
-__global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int world, int32_t* epoch, int32_t* status) {
+__global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int world, int32_t* epoch, int32_t* status, uint64_t limit_ns) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ int s_epoch;
@@ -73,7 +73,7 @@ __global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int world, int32_t
         volatile int32_t* mine = reinterpret_cast<volatile int32_t*>(flags.p[rank]) + threadIdx.x;
         const uint64_t t0 = globaltimer_ns();
         while (*mine < ep) {
-            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            if (globaltimer_ns() - t0 > limit_ns) {
                 if (atomicCAS(status, 0, 20) == 0) { status[1] = rank; status[2] = threadIdx.x; }
                 break;
             }
@@ -280,7 +280,7 @@ extern "C" int scmx_peer_barrier(const void* const* flag_peers, int rank, int wo
     int rc = fill_peers(&f, flag_peers, world, "peer_barrier");
     if (rc) return rc;
     SCMX_REQUIRE(rank >= 0 && rank < world && epoch && status, SCMX_EINVAL, "peer_barrier: bad rank / epoch / status");
-    launch_pdl(peer_barrier_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, f, rank, world, epoch, status);
+    launch_pdl(peer_barrier_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, f, rank, world, epoch, status, (uint64_t)g_wait_limit_ns);
     SCMX_LAUNCH_OK("peer_barrier_kernel");
     return SCMX_OK;
 }

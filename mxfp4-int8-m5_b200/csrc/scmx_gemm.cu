@@ -41,6 +41,7 @@ struct GemmArgs {
     int E;
     int e_begin, e_end;          // grouped: experts handled by this launch; B rows are relative to e_begin
     int32_t* status;
+    uint64_t wait_ns;            // limit of every mbarrier wait
     const uint16_t* silu_lut;    // 65536-entry bf16 table of silu(g) indexed by the bf16 bits of g (EPI 3)
     // EPI 1 with a return map (expert parallelism): output row r is stored at row ret_row[r] of peer_out[ret_rank[r]], the
     // buffer of the GPU the token came from, instead of row r of `out`: the GEMM's epilogue is the return exchange.
@@ -305,7 +306,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_i8_kernel(const __grid_co
             for (int t = blockIdx.x; t < total && fail == 0; t += gridDim.x) {
                 const Tile tl = get_tile<BN>(a, t, tiles_m, slot0);
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    if (int w = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag)) { fail = w == 1 ? 1 : -1; break; }
+                    if (int w = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, a.wait_ns)) { fail = w == 1 ? 1 : -1; break; }
                     const uint32_t sa = sbase + stage * L::STAGE_BYTES, sb = sa + L::A_BYTES;
                     mbar_expect_tx(bar_full + 8 * stage, L::STAGE_BYTES);
                     tma_load_2d(sa, &tmA, kb * BK, tl.row0, bar_full + 8 * stage);
@@ -321,11 +322,11 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_i8_kernel(const __grid_co
             int stage = 0;
             uint32_t phase = 0, acc = 0, acc_phase = 0;
             for (int t = blockIdx.x; t < total && fail == 0; t += gridDim.x) {
-                if (int w = mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag)) { fail = w == 1 ? 2 : -1; break; }
+                if (int w = mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, a.wait_ns)) { fail = w == 1 ? 2 : -1; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    if (int w = mbar_wait(bar_full + 8 * stage, phase, abort_flag)) { fail = w == 1 ? 3 : -1; break; }
+                    if (int w = mbar_wait(bar_full + 8 * stage, phase, abort_flag, a.wait_ns)) { fail = w == 1 ? 3 : -1; break; }
                     tc_fence_after();
                     const uint32_t sa = sbase + stage * L::STAGE_BYTES, sb = sa + L::A_BYTES;
                     const uint64_t da = umma_desc(sa), db = umma_desc(sb);
@@ -356,7 +357,7 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_i8_kernel(const __grid_co
             if (a.epi != 0) {
                 for (int i = et; i < BN; i += EPI_THREADS) ws[i] = (tl.n0 + i < a.N) ? a.wscale[tl.wrow + i] : 0.0f;
             }
-            if (int w = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) fail = w == 1 ? 4 : -1;
+            if (int w = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, a.wait_ns)) fail = w == 1 ? 4 : -1;
             // the epilogue threads agree on giving up (and see the staged scales) before anyone touches TMEM
             epilogue_bar();
             if (*abort_flag) { if (!fail) fail = -1; break; }
@@ -474,25 +475,17 @@ static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, 
 }
 
 static int g_bn_override = 0;      // 0 = choose per problem
-static int g_num_sms = 0;
-
-static int num_sms() {
-    if (!g_num_sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
-        if (g_num_sms <= 0) g_num_sms = 148;
-    }
-    return g_num_sms;
-}
+static int num_sms() { return sm_count(); }
 
 template <int BN, int STAGES>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& a, int grid, cudaStream_t st) {
     using L = Smem<BN, STAGES>;
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {};      // the attribute belongs to the current device's copy of the kernel
+    const int dev = current_device();
+    SCMX_REQUIRE(dev >= 0, SCMX_ECUDA, "no current CUDA device (ordinal 0..63)");
+    if (!configured[dev]) {
         SCMX_CUDA_OK(cudaFuncSetAttribute(gemm_i8_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-        configured = true;
+        configured[dev] = true;
     }
     launch_pdl(gemm_i8_kernel<BN, STAGES>, dim3(grid), dim3(CTA_THREADS), (size_t)L::TOTAL, st, tmA, tmB, a);
     SCMX_LAUNCH_OK("gemm_i8_kernel");
@@ -501,6 +494,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
 
 static int run_gemm(const int8_t* xq, int64_t a_rows, const int8_t* wq, int64_t b_rows, GemmArgs& a, cudaStream_t st) {
     int bn = g_bn_override ? g_bn_override : (a.N >= 256 ? 256 : 128);
+    a.wait_ns = g_wait_limit_ns;
     if (a.epi == 3) {
         int rc3 = silu_lut_ptr(st, &a.silu_lut);
         if (rc3) return rc3;
@@ -690,12 +684,16 @@ static __device__ __align__(256) int8_t g_moe_static_scratch[2 * MOE_STATIC_HALF
 
 // The array's name is only a host-side handle; kernels need its device address, looked up once per device with that
 // device current.
-static int moe_static_scratch_ptr(int8_t** out) {
+static int moe_static_scratch_ptr(cudaStream_t st, int8_t** out) {
     static int8_t* ptrs[64] = {};
     int dev = 0;
     SCMX_CUDA_OK(cudaGetDevice(&dev));
     SCMX_REQUIRE(dev >= 0 && dev < 64, SCMX_ELIMIT, "device ordinal %d out of range", dev);
     if (!ptrs[dev]) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        SCMX_CUDA_OK(cudaStreamIsCapturing(st, &cap));
+        SCMX_REQUIRE(cap == cudaStreamCaptureStatusNone, SCMX_EINVAL,
+                     "moe_mm_static: the first call on a device looks up the built-in scratch; make it outside stream capture");
         int8_t* p = nullptr;
         const cudaError_t e = cudaGetSymbolAddress((void**)&p, g_moe_static_scratch);
         if (e != cudaSuccess || p == nullptr) {
@@ -728,7 +726,7 @@ extern "C" int scmx_moe_mm_static(const int8_t* xq, int64_t R, const uint32_t* c
                  (long long)(N * K), (long long)MOE_STATIC_HALF_BYTES);
     if (R == 0) return SCMX_OK;
     int8_t* scratch = nullptr;
-    rc = moe_static_scratch_ptr(&scratch);
+    rc = moe_static_scratch_ptr((cudaStream_t)stream, &scratch);
     if (rc) return rc;
     const int epp = (int)(MOE_STATIC_HALF_BYTES / (N * K));      // experts decoded per pass (>= 1)
     const int64_t half = MOE_STATIC_HALF_BYTES;

@@ -16,6 +16,10 @@
 
 namespace scmx {
 
+// scmx_gemv_multi.cu
+int gemv_stream_single(const int8_t* xq, const float* xscale, const uint32_t* codes, const uint8_t* bcodes, const float* wscale,
+                       int64_t N, int64_t K, const DevFormat& f, int epi, const uint16_t* res, void* out, int pdl, cudaStream_t st);
+
 struct GemvArgs {
     const int8_t* xq;
     const float* xscale;
@@ -35,24 +39,6 @@ struct GemvArgs {
     DevFormat f;
 };
 
-// sum over the 8 codes of word w of (+-x) * magnitude: 11 instructions
-__device__ __forceinline__ int word_dot(uint32_t w, uint32_t x0, uint32_t xn0, uint32_t x1, uint32_t xn1, uint32_t mlo, uint32_t mhi,
-                                        int acc) {
-    const uint32_t sel = w & 0x77777777u;
-    const uint32_t ssel = ((w >> 1) & 0x44444444u) | 0x32103210u;
-    acc = dp4a_ss(prmt(x0, xn0, ssel), prmt(mlo, mhi, sel), acc);
-    return dp4a_ss(prmt(x1, xn1, ssel >> 16), prmt(mlo, mhi, sel >> 16), acc);
-}
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ uint32_t lds8(uint32_t addr) {
-    uint32_t v;
-    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
-    return v;
-}
 
 // PRO 0: INT8 input row and its scale are given.  PRO 1 / 2: the input is a bf16 row; every CTA first computes the
 // per-token INT8 row (PRO 2: of its RMSNorm) in shared memory with the arithmetic of the row kernels (act_quant,
@@ -251,232 +237,6 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvArgs a) {
     }
 }
 
-// ---- streaming variant for dense GEMVs ------------------------------------------------------------------------------------
-// A persistent CTA (one per SM, 544 threads) walks over tiles of TR consecutive weight rows.  The rows of a tile are
-// contiguous in the packed layout, so one thread streams each tile into a shared-memory ring with two untiled bulk copies
-// (codes, block codes) that complete on an mbarrier; sixteen consumer warps expand and accumulate from shared memory
-// (warp = 4 rows x one K split) and release the stage through a second mbarrier.  Copies run STAGES tiles ahead of the
-// arithmetic, and since weights do not depend on the previous kernel they start before griddepcontrol.wait: with one CTA
-// of < 112 KB per SM the next GEMV of a chain is already resident and filling its ring while this one finishes.
-constexpr int SG_STAGE_BYTES = 65536;      // packed codes per stage
-constexpr int SG_BC_BYTES = 2048;          // block codes per stage
-constexpr int SG_X_BYTES = 8192;           // INT8 activations (K <= 8192)
-constexpr int SG_STAGES = 3;
-constexpr int SG_NW = 16;                  // consumer warps
-constexpr int SG_THREADS = 32 * (SG_NW + 1);   // consumer warps + 1 producer warp
-
-struct StreamArgs {
-    GemvArgs g;
-    int tr;            // rows per tile (4, 8, 16, 32 or 64)
-    int n_tiles;
-    int mode;          // 0 normal; 1 = measurement aid: stream the tiles but skip the arithmetic
-    int32_t* status;
-};
-
-template <bool B32>
-__global__ void __launch_bounds__(SG_THREADS, 1) gemv_stream_kernel(const StreamArgs sa) {
-    extern __shared__ uint8_t smem_raw[];
-    const GemvArgs& a = sa.g;
-    uint8_t* smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);     // stays a shared-space pointer
-    // layout: [STAGES][codes 64 KB][bcodes 2 KB] | x (K bytes) | split-K sums [4][16][4] | split-K counters [4][16] |
-    //         barriers | abort flag
-    uint8_t* s_x = smem + SG_STAGES * (SG_STAGE_BYTES + SG_BC_BYTES);
-    int* s_part = reinterpret_cast<int*>(s_x + SG_X_BYTES);
-    int* s_cnt = s_part + 256;
-    const uint32_t bar_full = smem_u32(s_cnt + 64), bar_empty = bar_full + 8 * SG_STAGES;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(s_cnt + 64 + 4 * SG_STAGES);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int K = a.K, row_bytes = K / 2, bc_row = a.bc_row_bytes;
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < SG_STAGES; ++s) {
-            mbar_init(bar_full + 8 * s, 1);
-            mbar_init(bar_empty + 8 * s, SG_NW);
-        }
-        *abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
-    if (threadIdx.x < 320) s_part[threadIdx.x] = 0;      // split-K sums and counters
-    pdl_launch_dependents();
-    __syncthreads();
-    int fail = 0;
-    if (warp == SG_NW) {
-        // ---- producer: weights only, so it does not wait for the previous kernel
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            for (int t = blockIdx.x; t < sa.n_tiles; t += gridDim.x) {
-                if (int w = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag)) { fail = w == 1 ? 1 : -1; break; }
-                const int r0 = t * sa.tr;
-                const int rows = min(sa.tr, a.N - r0);
-                const uint32_t dst = smem_u32(smem + stage * (SG_STAGE_BYTES + SG_BC_BYTES));
-                const uint32_t nb_codes = (uint32_t)rows * row_bytes, nb_bc = (uint32_t)rows * bc_row;
-                mbar_expect_tx(bar_full + 8 * stage, nb_codes + nb_bc);
-                bulk_load(dst, reinterpret_cast<const uint8_t*>(a.codes) + (size_t)r0 * row_bytes, nb_codes, bar_full + 8 * stage);
-                bulk_load(dst + SG_STAGE_BYTES, a.bcodes + (size_t)r0 * bc_row, nb_bc, bar_full + 8 * stage);
-                if (++stage == SG_STAGES) { stage = 0; phase ^= 1; }
-            }
-        }
-    } else {
-        // ---- consumers: activations come from the previous kernel
-        pdl_wait();
-        for (int i = threadIdx.x; i < K / 16; i += 32 * SG_NW)
-            reinterpret_cast<uint4*>(s_x)[i] = reinterpret_cast<const uint4*>(a.xq)[i];
-        asm volatile("bar.sync 1, %0;" ::"n"(32 * SG_NW) : "memory");
-        const int rg = sa.tr / 4;                 // row groups per tile
-        const int sk = SG_NW / rg;                // K splits per row group
-        const int rgi = warp % rg, ks = warp / rg;
-        const int kbeg = ks * (K / sk), kend = kbeg + K / sk;
-        const float xs = a.epi != 0 ? a.xscale[0] : 0.0f;
-        const uint32_t mlo = a.f.mag_lo, mhi = a.f.mag_hi;
-        // A lane visits the same K offsets in every tile.  When its K range is at most two steps of 1024 codes the
-        // activations (and their negations) for those offsets stay in registers for the whole kernel.
-        const bool xcache = (kend - kbeg) <= 2048;
-        uint32_t xr[2][8], xnr[2][8];
-#pragma unroll
-        for (int sidx = 0; sidx < 2; ++sidx) {
-            const int k0 = kbeg + lane * 32 + sidx * 1024;
-            const bool ok = xcache && k0 < kend;
-            const uint4 xa = ok ? *reinterpret_cast<const uint4*>(s_x + k0) : make_uint4(0, 0, 0, 0);
-            const uint4 xb = ok ? *reinterpret_cast<const uint4*>(s_x + k0 + 16) : make_uint4(0, 0, 0, 0);
-            const uint32_t xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-#pragma unroll
-            for (int j = 0; j < 8; ++j) { xr[sidx][j] = xv[j]; xnr[sidx][j] = neg4(xv[j]); }
-        }
-        // block-code byte offset and bit shift of the lane's (up to two cached) K offsets: the same for every row and tile
-        uint32_t bc_off[2], bc_sh[2];
-#pragma unroll
-        for (int sidx = 0; sidx < 2; ++sidx) {
-            const int blk = block_of(a.f, kbeg + lane * 32 + sidx * 1024);
-            bc_off[sidx] = (uint32_t)(blk >> a.f.pb_shift);
-            bc_sh[sidx] = (uint32_t)((blk & a.f.pb_mask) << a.f.bc_shift);
-        }
-        const uint32_t row_off = (uint32_t)(4 * rgi) * (uint32_t)row_bytes, rb_off = SG_STAGE_BYTES + (uint32_t)(4 * rgi) * (uint32_t)bc_row;
-        int stage = 0, it = 0;
-        uint32_t phase = 0;
-        for (int t = blockIdx.x; t < sa.n_tiles; t += gridDim.x) {
-            if (int w = mbar_wait(bar_full + 8 * stage, phase, abort_flag)) { fail = w == 1 ? 2 : -1; }
-            if (fail) break;
-            const uint8_t* st = smem + stage * (SG_STAGE_BYTES + SG_BC_BYTES);
-            const uint32_t st_s = smem_u32(st);
-            const int r0 = t * sa.tr + 4 * rgi;      // first of this warp's 4 rows
-            const bool rows_ok = r0 < a.N;
-            int tot[4] = {0, 0, 0, 0};
-            if (rows_ok) {
-#pragma unroll 2
-                for (int sidx = 0; sidx < 32; ++sidx) {
-                    const int k0 = kbeg + lane * 32 + sidx * 1024;
-                    if (k0 >= kend) break;
-                    uint32_t x[8], xn[8];
-                    if (xcache) {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) { x[j] = xr[sidx & 1][j]; xn[j] = xnr[sidx & 1][j]; }
-                    } else {
-                        const uint4 xa = *reinterpret_cast<const uint4*>(s_x + k0);
-                        const uint4 xb = *reinterpret_cast<const uint4*>(s_x + k0 + 16);
-                        const uint32_t xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) { x[j] = xv[j]; xn[j] = neg4(xv[j]); }
-                    }
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) {
-                        const uint32_t row_s = st_s + row_off + (uint32_t)r * (uint32_t)row_bytes;
-                        const uint4 wv = lds128(row_s + (uint32_t)(k0 >> 1));
-                        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
-                        if (sa.mode == 1) { tot[r] += (int)(ww[0] ^ ww[1] ^ ww[2] ^ ww[3] ^ x[r]); continue; }
-                        const uint32_t rb_s = st_s + rb_off + (uint32_t)r * (uint32_t)bc_row;
-                        const uint8_t* rb = st + SG_STAGE_BYTES + (size_t)(4 * rgi + r) * bc_row;
-                        if (B32) {
-                            uint32_t code;
-                            if (xcache) {
-                                code = (lds8(rb_s + bc_off[sidx & 1]) >> bc_sh[sidx & 1]) & a.f.bc_mask;
-                            } else {
-                                const int blk = block_of(a.f, k0);
-                                code = (lds8(rb_s + (uint32_t)(blk >> a.f.pb_shift)) >> ((blk & a.f.pb_mask) << a.f.bc_shift)) & a.f.bc_mask;
-                            }
-                            int bs = 0;
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) bs = word_dot(ww[j], x[2 * j], xn[2 * j], x[2 * j + 1], xn[2 * j + 1], mlo, mhi, bs);
-                            tot[r] += a.f.pow2 ? (bs << code) : bs * (int)fmt_mult(a.f, code);
-                        } else {
-                            const int bit0 = (k0 >> a.f.block_shift) << a.f.bc_shift;
-                            const int nbytes = (((32 >> a.f.block_shift) << a.f.bc_shift) + 7) / 8;
-                            uint32_t bcv = 0;
-                            for (int i = 0; i < nbytes; ++i) bcv |= (uint32_t)rb[bit0 / 8 + i] << (8 * i);
-                            bcv >>= (bit0 % 8);
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const int bi = (8 * j) >> a.f.block_shift;
-                                const uint32_t code = (bcv >> (bi << a.f.bc_shift)) & a.f.bc_mask;
-                                const uint32_t sel = ww[j] & 0x77777777u;
-                                const uint32_t ssel = ((ww[j] >> 1) & 0x44444444u) | 0x32103210u;
-                                int bs = __dp4a((int)__byte_perm(x[2 * j], xn[2 * j], ssel), (int)__byte_perm(a.f.mag_lo, a.f.mag_hi, sel), 0);
-                                bs = __dp4a((int)__byte_perm(x[2 * j + 1], xn[2 * j + 1], ssel >> 16),
-                                            (int)__byte_perm(a.f.mag_lo, a.f.mag_hi, sel >> 16), bs);
-                                tot[r] += bs * (int)fmt_mult(a.f, code);
-                            }
-                        }
-                    }
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_empty + 8 * stage);       // this warp no longer reads the stage
-            if (++stage == SG_STAGES) { stage = 0; phase ^= 1; }
-#pragma unroll
-            for (int r = 0; r < 4; ++r) tot[r] = warp_sum(tot[r]);
-            bool writer = lane == 0;
-            if (sk > 1 && lane == 0) {
-                // add the K splits of a row group (exact integers) without a barrier: the last split to arrive finishes
-                int* accp = s_part + ((it & 3) * 16 + rgi) * 4;
-#pragma unroll
-                for (int r = 0; r < 4; ++r) atomicAdd(accp + r, tot[r]);
-                __threadfence_block();
-                const int c = atomicAdd(s_cnt + (it & 3) * 16 + rgi, 1);
-                writer = c == sk - 1;
-                if (writer) {
-                    __threadfence_block();
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) tot[r] = atomicExch(accp + r, 0);
-                    atomicExch(s_cnt + (it & 3) * 16 + rgi, 0);
-                }
-            }
-            ++it;
-            if (writer && rows_ok) {
-                const float* ws = a.wscale + r0;
-                if (a.epi == 0) {
-                    int32_t* o = reinterpret_cast<int32_t*>(a.out) + r0;
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) o[r] = tot[r];
-                } else {
-                    float y[4];
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) y[r] = scale_acc(tot[r], xs, ws[r]);
-                    uint16_t* out = reinterpret_cast<uint16_t*>(a.out);
-                    if (a.epi == 1) {
-#pragma unroll
-                        for (int r = 0; r < 4; ++r) out[r0 + r] = f32_to_bf16(y[r]);
-                    } else if (a.epi == 2) {
-#pragma unroll
-                        for (int r = 0; r < 4; ++r) out[r0 + r] = f32_to_bf16(__fadd_rn(bf16_to_f32(a.res[r0 + r]), y[r]));
-                    } else {
-                        out[r0 / 2] = f32_to_bf16(swiglu_bf16(y[0], y[2]));
-                        out[r0 / 2 + 1] = f32_to_bf16(swiglu_bf16(y[1], y[3]));
-                    }
-                }
-            }
-        }
-    }
-    if (fail > 0 && sa.status && atomicCAS(sa.status, 0, 10 + fail) == 0) {
-        sa.status[1] = blockIdx.x;
-        sa.status[2] = threadIdx.x;
-    }
-    __syncthreads();
-    if (*abort_flag) {      // give outstanding bulk copies time to land before the shared memory is released
-        const uint64_t t0 = globaltimer_ns();
-        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
-    }
-}
-
 template <int STEPS, bool B32>
 static cudaError_t launch_gemv(const GemvArgs& a, dim3 grid, int threads, int pdl, cudaStream_t st) {
     cudaLaunchConfig_t cfg = {};
@@ -500,9 +260,10 @@ static cudaError_t launch_gemv(const GemvArgs& a, dim3 grid, int threads, int pd
 
 using namespace scmx;
 
-static int g_gemv_stream = 1;
-extern "C" int scmx_set_gemv_stream(int enable) {
-    g_gemv_stream = enable;
+static int g_gemv_stream = 1;      // 0 never, 1 for matrices of 16 MB and more, 2 whenever the shape allows
+extern "C" int scmx_set_gemv_stream(int mode) {
+    SCMX_REQUIRE(mode >= 0 && mode <= 2, SCMX_EINVAL, "set_gemv_stream: mode=%d (0 off, 1 automatic, 2 whenever the shape allows)", mode);
+    g_gemv_stream = mode;
     return SCMX_OK;
 }
 
@@ -542,45 +303,13 @@ static int gemv_impl(const int8_t* xq, const float* xscale, const uint16_t* xbf,
     a.xq = xq; a.xscale = xscale; a.codes = codes; a.bcodes = bcodes; a.wscale = wscale; a.res = res; a.eidx = eidx;
     a.out = out; a.N = (int)N; a.K = (int)K; a.epi = epi; a.n_routed = n_routed; a.shared = shared; a.xstride = xstride;
     a.bc_row_bytes = (int)(K / (a.f.block * a.f.blocks_per_byte));
-    // ---- streaming kernel for dense GEMVs whose tiles satisfy the bulk-copy alignment rules
-    // (matrices under 16 MB finish within a few microseconds either way and start faster with the register kernel below)
-    if (!eidx && xbf == nullptr && (g_gemv_stream == 2 || g_gemv_stream == 3 || N * K / 2 >= (16ll << 20)) && K <= SG_X_BYTES && K % 32 == 0 && (a.bc_row_bytes % 4) == 0 && (reinterpret_cast<uintptr_t>(bcodes) & 15) == 0 &&
-        g_gemv_stream) {
-        int tr = 64;
-        while (tr > 4 && ((int64_t)tr * (K / 2) > SG_STAGE_BYTES || (N + tr - 1) / tr < 96)) tr >>= 1;
-        if ((int64_t)tr * (K / 2) <= SG_STAGE_BYTES && (int64_t)tr * a.bc_row_bytes <= SG_BC_BYTES && (K / (SG_NW / (tr / 4))) % 32 == 0) {
-            StreamArgs sa;
-            sa.g = a;
-            sa.tr = tr;
-            sa.n_tiles = (int)((N + tr - 1) / tr);
-            sa.status = nullptr;
-            sa.mode = g_gemv_stream == 2 ? 1 : 0;
-            static int n_sm = 0;
-            if (!n_sm) {
-                int dev = 0;
-                cudaGetDevice(&dev);
-                cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
-            }
-            const int grid = sa.n_tiles < n_sm ? sa.n_tiles : n_sm;
-            const size_t smem = SG_STAGES * (SG_STAGE_BYTES + SG_BC_BYTES) + SG_X_BYTES + 1280 + 8 * 2 * SG_STAGES + 16 + 128;
-            const bool b32s = a.f.block % 32 == 0;
-            static bool configured = false;
-            if (!configured) {
-                SCMX_CUDA_OK(cudaFuncSetAttribute(gemv_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                SCMX_CUDA_OK(cudaFuncSetAttribute(gemv_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                configured = true;
-            }
-            const int keep = g_use_pdl;
-            g_use_pdl = pdl ? keep : 0;
-            cudaError_t e = b32s ? launch_pdl(gemv_stream_kernel<true>, dim3(grid), dim3(SG_THREADS), smem, (cudaStream_t)stream, sa)
-                                 : launch_pdl(gemv_stream_kernel<false>, dim3(grid), dim3(SG_THREADS), smem, (cudaStream_t)stream, sa);
-            g_use_pdl = keep;
-            if (e != cudaSuccess) {
-                set_error("gemv_stream launch failed: %s", cudaGetErrorString(e));
-                return SCMX_ECUDA;
-            }
-            return SCMX_OK;
-        }
+    // ---- streaming kernel (bulk-copy ring, persistent CTAs) for dense GEMVs that satisfy its alignment rules; matrices
+    // under 16 MB finish within a few microseconds either way and start faster with the register kernel below
+    if (!eidx && xbf == nullptr && g_gemv_stream && (g_gemv_stream == 2 || N * K / 2 >= (16ll << 20)) && K <= 8192 &&
+        (a.bc_row_bytes % 4) == 0 && (a.f.block == 8 || a.f.block == 16 || a.f.block % 32 == 0) && a.f.block_shift >= 0 &&
+        ((reinterpret_cast<uintptr_t>(bcodes) | reinterpret_cast<uintptr_t>(wscale)) & 15) == 0) {
+        rc = gemv_stream_single(xq, xscale, codes, bcodes, wscale, N, K, a.f, epi, res, out, pdl, (cudaStream_t)stream);
+        if (rc != SCMX_ELIMIT) return rc;         // SCMX_ELIMIT: the shape does not fit the streaming kernel
     }
     const int ksteps = (int)((K + 1023) / 1024);
     // A warp streams `steps` K-steps of 1024 codes for its 4 rows; the remaining K-steps are split over `sk` warps of

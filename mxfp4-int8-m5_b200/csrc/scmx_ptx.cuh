@@ -5,7 +5,7 @@
 
 namespace scmx {
 
-constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // 2 s: after this a wait gives up and the kernel winds down
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // default limit, 2 s: after this a wait gives up and the kernel winds down
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -35,7 +35,8 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
     return t;
 }
 // Bounded wait: 0 = barrier phase completed, 1 = the time limit ran out, 2 = another role of this CTA gave up first.
-__device__ __forceinline__ int mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ int mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                         uint64_t limit_ns = WAIT_LIMIT_NS) {
     if (mbar_try_wait(bar, parity)) return 0;
     const uint64_t t0 = globaltimer_ns();
     for (;;) {
@@ -43,7 +44,7 @@ __device__ __forceinline__ int mbar_wait(uint32_t bar, uint32_t parity, volatile
         for (int i = 0; i < 64; ++i)
             if (mbar_try_wait(bar, parity)) return 0;
         if (*abort_flag) return 2;
-        if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) { *abort_flag = 1; return 1; }
+        if (globaltimer_ns() - t0 > limit_ns) { *abort_flag = 1; return 1; }
     }
 }
 

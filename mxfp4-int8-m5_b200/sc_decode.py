@@ -3,6 +3,8 @@ e2e/sc_decode.py `gemv`.  The kernel accumulates exact INT32 totals (DP4A) and a
 decode and prefill produce the same bits.  Prologues pro=1 / pro=2 (activation quantization / RMSNorm + quantization
 of a bf16 input row) run as the separate row kernel followed by the GEMV, or - on request, see FUSE_PROLOGUE - inside the
 GEMV kernel (scmx_gemv_pro; K <= 8192, register kernel only).  Both give the same bits."""
+import ctypes
+
 import torch
 
 from . import _lib
@@ -57,3 +59,38 @@ def gemv(xq, codes, bcodes, xscale, wscale, N, epi, dtype=torch.bfloat16, res=No
                   F.DEFAULT.c_struct(), epi, _lib.ptr(res) if epi == 2 else None, _lib.ptr(eidx), nslot,
                   -1 if shared is None else int(shared), xstride, _lib.ptr(out), int(USE_PDL), _lib.stream())
     return out if eidx is None else out.reshape(S_, no)
+
+
+class GemvList:
+    """A list of independent dense GEMVs run as ONE persistent launch (scmx_gemv_multi): the packed weights of all jobs
+    stream through one shared-memory ring without a pause at matrix boundaries.  jobs: iterable of
+    (xq int8 [K], codes, bcodes, xscale f32 [1], wscale, N, epi, res-or-None); every input must be complete before run()
+    is launched (jobs cannot feed each other).  Outputs are allocated once and reused by every run()."""
+
+    def __init__(self, jobs):
+        jobs = list(jobs)
+        assert 1 <= len(jobs) <= 512
+        self.n = len(jobs)
+        self.keep = jobs                                  # the tensors the records point at
+        self.fmt = F.DEFAULT
+        self.host = (_lib.ScmxGemvJob * self.n)()
+        self.outs = []
+        for rec, (xq, codes, bcodes, xscale, wscale, N, epi, res) in zip(self.host, jobs):
+            _lib.require_cuda(xq, codes, bcodes, xscale, wscale, res)
+            assert xq.dtype == torch.int8 and xq.dim() == 1 and epi in (0, 1, 2, 3)
+            no = N // 2 if epi == 3 else N
+            out = torch.empty(no, dtype=torch.int32 if epi == 0 else torch.bfloat16, device=xq.device)
+            self.outs.append(out)
+            rec.codes, rec.bcodes, rec.wscale, rec.xq = codes.data_ptr(), bcodes.data_ptr(), wscale.data_ptr(), xq.data_ptr()
+            rec.xscale = xscale.data_ptr() if xscale is not None else None
+            rec.res = res.data_ptr() if (epi == 2 and res is not None) else None
+            rec.out, rec.N, rec.K, rec.epi = out.data_ptr(), N, xq.shape[0], epi
+        _lib.call("scmx_gemv_multi_plan", ctypes.byref(self.host), self.n, self.fmt.c_struct())
+        raw = torch.frombuffer(bytearray(bytes(self.host)), dtype=torch.uint8).clone()
+        self.dev = raw.to(jobs[0][0].device)
+        self.tiles = int(self.host[0].plan[8])
+
+    def run(self):
+        _lib.call("scmx_gemv_multi", ctypes.byref(self.host), _lib.ptr(self.dev), self.n, self.fmt.c_struct(),
+                  _lib.ptr(_lib.status_buffer()), int(USE_PDL), _lib.stream())
+        return self.outs

@@ -196,3 +196,33 @@ def test_dense_stack_overlap_equals_serial(scmx):
     torch.cuda.synchronize()
     scmx._lib.check_status()
     assert torch.equal(a, b) and torch.equal(a, c)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_one_process_two_devices(scmx):
+    """One process driving two GPUs: per-device set-up (shared-memory limits, SM counts, tables) is kept per device, so
+    the GEMM with > 48 KB of shared memory, the SwiGLU table and the streaming GEMV work on the second device too."""
+    S, G, F = scmx.sc_kernels, scmx.sc_decode, scmx.sc_format
+    outs = []
+    for dev in (0, 1):
+        with torch.cuda.device(dev):
+            g = torch.Generator(device=f"cuda:{dev}").manual_seed(3)
+            xq = torch.randint(-127, 128, (256, 1024), dtype=torch.int8, device=f"cuda:{dev}", generator=g)
+            wq = torch.randint(-96, 97, (512, 1024), dtype=torch.int8, device=f"cuda:{dev}", generator=g)
+            xs = torch.rand(256, device=f"cuda:{dev}", generator=g) * 1e-2
+            ws = torch.rand(512, device=f"cuda:{dev}", generator=g) * 1e-2
+            acc = S.mm_i8_i32(xq, wq)
+            y3 = S.mm_epi(xq, wq, xs, ws, 3)
+            w = torch.randn((1024, 2048), device=f"cuda:{dev}", generator=g) * 0.02
+            c, b, s, _, _ = F.quantize_device(w, want_qw=False)
+            scmx._lib.call("scmx_set_gemv_stream", 2)
+            try:
+                yv = G.gemv(xq[0].repeat(2), c, b, xs[:1], s, 1024, 1)
+            finally:
+                scmx._lib.call("scmx_set_gemv_stream", 1)
+            torch.cuda.synchronize()
+            scmx._lib.check_status()
+            assert torch.equal(acc, torch._int_mm(xq, wq.t().contiguous()))
+            outs.append((acc.cpu(), y3.cpu(), yv.cpu()))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)

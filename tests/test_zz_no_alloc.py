@@ -53,6 +53,24 @@ def test_static_scratch_matches_caller_scratch_twice(scmx):
             assert torch.equal(out, ref), f"call {seed}, epi {epi}: static-scratch result differs"
 
 
+def test_static_scratch_several_passes_and_swiglu(scmx):
+    """N * K = 4 MiB and five experts: two experts fit one 8 MiB half, so the call runs three passes and uses both halves
+    (the first one twice); then one call with the SwiGLU epilogue.  Bit for bit against scmx_moe_mm."""
+    M_ = scmx.sc_moe
+    E, N, K, R = 5, 2048, 2048, 900
+    codes, bcodes, ws, off, ts, xq, xs = _case(scmx, 7, E, N, K, R)
+    ex = torch.sort(torch.randint(0, E, (R,), device="cuda")).values.to(torch.int32)      # every expert, incl. the last pass's
+    off, ts, _ = M_.segments(ex, E, 128)
+    for epi in (1, 0, 3):
+        ref = M_.moe_mm(xq, R, codes, bcodes, ws, off, ts, 0, N, epi, xs)
+        out = torch.full_like(ref, -3)
+        rc = _static(scmx, xq, R, codes, bcodes, ws, off, ts, N, epi, xs, out)
+        assert rc == 0, scmx._lib.lib().scmx_last_error_string().decode()
+        torch.cuda.synchronize()
+        scmx._lib.check_status()
+        assert torch.equal(out, ref), f"epi {epi}: static-scratch result differs over three passes"
+
+
 def test_static_scratch_rejects_oversize(scmx):
     L = scmx._lib
     p = ctypes.c_void_p(256)
