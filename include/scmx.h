@@ -139,6 +139,10 @@ int scmx_mm_i8(const int8_t* xq, const int8_t* wq, int64_t M, int64_t N, int64_t
 /* Process-wide tuning hint for the N tile of the GEMM kernels: 0 = automatic, 128 or 256.  Counterpart of the
  * module-level tile constants TM, TN, NSG, GROUP_M (e2e/sc_kernels.py:25) and the `tile=` arguments. */
 int scmx_set_gemm_tile(int bn);
+/* Process-wide switch (default on): dense GEMMs with M > 128 and N >= 256 run on pairs of CTAs that share a 256 x 256 tile
+ * (tcgen05 cta_group::2); off = every CTA computes 128 x 256 tiles of its own.  Same results.  scmx_set_gemm_tile with a
+ * non-zero value also selects the single-CTA kernel.  No counterpart in the reference. */
+int scmx_set_gemm_pair(int enable);
 
 /* Process-wide switches with no counterpart in the reference: programmatic dependent launch for the kernels of the chains
  * (default on) and the streaming (bulk-copy, persistent) form of the dense GEMV: mode 0 = never, 1 = for matrices of

@@ -58,6 +58,7 @@ SIGNATURES = {
     "scmx_attn_decode": [c_vp, c_vp, c_vp, c_i64, c_vp, c_i64, c_float, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp],
     "scmx_mm_i8": [c_vp, c_vp, c_i64, c_i64, c_i64, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp],
     "scmx_set_gemm_tile": [c_int],
+    "scmx_set_gemm_pair": [c_int],
     "scmx_set_pdl": [c_int],
     "scmx_set_wait_limit_ns": [ctypes.c_uint64],
     "scmx_set_status_word": [c_vp],

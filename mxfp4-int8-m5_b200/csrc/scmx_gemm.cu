@@ -179,17 +179,68 @@ __device__ __forceinline__ float bf16_lo(uint32_t p) { return __uint_as_float(p 
 __device__ __forceinline__ float bf16_hi(uint32_t p) { return __uint_as_float(p & 0xFFFF0000u); }
 __device__ __forceinline__ float scale2(uint32_t acc, float xs, float w) { return __fmul_rn(__fmul_rn((float)(int)acc, xs), w); }
 
-// r: 32 INT32 accumulators of columns n .. n+31 of row `row`; ws: the 32 staged weight scales.
-// EPI 1: T((float(acc)*xs)*ws); EPI 2: T(res + T(...)); EPI 3: per 4 columns [g0,g1,u0,u1] -> T(silu(T(g)) * T(u)) x 2, where
-// silu(g) = T(g * sigmoid_T(g)) is read from a 65536-entry table indexed by the bf16 bits of g (built once per device by
-// evaluating the step-by-step bf16 formula for every gate value, so the table holds exactly the bits the formula gives).
-__device__ __forceinline__ void epilogue_chunk(const GemmArgs& a, const uint32_t (&r)[32], const float* ws, float xs, int row,
-                                               int n, bool row_ok) {
-    if (!row_ok || n >= a.N) return;
-    if (a.epi == 0) {
-        uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<int32_t*>(a.out) + (size_t)row * a.N + n);
+// ---- epilogue of one warp: 32 rows x BN/2 accumulator columns ----------------------------------------------------------------
+// tcgen05.ld hands every thread ONE row (32 consecutive columns per load), so storing straight from registers would write 32
+// different rows per instruction, 16 bytes each.  Instead the converted values go through a small shared-memory staging area
+// (per warp 32 rows x 128 bytes, pitch 144 so that both the row-per-thread writes and the row-wise reads are free of bank
+// conflicts) and leave as full 128-byte lines: 4 rows per store instruction.  The residual of EPI 2 comes in the same way
+// (coalesced loads issued before the accumulators are awaited, staged, read back row-per-thread).
+//   EPI 0: INT32; EPI 1: T((float(acc)*xs)*ws); EPI 2: T(res + T(...)); EPI 3: per 4 columns [g0,g1,u0,u1] ->
+//   T(silu(T(g)) * T(u)) x 2 with silu(g) = T(g * sigmoid_T(g)) read from a 65536-entry table indexed by the bf16 bits of g
+//   (built once per device by evaluating the step-by-step bf16 formula for every gate value).
+constexpr int EPI_PITCH = 144;
+constexpr int EPI_STAGE_WARP = 32 * EPI_PITCH;          // 4608 bytes per epilogue warp
+constexpr int EPI_STAGE_BYTES = EPI_WARPS * EPI_STAGE_WARP;
+
+// Start of output row `row` (row_bytes per row): the local output, or with a return map the buffer of the GPU the row's token
+// came from; null when the map is inconsistent (nothing is stored then).
+__device__ __forceinline__ uint8_t* out_row_ptr(const GemmArgs& a, int row, size_t row_bytes) {
+    if (a.ret_rank != nullptr) {
+        const int rr = a.ret_rank[row], r2 = a.ret_row[row];
+        if (rr < 0 || rr >= 8 || r2 < 0) return nullptr;
+        uint16_t* base = a.peer_out[rr];
+        return base == nullptr ? nullptr : reinterpret_cast<uint8_t*>(base) + (size_t)r2 * row_bytes;
+    }
+    return reinterpret_cast<uint8_t*>(a.out) + (size_t)row * row_bytes;
+}
+
+// Staged 32 x 128 bytes -> global memory; `valid` = bytes of the unit that lie inside the matrix (a multiple of 16).
+__device__ __forceinline__ void epi_drain(const GemmArgs& a, const uint8_t* stg, int lane, int row0, int row_end, size_t row_bytes,
+                                          size_t col_byte0, int valid) {
+    const int piece = lane & 7, rsub = lane >> 3;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+    for (int i = 0; i < 8; ++i) {
+        const int rl = 4 * i + rsub;
+        const uint4 v = *reinterpret_cast<const uint4*>(stg + rl * EPI_PITCH + piece * 16);
+        const int row = row0 + rl;
+        if (row < row_end && piece * 16 < valid) {
+            uint8_t* p = out_row_ptr(a, row, row_bytes);
+            if (p != nullptr) *reinterpret_cast<uint4*>(p + col_byte0 + piece * 16) = v;
+        }
+    }
+}
+
+// Coalesced load of the residual of one 64-column unit (32 rows x 128 bytes) into registers, in the staging layout.
+__device__ __forceinline__ void epi_load_res(const GemmArgs& a, uint4 (&rp)[8], int lane, int row0, int row_end, int n_unit) {
+    const int piece = lane & 7, rsub = lane >> 3;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int row = row0 + 4 * i + rsub, col = n_unit + piece * 8;
+        rp[i] = make_uint4(0, 0, 0, 0);
+        if (row < row_end && col < a.N) rp[i] = __ldg(reinterpret_cast<const uint4*>(a.res + (size_t)row * a.N + col));
+    }
+}
+__device__ __forceinline__ void epi_stage_res(uint8_t* stg, const uint4 (&rp)[8], int lane) {
+    const int piece = lane & 7, rsub = lane >> 3;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) *reinterpret_cast<uint4*>(stg + (4 * i + rsub) * EPI_PITCH + piece * 16) = rp[i];
+}
+
+// One 32-column chunk of the thread's row -> staged output bytes.  ws: the chunk's 32 staged weight scales.
+__device__ __forceinline__ void epi_convert(const GemmArgs& a, const uint32_t (&r)[32], const float* ws, float xs, uint8_t* my, int c) {
+    if (a.epi == 0) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) reinterpret_cast<uint4*>(my)[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
     } else if (a.epi == 3) {
         uint32_t pk[8];
 #pragma unroll
@@ -201,17 +252,17 @@ __device__ __forceinline__ void epilogue_chunk(const GemmArgs& a, const uint32_t
             const float s1 = __uint_as_float((uint32_t)__ldg(a.silu_lut + (gg >> 16)) << 16);
             pk[g] = pack_bf16x2(__fmul_rn(s0, bf16_lo(uu)), __fmul_rn(s1, bf16_hi(uu)));
         }
-        uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(a.out) + (size_t)row * (a.N / 2) + n / 2);
+        uint4* o = reinterpret_cast<uint4*>(my + 32 * c);                 // 16 outputs = 32 bytes per chunk
         o[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
         o[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
     } else {
+        uint4* o = reinterpret_cast<uint4*>(my + 64 * (c & 1));           // 32 outputs = 64 bytes per chunk, two chunks per unit
         uint32_t pk[16];
         if (a.epi == 2) {
-            const uint4* rp = reinterpret_cast<const uint4*>(a.res + (size_t)row * a.N + n);
             uint32_t rr[16];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const uint4 v = rp[j];
+                const uint4 v = o[j];                                      // the staged residual of this row
                 rr[4 * j] = v.x; rr[4 * j + 1] = v.y; rr[4 * j + 2] = v.z; rr[4 * j + 3] = v.w;
             }
 #pragma unroll
@@ -227,15 +278,58 @@ __device__ __forceinline__ void epilogue_chunk(const GemmArgs& a, const uint32_t
                 pk[j] = pack_bf16x2(scale2(r[2 * j], xs, w2.x), scale2(r[2 * j + 1], xs, w2.y));
             }
         }
-        uint16_t* orow = reinterpret_cast<uint16_t*>(a.out) + (size_t)row * a.N;
-        if (a.ret_rank != nullptr) {                          // the row's home: a peer GPU's (or this GPU's) return buffer
-            const int rr = a.ret_rank[row], r2 = a.ret_row[row];
-            if (rr < 0 || rr >= 8 || r2 < 0 || a.peer_out[rr] == nullptr) return;     // inconsistent tables: store nothing
-            orow = a.peer_out[rr] + (size_t)r2 * a.N;
-        }
-        uint4* o = reinterpret_cast<uint4*>(orow + n);
 #pragma unroll
         for (int j = 0; j < 4; ++j) o[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
+    }
+}
+
+// The warp's part of a tile.  taddr: TMEM address of its lane quarter and column half; ws: staged scales of that half;
+// row0 / row_end: its 32 rows and the first row not to store; n0: first accumulator column of its half; rp: the residual of
+// the first 64-column unit, loaded by the caller (epi_load_res) before it waited for the accumulators.
+template <int BN>
+__device__ __forceinline__ void epilogue_warp(const GemmArgs& a, uint32_t taddr, const float* ws, int row0, int row_end, int n0,
+                                              uint8_t* stg, int lane, float xs, uint4 (&rp)[8]) {
+    constexpr int CHUNKS = BN / 64;           // 32-column chunks per warp
+    uint8_t* my = stg + lane * EPI_PITCH;
+    uint32_t r0[32], r1[32];
+    tmem_ld32(taddr, r0);
+    if (a.epi == 2) {
+        epi_stage_res(stg, rp, lane);
+        __syncwarp();
+        if (CHUNKS > 2) epi_load_res(a, rp, lane, row0, row_end, n0 + 64);
+    }
+    tmem_ld_wait();
+#pragma unroll
+    for (int c = 0; c < CHUNKS; c += 2) {
+        tmem_ld32(taddr + (c + 1) * 32, r1);
+        epi_convert(a, r0, ws + c * 32, xs, my, c);
+        if (a.epi == 0) {
+            __syncwarp();
+            epi_drain(a, stg, lane, row0, row_end, (size_t)a.N * 4, (size_t)(n0 + c * 32) * 4, min(128, (a.N - (n0 + c * 32)) * 4));
+            __syncwarp();
+        }
+        tmem_ld_wait();
+        if (c + 2 < CHUNKS) tmem_ld32(taddr + (c + 2) * 32, r0);
+        epi_convert(a, r1, ws + (c + 1) * 32, xs, my, c + 1);
+        if (a.epi == 0) {
+            __syncwarp();
+            epi_drain(a, stg, lane, row0, row_end, (size_t)a.N * 4, (size_t)(n0 + (c + 1) * 32) * 4, min(128, (a.N - (n0 + (c + 1) * 32)) * 4));
+            __syncwarp();
+        } else if (a.epi != 3) {
+            __syncwarp();
+            epi_drain(a, stg, lane, row0, row_end, (size_t)a.N * 2, (size_t)(n0 + c * 32) * 2, min(128, (a.N - (n0 + c * 32)) * 2));
+            __syncwarp();
+            if (a.epi == 2 && c + 2 < CHUNKS) {
+                epi_stage_res(stg, rp, lane);
+                __syncwarp();
+            }
+        }
+        if (c + 2 < CHUNKS) tmem_ld_wait();
+    }
+    if (a.epi == 3) {
+        __syncwarp();
+        epi_drain(a, stg, lane, row0, row_end, (size_t)a.N, (size_t)n0, min(32 * CHUNKS, a.N - n0));
+        __syncwarp();
     }
 }
 
@@ -248,7 +342,8 @@ struct Smem {
     static constexpr int BAR_OFF = STAGES * STAGE_BYTES;                 // full[STAGES], empty[STAGES], tfull[2], tempty[2]
     static constexpr int MISC_OFF = BAR_OFF + 8 * (2 * STAGES + 4);      // tmem base (u32), abort flag (int)
     static constexpr int WS_OFF = MISC_OFF + 16;                         // wscale staging [2][BN] float
-    static constexpr int TOTAL = WS_OFF + 2 * BN * 4 + 1024;             // + slack for 1024-byte alignment
+    static constexpr int EPI_OFF = WS_OFF + 2 * BN * 4;                  // epilogue staging, 16-byte aligned
+    static constexpr int TOTAL = EPI_OFF + EPI_STAGE_BYTES + 1024;       // + slack for 1024-byte alignment
 };
 
 template <int BN, int STAGES>
@@ -349,7 +444,6 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_i8_kernel(const __grid_co
         const int q = warp & 3;
         const int chalf = (warp - 2) >> 2;
         const int et = threadIdx.x - 64;          // 0..255 among the epilogue threads
-        constexpr int CHUNKS = BN / 64;           // 32-column chunks per warp
         uint32_t acc = 0, acc_phase = 0;
         for (int t = blockIdx.x; t < total && fail == 0; t += gridDim.x) {
             const Tile tl = get_tile<BN>(a, t, tiles_m, slot0);
@@ -357,28 +451,18 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_i8_kernel(const __grid_co
             if (a.epi != 0) {
                 for (int i = et; i < BN; i += EPI_THREADS) ws[i] = (tl.n0 + i < a.N) ? a.wscale[tl.wrow + i] : 0.0f;
             }
+            // what does not depend on the accumulators is fetched before they are awaited: the row's activation scale, the residual
+            const int wrow0 = tl.row0 + 32 * q;
+            const float xs = (a.epi != 0 && wrow0 + lane < tl.row_end) ? a.xscale[wrow0 + lane] : 0.0f;
+            uint4 rp[8];
+            if (a.epi == 2) epi_load_res(a, rp, lane, wrow0, tl.row_end, tl.n0 + chalf * (BN / 2));
             if (int w = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, a.wait_ns)) fail = w == 1 ? 4 : -1;
             // the epilogue threads agree on giving up (and see the staged scales) before anyone touches TMEM
             epilogue_bar();
             if (*abort_flag) { if (!fail) fail = -1; break; }
             tc_fence_after();
-            const int row = tl.row0 + 32 * q + lane;
-            const bool row_ok = row < tl.row_end;
-            const float xs = (a.epi != 0 && row_ok) ? a.xscale[row] : 0.0f;
-            const uint32_t taddr = tmem_base + acc * BN + chalf * (BN / 2) + ((uint32_t)(32 * q) << 16);
-            uint32_t r0[32], r1[32];
-            tmem_ld32(taddr, r0);
-            tmem_ld_wait();
-#pragma unroll
-            for (int c = 0; c < CHUNKS; c += 2) {
-                // the next chunk's TMEM load is in flight while this chunk is converted and stored
-                tmem_ld32(taddr + (c + 1) * 32, r1);
-                epilogue_chunk(a, r0, ws + chalf * (BN / 2) + c * 32, xs, row, tl.n0 + chalf * (BN / 2) + c * 32, row_ok);
-                tmem_ld_wait();
-                if (c + 2 < CHUNKS) tmem_ld32(taddr + (c + 2) * 32, r0);
-                epilogue_chunk(a, r1, ws + chalf * (BN / 2) + (c + 1) * 32, xs, row, tl.n0 + chalf * (BN / 2) + (c + 1) * 32, row_ok);
-                if (c + 2 < CHUNKS) tmem_ld_wait();
-            }
+            epilogue_warp<BN>(a, tmem_base + acc * BN + chalf * (BN / 2) + ((uint32_t)(32 * q) << 16), ws + chalf * (BN / 2), wrow0,
+                              tl.row_end, tl.n0 + chalf * (BN / 2), smem + L::EPI_OFF + (warp - 2) * EPI_STAGE_WARP, lane, xs, rp);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
@@ -405,6 +489,228 @@ __global__ void __launch_bounds__(CTA_THREADS, 1) gemm_i8_kernel(const __grid_co
         __syncthreads();
     }
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+
+// ---- the same GEMM on CTA pairs (cta_group::2) ---------------------------------------------------------------------------
+// Two CTAs on neighbouring SMs (a cluster of 2) share one 256 x 256 output tile.  Each CTA loads ITS 128 rows of A and ITS
+// 128 of the tile's 256 weight rows (32 KB per K block instead of 48 KB for a 128 x 256 tile of its own), the leader CTA's MMA
+// thread issues tcgen05.mma.cta_group::2 M256 x N256 x K32, which reads both CTAs' shared memory and writes 128 accumulator
+// rows into each CTA's tensor memory, and each CTA runs the epilogue of its own 128 rows.  Operand bytes per MMA cycle drop by
+// a third, which is what bounds the single-CTA kernel (its TMA stages arrive slower than the tensor core consumes them).
+//   full[s]   lives in the leader: armed by the leader's producer for both CTAs' bytes; the peer's TMA loads complete on it
+//             through the .cta_group::2 form of the copy (no multicast: every CTA fetches its own tiles)
+//   empty[s], tmem_full[acc]   one copy per CTA, signalled in both CTAs by the leader's tcgen05.commit (multicast arrive)
+//   tmem_empty[acc]            lives in the leader: 8 epilogue warps of each CTA arrive (the peer's remotely)
+// Both CTAs meet at a cluster barrier after set-up and before tear-down, so neither touches the other's shared memory or
+// tensor memory outside that window.  Waits are bounded as in the single-CTA kernel.
+constexpr int PAIR_STAGES = 5;
+constexpr int PAIR_BN = 256;
+struct PairSmem {
+    static constexpr int A_BYTES = BM * BK;                 // this CTA's 128 rows of the 256-row A tile
+    static constexpr int B_BYTES = (PAIR_BN / 2) * BK;      // this CTA's 128 of the tile's 256 weight rows
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int BAR_OFF = PAIR_STAGES * STAGE_BYTES;
+    static constexpr int MISC_OFF = BAR_OFF + 8 * (2 * PAIR_STAGES + 4);
+    static constexpr int WS_OFF = MISC_OFF + 16;
+    static constexpr int EPI_OFF = WS_OFF + 2 * PAIR_BN * 4;
+    static constexpr int TOTAL = EPI_OFF + EPI_STAGE_BYTES + 1024;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA tile load of a CTA pair: the data lands in this CTA's shared memory, the bytes are counted on an mbarrier that may
+// live in the other CTA of the pair (`bar` is a shared::cluster address).  No multicast.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrive on the mbarrier at this shared-memory offset in BOTH CTAs of the pair once the MMAs issued so far have completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(mask) : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(CTA_THREADS, 1)
+    gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmArgs a) {
+    using L = PairSmem;
+    constexpr int STAGES = PAIR_STAGES, BN = PAIR_BN;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bar_full = sbase + L::BAR_OFF, bar_empty = bar_full + 8 * STAGES;
+    const uint32_t bar_tfull = bar_empty + 8 * STAGES, bar_tempty = bar_tfull + 16;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + L::MISC_OFF);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::MISC_OFF + 4);
+    float* ws_stage = reinterpret_cast<float*>(smem + L::WS_OFF);
+    constexpr uint32_t TMEM_COLS = 2 * BN;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar_tfull + 8 * i, 1);
+            mbar_init(bar_tempty + 8 * i, 2 * EPI_WARPS);      // the epilogue warps of both CTAs
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc2(smem_u32(tmem_slot), TMEM_COLS);
+        tmem_relinquish2();
+    }
+    pdl_launch_dependents();
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();             // the peer's barriers exist before anything is sent to them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();
+
+    const uint32_t full_leader = mapa_u32(bar_full, 0), tempty_leader = mapa_u32(bar_tempty, 0);
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    const int tiles_m = (a.M + 2 * BM - 1) / (2 * BM), tiles_n = (a.N + BN - 1) / BN;
+    const int total = tiles_m * tiles_n;
+    const int num_kb = (a.K + BK - 1) / BK;
+    int fail = 0;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int t = pair; t < total && fail == 0; t += npairs) {
+                const int nt = t / tiles_m, mt = t - nt * tiles_m;
+                const int row0 = mt * 2 * BM + (int)rank * BM, brow = nt * BN + (int)rank * (BN / 2);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (int w = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, a.wait_ns)) { fail = w == 1 ? 1 : -1; break; }
+                    const uint32_t sa = sbase + stage * L::STAGE_BYTES, sb = sa + L::A_BYTES;
+                    if (leader) mbar_expect_tx(bar_full + 8 * stage, 2 * L::STAGE_BYTES);
+                    tma_load_2d_pair(sa, &tmA, kb * BK, row0, full_leader + 8 * stage);
+                    tma_load_2d_pair(sb, &tmB, kb * BK, brow, full_leader + 8 * stage);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = umma_idesc(2 * BM, BN);
+            int stage = 0;
+            uint32_t phase = 0, acc = 0, acc_phase = 0;
+            for (int t = pair; t < total && fail == 0; t += npairs) {
+                if (int w = mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, a.wait_ns)) { fail = w == 1 ? 2 : -1; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (int w = mbar_wait(bar_full + 8 * stage, phase, abort_flag, a.wait_ns)) { fail = w == 1 ? 3 : -1; break; }
+                    tc_fence_after();
+                    const uint32_t sa = sbase + stage * L::STAGE_BYTES, sb = sa + L::A_BYTES;
+                    const uint64_t da = umma_desc(sa), db = umma_desc(sb);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_i8_pair(d_tmem, da + (uint64_t)(k * (UMMA_K >> 4)), db + (uint64_t)(k * (UMMA_K >> 4)), idesc,
+                                     (kb | k) != 0 ? 1u : 0u);
+                    umma_commit_pair(bar_empty + 8 * stage);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (fail) break;
+                umma_commit_pair(bar_tfull + 8 * acc);
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1;
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        const int chalf = (warp - 2) >> 2;
+        const int et = threadIdx.x - 64;
+        uint32_t acc = 0, acc_phase = 0;
+        for (int t = pair; t < total && fail == 0; t += npairs) {
+            const int nt = t / tiles_m, mt = t - nt * tiles_m;
+            const int n0 = nt * BN, row0 = mt * 2 * BM + (int)rank * BM;
+            float* ws = ws_stage + acc * BN;
+            if (a.epi != 0) {
+                for (int i = et; i < BN; i += EPI_THREADS) ws[i] = (n0 + i < a.N) ? a.wscale[n0 + i] : 0.0f;
+            }
+            const int wrow0 = row0 + 32 * q;
+            const float xs = (a.epi != 0 && wrow0 + lane < a.M) ? a.xscale[wrow0 + lane] : 0.0f;
+            uint4 rp[8];
+            if (a.epi == 2) epi_load_res(a, rp, lane, wrow0, a.M, n0 + chalf * (BN / 2));
+            if (int w = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, a.wait_ns)) fail = w == 1 ? 4 : -1;
+            epilogue_bar();
+            if (*abort_flag) { if (!fail) fail = -1; break; }
+            tc_fence_after();
+            epilogue_warp<BN>(a, tmem_base + acc * BN + chalf * (BN / 2) + ((uint32_t)(32 * q) << 16), ws + chalf * (BN / 2), wrow0, a.M,
+                              n0 + chalf * (BN / 2), smem + L::EPI_OFF + (warp - 2) * EPI_STAGE_WARP, lane, xs, rp);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if (leader) mbar_arrive(bar_tempty + 8 * acc);
+                else mbar_arrive_cluster(tempty_leader + 8 * acc);
+            }
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1;
+        }
+    }
+
+    if (fail > 0) {
+        if (atomicCAS(a.status, 0, fail) == 0) {
+            a.status[1] = blockIdx.x;
+            a.status[2] = threadIdx.x;
+        }
+    }
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);   // 0.2 ms for outstanding TMA writes
+        __syncthreads();
+    }
+    cluster_sync_all();             // both CTAs are done with each other's shared and tensor memory
+    tc_fence_after();
+    if (warp == 1) tmem_dealloc2(tmem_base, TMEM_COLS);
 }
 
 
@@ -475,6 +781,7 @@ static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, 
 }
 
 static int g_bn_override = 0;      // 0 = choose per problem
+static int g_use_pair = 1;         // dense GEMMs of at least 256 x 256 run on CTA pairs
 static int num_sms() { return sm_count(); }
 
 template <int BN, int STAGES>
@@ -502,6 +809,22 @@ static int run_gemm(const int8_t* xq, int64_t a_rows, const int8_t* wq, int64_t 
     CUtensorMap tmA, tmB;
     int rc = make_map(&tmA, xq, a_rows, a.K, BM);
     if (rc) return rc;
+    if (a.E == 0 && g_use_pair && !g_bn_override && a.M > BM && a.N >= PAIR_BN && a.ret_rank == nullptr) {
+        rc = make_map(&tmB, wq, b_rows, a.K, PAIR_BN / 2);
+        if (rc) return rc;
+        const int64_t tiles = ((a.M + 2 * BM - 1) / (2 * BM)) * (int64_t)((a.N + PAIR_BN - 1) / PAIR_BN);
+        int pairs = num_sms() / 2;
+        if (tiles < pairs) pairs = (int)tiles;
+        static bool configured[64] = {};
+        const int dev = current_device();
+        SCMX_REQUIRE(dev >= 0, SCMX_ECUDA, "no current CUDA device (ordinal 0..63)");
+        if (!configured[dev]) {
+            SCMX_CUDA_OK(cudaFuncSetAttribute(gemm_i8_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::TOTAL));
+            configured[dev] = true;
+        }
+        SCMX_PDL_OK("gemm_i8_pair_kernel", launch_pdl(gemm_i8_pair_kernel, dim3(2 * pairs), dim3(CTA_THREADS), (size_t)PairSmem::TOTAL, st, tmA, tmB, a));
+        return SCMX_OK;
+    }
     rc = make_map(&tmB, wq, b_rows, a.K, bn);
     if (rc) return rc;
     int grid = num_sms();
@@ -509,8 +832,8 @@ static int run_gemm(const int8_t* xq, int64_t a_rows, const int8_t* wq, int64_t 
         const int64_t tiles = ((a.M + BM - 1) / BM) * (int64_t)((a.N + bn - 1) / bn);
         if (tiles < grid) grid = (int)tiles;
     }
-    if (bn == 256) return launch_gemm<256, 4>(tmA, tmB, a, grid, st);
-    return launch_gemm<128, 6>(tmA, tmB, a, grid, st);
+    if (bn == 256) return launch_gemm<256, 3>(tmA, tmB, a, grid, st);
+    return launch_gemm<128, 5>(tmA, tmB, a, grid, st);
 }
 
 // A per-device side stream and the events that order it against the caller's stream (created on first use; event waits and
@@ -552,6 +875,11 @@ static int check_common(const char* who, int64_t N, int64_t K, int epi, const fl
 }  // namespace scmx
 
 using namespace scmx;
+
+extern "C" int scmx_set_gemm_pair(int enable) {
+    g_use_pair = enable ? 1 : 0;
+    return SCMX_OK;
+}
 
 extern "C" int scmx_set_gemm_tile(int bn) {
     SCMX_REQUIRE(bn == 0 || bn == 128 || bn == 256, SCMX_EINVAL, "set_gemm_tile: bn=%d (0 = automatic, 128 or 256)", bn);

@@ -392,3 +392,32 @@ def test_gemv_fused_prologue_equals_row_kernel_then_gemv(scmx, oracle, K):
     for fuse in (True, False):
         outs.append(G.gemv(xr, cE, bE, None, sE, Ne, 1, eidx=e, xstride=1, pro=1, fuse=fuse))
     assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("M,N,K,epi", [(2048, 4096, 2048, 1), (2048, 2048, 6144, 2), (1024, 1344, 1024, 3), (256, 256, 128, 0),
+                                       (640, 288, 4096, 1)])
+def test_pair_kernel_equals_single_cta_kernel(scmx, M, N, K, epi):
+    """Dense GEMMs run on CTA pairs (cta_group::2, 256 x 256 tiles) by default; the single-CTA kernel (128 x 256 tiles) must
+    give the same bits for every epilogue, with ragged M and N tails."""
+    S = scmx.sc_kernels
+    g = torch.Generator(device="cuda").manual_seed(M + N)
+    xq = torch.randint(-127, 128, (M, K), dtype=torch.int8, device="cuda", generator=g)
+    wq = torch.randint(-96, 97, (N, K), dtype=torch.int8, device="cuda", generator=g)
+    xs = torch.rand(M, device="cuda", generator=g) * 1e-3
+    ws = torch.rand(N, device="cuda", generator=g) * 1e-3
+    res = torch.randn((M, N), device="cuda", generator=g).to(torch.bfloat16)
+
+    def run():
+        if epi == 0:
+            return S.mm_i8_i32(xq, wq)
+        return S.mm_epi(xq, wq, xs, ws, epi, res=res if epi == 2 else None)
+    a = run()
+    scmx._lib.call("scmx_set_gemm_pair", 0)
+    try:
+        b = run()
+    finally:
+        scmx._lib.call("scmx_set_gemm_pair", 1)
+    _status_ok(scmx)
+    assert torch.equal(a, b)
+    if epi == 0:
+        assert torch.equal(a, torch._int_mm(xq, wq.t()) if M > 32 and M % 8 == 0 else a)
