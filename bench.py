@@ -837,6 +837,13 @@ def run_case(args):
         ws = torch.full((12288,), 2.0 ** -9, device="cuda")
         for _ in range(4):
             S.mm_epi(xq, wq, xs, ws, 3)
+    elif args.case == "gemmw4":   # the same GEMM straight from packed weights (tiles expanded inside the K loop)
+        xq = torch.randint(-127, 128, (2048, 2048), dtype=torch.int8, device="cuda", generator=g)
+        w = torch.randn((12288, 2048), generator=g, device="cuda") * 0.02
+        c, b, ws, _, _ = F.quantize_device(w, want_qw=False)
+        xs = torch.full((2048,), 1e-2, device="cuda")
+        for _ in range(4):
+            S.mm_w4_epi(xq, c, b, xs, ws, 12288, 3)
     elif args.case == "gemv":     # 12 distinct gate|up weight sets (154 MB > L2), one GEMV each, two passes
         sets = []
         for _ in range(12):
@@ -847,6 +854,18 @@ def run_case(args):
         for _ in range(2):
             for c, b, w_ in sets:
                 G.gemv(xq, c, b, xs, w_, 12288, 3)
+    elif args.case == "gemvlist":  # 24 GEMVs (6 layers x qkv, o, gate|up, down; 154 MB of packed weights) as one persistent launch, 3 launches
+        jobs = []
+        xqs = {k: torch.randint(-127, 128, (k,), dtype=torch.int8, device="cuda", generator=g) for k in (2048, 6144)}
+        xs = torch.full((1,), 1e-2, device="cuda")
+        res = torch.zeros(2048, dtype=torch.bfloat16, device="cuda")
+        for _ in range(6):
+            for (n, k), epi in zip(QWEN["groups"].values(), (1, 2, 3, 2)):
+                c, b, w_, _, _ = F.quantize_device(torch.randn((n, k), generator=g, device="cuda") * 0.02, want_qw=False)
+                jobs.append((xqs[k], c, b, xs, w_, n, epi, res if epi == 2 else None))
+        gl = G.GemvList(jobs)
+        for _ in range(3):
+            gl.run()
     elif args.case == "gemvbig":  # one LM-head-shaped GEMV, 151936 x 2048 (160 MB of packed weights), three launches
         w = torch.randn((151936, 2048), generator=g, device="cuda") * 0.02
         c, b, w_, _, _ = F.quantize_device(w, want_qw=False)
@@ -899,7 +918,7 @@ def main():
     ap.add_argument("--no-overlap", action="store_true", help="decode weights on the main stream instead of a side stream")
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic stream serialization")
     ap.add_argument("--dense-only", action="store_true", help="skip the roofline / decode / MoE / CPU sections")
-    ap.add_argument("--case", choices=["gemm", "gemv", "gemvbig", "moe", "models", "decodestep", "decodechain"], help="run one small kernel case (for profiler captures) and exit")
+    ap.add_argument("--case", choices=["gemm", "gemmw4", "gemv", "gemvbig", "gemvlist", "moe", "models", "decodestep", "decodechain"], help="run one small kernel case (for profiler captures) and exit")
     args = ap.parse_args()
     if args.case:
         run_case(args)

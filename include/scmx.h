@@ -195,6 +195,23 @@ int scmx_moe_mm(const int8_t* xq, int64_t R, const uint32_t* codes, const uint8_
                 const float* xscale, void* out, int tm, int experts_per_pass, int8_t* scratch, int64_t scratch_bytes,
                 int32_t* status, void* stream);
 
+/* The GEMMs straight from packed weights, single pass: the 4-bit tiles are expanded to INT8 in shared memory inside the K
+ * loop of the tensor-core kernel (CTA pairs; four unpack warps per CTA), so decoded weights never reach global memory and
+ * no scratch is needed.  scmx_mm_w4 = scmx_mm_i8 on unpack_i8's output, the single-pass W4A8 linear of the reference
+ * (kernels/w4a8.metal:78-155, e2e/w4a8_mlx.py:88-135); scmx_moe_mm_w4 = sc_moe.moe_mm with its in-kernel unpack
+ * (e2e/sc_moe.py:19-92,169-185).  Same results as the two-kernel forms, bit for bit.  Format rule: K % 128 == 0 and the
+ * block codes of 128 weights form one field of 8, 16 or 32 bits (block 32 / 2-bit codes, block 16 / 2- or 4-bit codes, ...;
+ * scmx_w4_supported returns 1 when a format and K qualify).  Grouped form: E <= 512, rows [off[e], off[e+1]) use expert e;
+ * no tile table is needed (the kernel derives its own 256-row tiles from off).  status codes as scmx_mm_i8, plus 6 =
+ * an unpack warp waited for a packed tile. */
+int scmx_w4_supported(const scmx_format* fmt, int64_t K);
+int scmx_mm_w4(const int8_t* xq, const uint32_t* codes, const uint8_t* bcodes, int64_t M, int64_t N, int64_t K,
+               const scmx_format* fmt, int epi, const float* xscale, const float* wscale, const uint16_t* res, void* out,
+               int32_t* status, void* stream);
+int scmx_moe_mm_w4(const int8_t* xq, int64_t R, const uint32_t* codes, const uint8_t* bcodes, const float* wscale,
+                   const int32_t* off, int E, int64_t N, int64_t K, const scmx_format* fmt, int epi, const float* xscale,
+                   void* out, int32_t* status, void* stream);
+
 /* scmx_moe_mm without a scratch argument; it has no counterpart in the reference (whose arrays are allocated by MLX).
  * For hosts that cannot hand the library device memory at call time: a serving process that gave all of HBM to its own
  * pool at start-up (a cudaMalloc there would fail, or stall the device mid-request), or a foreign-language runtime bound

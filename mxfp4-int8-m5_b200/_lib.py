@@ -57,6 +57,9 @@ SIGNATURES = {
                       c_i64, c_vp, c_vp, c_i64, c_i64, c_vp],
     "scmx_attn_decode": [c_vp, c_vp, c_vp, c_i64, c_vp, c_i64, c_float, c_int, c_int, c_int, c_int, c_vp, c_vp, c_vp, c_vp],
     "scmx_mm_i8": [c_vp, c_vp, c_i64, c_i64, c_i64, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp],
+    "scmx_w4_supported": [_FMT_P, c_i64],
+    "scmx_mm_w4": [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, _FMT_P, c_int, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp],
+    "scmx_moe_mm_w4": [c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, _FMT_P, c_int, c_vp, c_vp, c_vp, c_vp],
     "scmx_set_gemm_tile": [c_int],
     "scmx_set_gemm_pair": [c_int],
     "scmx_set_pdl": [c_int],
@@ -162,7 +165,7 @@ def check_status():
         raise ScmxError(f"device-side wait ran out: {describe_status(v[0])} (CTA or rank {v[1]}, thread {v[2]})")
 
 
-_GEMM_ROLES = {1: "GEMM producer waiting for a free stage", 2: "GEMM MMA warp waiting for a free accumulator",
+_GEMM_ROLES = {6: "GEMM unpack warp waiting for a packed weight tile", 1: "GEMM producer waiting for a free stage", 2: "GEMM MMA warp waiting for a free accumulator",
                3: "GEMM MMA warp waiting for operands", 4: "GEMM epilogue waiting for an accumulator",
                5: "GEMM CTA pair waiting for its peer", 11: "streaming GEMV producer waiting for a free stage",
                12: "streaming GEMV consumer waiting for a tile", 20: "peer barrier waiting for another rank's flag"}

@@ -29,6 +29,18 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return ok;
 }
+// The same test with acquire semantics at cluster scope: for barriers on which threads of the other CTA of a pair arrive.
+__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
 __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -43,6 +55,18 @@ __device__ __forceinline__ int mbar_wait(uint32_t bar, uint32_t parity, volatile
 #pragma unroll 1
         for (int i = 0; i < 64; ++i)
             if (mbar_try_wait(bar, parity)) return 0;
+        if (*abort_flag) return 2;
+        if (globaltimer_ns() - t0 > limit_ns) { *abort_flag = 1; return 1; }
+    }
+}
+
+__device__ __forceinline__ int mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint64_t limit_ns) {
+    if (mbar_try_wait_cluster(bar, parity)) return 0;
+    const uint64_t t0 = globaltimer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait_cluster(bar, parity)) return 0;
         if (*abort_flag) return 2;
         if (globaltimer_ns() - t0 > limit_ns) { *abort_flag = 1; return 1; }
     }

@@ -14,7 +14,10 @@ class MoeBlock:
         (moe_mm_i8) instead of decoding per call.  early_decode (default, when the INT8 copies of all experts fit in
         1 GiB): every step decodes all experts to INT8 on a side stream starting at the top of the step, under the
         RMSNorm / router / sort / gather kernels and the first grouped GEMM, and the GEMMs run on that (moe_mm_i8);
-        otherwise moe_mm decodes groups of experts between its GEMM passes."""
+        otherwise moe_mm decodes groups of experts between its GEMM passes.  With fewer than FUSED_BELOW rows per expert on
+        average (the reference's rule, e2e/fused_olmoe.py:205: two passes pay only when R // E >= 256) the grouped GEMM reads
+        the packed weights directly and expands them inside its K loop (sc_moe.moe_mm -> scmx_moe_mm_w4): nothing is decoded
+        to memory for a handful of rows per expert."""
         self.gu, self.dn, self.E, self.k, self.D, self.F, self.eps = gu, dn, n_experts, topk, D, F, eps
         dev = gu[0].device
         self.nw = torch.ones(D, dtype=torch.bfloat16, device=dev)
@@ -27,6 +30,11 @@ class MoeBlock:
             self.gu8 = torch.empty((n_experts * 2 * F, D), dtype=torch.int8, device=dev)
             self.dn8 = torch.empty((n_experts * D, F), dtype=torch.int8, device=dev)
             self.side = torch.cuda.Stream(device=dev)
+
+    FUSED_BELOW = 384      # measured on B200 (64 experts, 2048 x 1024): fused wins up to 256 rows per expert, ties at 512
+
+    def _fused(self, R):
+        return (not self.two_pass) and M_.FUSED_UNPACK and R // self.E < self.FUSED_BELOW
 
     def _start_decode(self):
         """Both expert sets -> INT8 on the side stream; returns the events the two GEMMs wait for."""
@@ -46,15 +54,20 @@ class MoeBlock:
         """Sorted INT8 rows [R + 128, D] -> bf16 expert outputs [R, D]."""
         D, F = self.D, self.F
         main = torch.cuda.current_stream()
-        if self.early and decoded is None:                    # called on its own: decode now (still on the side stream)
+        fused = self._fused(R)
+        if self.early and decoded is None and not fused:      # called on its own: decode now (still on the side stream)
             decoded = self._start_decode()
-        if self.two_pass or self.early:
+        if fused:
+            act = M_.moe_mm(xq_s, R, *self.gu, off, ts, mt, 2 * F, 3, xs_s)
+        elif self.two_pass or self.early:
             if decoded is not None:
                 main.wait_event(decoded[0])
             act = M_.moe_mm_i8(xq_s, R, self.gu8, self.gu[2], off, ts, mt, 2 * F, 3, xs_s)
         else:
             act = M_.moe_mm(xq_s, R, *self.gu, off, ts, mt, 2 * F, 3, xs_s)
         xq2, xs2 = S.act_quant(act, R + M_.TM)
+        if fused:
+            return M_.moe_mm(xq2, R, *self.dn, off, ts, mt, D, 1, xs2)
         if self.two_pass or self.early:
             if decoded is not None:
                 main.wait_event(decoded[1])
@@ -65,13 +78,13 @@ class MoeBlock:
         """h bf16 [L, D] (L a multiple of 128), router logits f32 [L, E] -> new residual stream bf16 [L, D]."""
         L = h.shape[0]
         R = L * self.k
-        decoded = self._start_decode() if self.early else None
+        decoded = self._start_decode() if (self.early and not self._fused(R)) else None
         xq, xs = S.rmsnorm_quant(h, self.nw, self.eps, L)
         inds, scores = M_.router_topk(logits, self.k)
         pos, tok, _, off, ts, mt = M_.route_sort(inds, self.E, M_.TM)
         xq_s, xs_s = M_.gather_rows(xq, xs, tok, R)
         yd = self.experts(xq_s, xs_s, R, off, ts, mt, decoded)
         hout, _, _ = M_.moe_combine(yd, pos, scores, h, self.nw, self.eps, L, quant=False)
-        if self.early:
+        if decoded is not None:
             torch.cuda.current_stream().wait_stream(self.side)
         return hout

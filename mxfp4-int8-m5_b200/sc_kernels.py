@@ -128,6 +128,23 @@ def mm_epi(xq, wq, xscale, wscale, epi, dtype=torch.bfloat16, res=None, deps=(),
     return out
 
 
+def mm_w4_epi(xq, codes, bcodes, xscale, wscale, N, epi, dtype=torch.bfloat16, res=None):
+    """mm_epi(xq, unpack_i8(codes, bcodes, N, K), ...) as ONE kernel: the packed weight tiles are expanded to INT8 in shared
+    memory inside the K loop (the single-pass form of the reference, kernels/w4a8.metal:78-155), so no INT8 copy of the
+    weights is written.  Same bits as the two-kernel form.  epi 0 returns the INT32 accumulators."""
+    _lib.require_cuda(xq, codes, bcodes, xscale, wscale, res)
+    M, K = xq.shape
+    assert dtype == torch.bfloat16 and epi in (0, 1, 2, 3)
+    assert M % TM == 0 and N % 32 == 0 and (epi != 2 or tuple(res.shape) == (M, N))
+    fmt = F.DEFAULT
+    assert _lib.lib().scmx_w4_supported(fmt.c_struct(), K), "format / K not covered by the packed-weight GEMM"
+    out = torch.empty((M, N), dtype=torch.int32, device=xq.device) if epi == 0 else \
+        torch.empty((M, N // 2 if epi == 3 else N), dtype=torch.bfloat16, device=xq.device)
+    _lib.call("scmx_mm_w4", _lib.ptr(xq), _lib.ptr(codes), _lib.ptr(bcodes), M, N, K, fmt.c_struct(), epi, _lib.ptr(xscale),
+              _lib.ptr(wscale), _lib.ptr(res) if epi == 2 else None, _lib.ptr(out), _lib.ptr(_lib.status_buffer()), _lib.stream())
+    return out
+
+
 def interleave_gate_up(Fdim):
     """Row permutation of [gate (F rows); up (F rows)] into groups g_2p, g_2p+1, u_2p, u_2p+1 for EPI 3."""
     p = np.arange(Fdim // 2)

@@ -15,6 +15,10 @@ from . import sc_kernels as S
 TM = 128
 EXPERTS_PER_PASS = 32    # experts decoded to INT8 per pass of moe_mm (two rotating scratch halves); 8 -> 32: -12 % on the half-block
 
+# moe_mm expands the packed expert tiles inside the GEMM kernel (scmx_moe_mm_w4) where the format allows it; False selects the
+# older form that decodes groups of experts to an INT8 scratch between GEMM passes (scmx_moe_mm).
+FUSED_UNPACK = True
+
 _scratch = {}
 
 
@@ -85,6 +89,10 @@ def moe_mm(xq, R, codes, bcodes, wscale, off, tstart, max_tiles, N, epi, xscale=
     E = wscale.shape[0]
     assert N % 32 == 0 and K % 16 == 0 and codes.numel() == E * N * K // 8
     out = _out(R, N, epi, xq.device)
+    if FUSED_UNPACK and E <= 512 and _lib.lib().scmx_w4_supported(F.DEFAULT.c_struct(), K):
+        _lib.call("scmx_moe_mm_w4", _lib.ptr(xq), R, _lib.ptr(codes), _lib.ptr(bcodes), _lib.ptr(wscale), _lib.ptr(off), E, N, K,
+                  F.DEFAULT.c_struct(), epi, _lib.ptr(xscale), _lib.ptr(out), _lib.ptr(_lib.status_buffer()), _lib.stream())
+        return out
     epp = min(EXPERTS_PER_PASS, E)
     need = 2 * epp * N * K
     key = (xq.device.index, need)
