@@ -28,6 +28,8 @@ sys.path.insert(0, ROOT)
 
 QWEN = dict(layers=28, M=2048, groups=dict(qkv=(4096, 2048), o=(2048, 2048), gu=(12288, 2048), down=(2048, 6144)))
 OLMOE = dict(layers=16, tokens=4096, D=2048, F=1024, E=64, topk=8)
+# large-MoE stress: 128 experts, block-16 integer-exact FP4 variant (e2m1 / B16 / power-of-two multipliers), Zipf-skewed routing
+MOE5 = dict(layers=48, tokens=8192, D=2048, F=768, E=128, topk=8, zipf=1.2, decode_steps=128)
 
 
 def qwen_ops(M=QWEN["M"], layers=QWEN["layers"]):
@@ -335,6 +337,141 @@ def build_moe_block(pkg, torch, cfg=OLMOE, shard=(0, 1), seed=0, two_pass=False)
                                   early_decode=world == 1)
 
 
+def zipf_logits(torch, tokens, E, s, seed):
+    """Router logits N(0, 1) + log zipf_pmf(rank(e); s) under a seeded permutation of the experts: expert popularity
+    follows a Zipf law while every token still draws its own noise.  Returns (logits f32 [tokens, E] on the GPU, perm)."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    perm = torch.randperm(E, generator=g, device="cuda")
+    rank = (perm + 1).double()
+    logp = (-s * rank.log() - (torch.arange(1, E + 1, device="cuda").double() ** -s).sum().log()).float()
+    return torch.randn((tokens, E), generator=g, device="cuda") + logp[None, :], perm
+
+
+def build_moe5_block(pkg, torch, fmt, shard=(0, 1), seed=0):
+    """E experts of gate|up [2F, D] (rows interleaved) and down [D, F], N(0, 0.02), packed by the format-family quantizer
+    (row base x per-block multiplier search) on the GPU; every expert its own draw and its own allocation."""
+    F, S = pkg.sc_format, pkg.sc_kernels
+    c = MOE5
+    rank, world = shard
+    D, Fd, E = c["D"], c["F"], c["E"]
+    perm = torch.from_numpy(S.interleave_gate_up(Fd)).cuda()
+    e0, e1 = rank * E // world, (rank + 1) * E // world
+
+    def pack(n, k, tag, p=None):
+        cs, bs, ss = [], [], []
+        for e in range(e0, e1):
+            g = torch.Generator(device="cuda").manual_seed(seed * 100003 + tag * 1009 + e)
+            w = torch.randn((n, k), generator=g, device="cuda") * 0.02
+            if p is not None:
+                w = w[p]
+            cc, b, s_, _ = F.family_quantize_device(w.contiguous(), fmt)
+            cs.append(cc); bs.append(b); ss.append(s_)
+        return torch.stack(cs), torch.stack(bs), torch.stack(ss)
+    return pkg.fused_moe.MoeBlock(pack(2 * Fd, D, 1, perm), pack(D, Fd, 2), e1 - e0, c["topk"], D, Fd, early_decode=world == 1)
+
+
+def bench_moe5(pkg, torch, dist=None, reps=5):
+    """Large-MoE stress (128 experts, F = 768, block-16 format family, Zipf(1.2) expert popularity): one half-block at 8192
+    prefill tokens (expert parallel when a process group is given) and, on one GPU, the batch-1 gather-GEMV decode step."""
+    F, S, M_, G = pkg.sc_format, pkg.sc_kernels, pkg.sc_moe, pkg.sc_decode
+    c = MOE5
+    world = dist.get_world_size() if dist is not None else 1
+    rank = dist.get_rank() if dist is not None else 0
+    fmt = F.Format(block=16)
+    S.set_format(fmt)
+    try:
+        blk = build_moe5_block(pkg, torch, fmt, shard=(rank, world))
+        Lr = c["tokens"] // world
+        layer = blk
+        if world > 1:
+            layer = pkg.parallel.PeerExpertParallelMoe(pkg, blk, c["E"], c["topk"], Lr)
+        g = torch.Generator(device="cuda").manual_seed(1)
+        h_all = torch.randn((c["tokens"], c["D"]), generator=g, device="cuda").to(torch.bfloat16)
+        lg_all, _ = zipf_logits(torch, c["tokens"], c["E"], c["zipf"], seed=2)
+        h, lg = h_all[rank * Lr:(rank + 1) * Lr].contiguous(), lg_all[rank * Lr:(rank + 1) * Lr].contiguous()
+        inds, _ = M_.router_topk(lg_all, c["topk"])
+        cnt = torch.bincount(inds.reshape(-1).long(), minlength=c["E"]).double()
+        per_rank = cnt.view(max(world, 1), -1).sum(1)
+        out = dict(tokens=c["tokens"], experts=c["E"], format="e2m1 / block 16 / multipliers 1,2,4,8 (format-family quantizer)",
+                   rows_per_expert=dict(max=int(cnt.max()), mean=float(cnt.mean()), min=int(cnt.min())),
+                   rows_per_rank=dict(max=int(per_rank.max()), mean=float(per_rank.mean()),
+                                      imbalance=float(per_rank.max() / per_rank.mean())))
+        for _ in range(3):
+            layer.step(h, lg)
+        torch.cuda.synchronize()
+        pkg._lib.check_status()
+        run = lambda: layer.step(h, lg)   # noqa: E731
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                layer.step(h, lg)
+            run = graph.replay
+        except Exception as e:   # noqa: BLE001
+            print(f"# moe5 graph capture unavailable ({type(e).__name__}: {e})", file=sys.stderr)
+            torch.cuda.synchronize()
+        for _ in range(2):
+            run()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        if dist is not None:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        ops = 2 * c["tokens"] * c["topk"] * 3 * c["F"] * c["D"]
+        out.update(ms_per_half_block=ms, tokens_per_s_one_layer=c["tokens"] / ms * 1e3,
+                   tokens_per_s_48_layers=c["tokens"] / (ms * c["layers"]) * 1e3, tops=ops / ms / 1e9,
+                   parallelism="single GPU" if world == 1 else f"ep{world}: {c['E'] // world} experts and {Lr} tokens per GPU")
+        pkg._lib.check_status()
+        if world == 1:
+            # batch-1 decode of the same layer: RMSNorm + INT8 of one row, router, gather-GEMV over the 8 chosen experts
+            # (gate|up with SwiGLU, then down on per-slot rows), weighted combine; 128 steps with fresh logits each
+            nw = torch.ones(c["D"], dtype=torch.bfloat16, device="cuda")
+            pos = torch.arange(c["topk"], dtype=torch.int32, device="cuda")
+            lg1, _ = zipf_logits(torch, c["decode_steps"], c["E"], c["zipf"], seed=3)
+            x1 = torch.randn((c["decode_steps"], 1, c["D"]), generator=g, device="cuda").to(torch.bfloat16)
+
+            def step(i):
+                xq, xs = S.rmsnorm_quant(x1[i], nw, 1e-5, 1)
+                ind1, sc1 = M_.router_topk(lg1[i:i + 1], c["topk"])
+                e = ind1.reshape(-1)
+                act = G.gemv(xq, blk.gu[0], blk.gu[1], xs, blk.gu[2], 2 * c["F"], 3, eidx=e, xstride=0)
+                yd = G.gemv(act, blk.dn[0], blk.dn[1], None, blk.dn[2], c["D"], 1, eidx=e, xstride=1, pro=1)
+                return M_.moe_combine(yd, pos, sc1, x1[i], nw, 1e-5, 1, quant=False)[0]
+            step(0)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for i in range(c["decode_steps"]):
+                    step(i)
+            graph.replay()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(3):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) / 3 / c["decode_steps"] * 1e3
+            nb = c["topk"] * (gemv_bytes_fmt(2 * c["F"], c["D"], 16, 2) + gemv_bytes_fmt(c["D"], c["F"], 16, 2))
+            out["decode"] = dict(steps=c["decode_steps"], us_per_step_one_layer=us, packed_bytes_per_step=nb, gbs=nb / us / 1e3,
+                                 form="gather-GEMV over the 8 routed experts (register kernel, expert ids read on the device)")
+            pkg._lib.check_status()
+        return out
+    finally:
+        S.set_format(F.Format())
+
+
+def gemv_bytes_fmt(n, k, block, bc_bits):
+    return n * k // 2 + n * k * bc_bits // (8 * block) + 4 * n + k + 4 + 2 * n
+
+
 def bench_moe(pkg, torch, dist=None, reps=5, weak=False, blk=None):
     """OLMoE-shaped MoE half-block at 4096 tokens: quant -> route -> (dispatch) -> two grouped GEMMs -> (return) -> combine.
     With a process group: experts sharded by rank, tokens split by rank, dispatch and return over NVLink.
@@ -534,6 +671,15 @@ def run_ours(args):
     if args.no_pdl:
         pkg._lib.call("scmx_set_pdl", 0)
     pk = peaks()
+    if args.workload == "moe5":
+        r = bench_moe5(pkg, torch, dist if world > 1 else None)
+        if rank == 0:
+            print(json.dumps(dict(metric="moe_prefill_tokens_per_s", value=r["tokens_per_s_one_layer"], unit="tokens/s (one layer)",
+                                  n_gpus=world, config=dict(workload="large-MoE stress: 128 experts, F=768, block-16 format, "
+                                                                     "Zipf(1.2) routing, 8192 tokens"), moe5=r)))
+        if world > 1:
+            dist.destroy_process_group()
+        return
     parity = None
     if world > 1:
         try:
@@ -695,6 +841,11 @@ def run_ours(args):
             line["moe_weak"] = bench_moe(pkg, torch, dist, weak=True)
         except Exception as e:   # noqa: BLE001
             line["moe_weak"] = dict(error=f"{type(e).__name__}: {e}")
+    torch.cuda.empty_cache()
+    try:
+        line["moe5"] = bench_moe5(pkg, torch, dist if world > 1 else None)
+    except Exception as e:   # noqa: BLE001
+        line["moe5"] = dict(error=f"{type(e).__name__}: {e}"[:300])
     if world == 1:
         torch.cuda.empty_cache()
         try:       # whole-model time to first token and decode tokens/s through the fused callers (attention included)
@@ -898,6 +1049,41 @@ def run_case(args):
             torch.cuda.profiler.stop()
         torch.cuda.synchronize()
         dec.check_status()
+    elif args.case == "ep1":      # the per-rank work of the 8-GPU expert-parallel half-block on one GPU: a world of one rank
+        # with 8 experts (top-8: every token visits all of them) and 512 tokens = 4096 rows, through the peer-memory kernels
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+        cfg = dict(OLMOE, E=8, tokens=512)
+        blk = build_moe_block(pkg, torch, cfg=cfg, shard=(0, 1))
+        blk.early = False
+        layer = pkg.parallel.PeerExpertParallelMoe(pkg, blk, 8, 8, 512)
+        h = torch.randn((512, 2048), generator=g, device="cuda").to(torch.bfloat16)
+        lg = torch.randn((512, 8), generator=g, device="cuda")
+        for _ in range(3):
+            layer.step(h, lg)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            layer.step(h, lg)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(20):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        print(json.dumps(dict(case="ep1", ms_per_half_block=e0.elapsed_time(e1) / 20)))
+        torch.cuda.profiler.start()
+        graph.replay()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        pkg._lib.check_status()
+        dist.destroy_process_group()
+        return
     elif args.case == "models":
         print(json.dumps(dict(case="models", models=bench_models(pkg, torch))))
         return
@@ -918,7 +1104,8 @@ def main():
     ap.add_argument("--no-overlap", action="store_true", help="decode weights on the main stream instead of a side stream")
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic stream serialization")
     ap.add_argument("--dense-only", action="store_true", help="skip the roofline / decode / MoE / CPU sections")
-    ap.add_argument("--case", choices=["gemm", "gemmw4", "gemv", "gemvbig", "gemvlist", "moe", "models", "decodestep", "decodechain"], help="run one small kernel case (for profiler captures) and exit")
+    ap.add_argument("--workload", default="all", choices=["all", "moe5"], help="moe5: only the large-MoE stress section")
+    ap.add_argument("--case", choices=["gemm", "gemmw4", "gemv", "gemvbig", "gemvlist", "moe", "ep1", "models", "decodestep", "decodechain"], help="run one small kernel case (for profiler captures) and exit")
     args = ap.parse_args()
     if args.case:
         run_case(args)

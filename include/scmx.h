@@ -212,6 +212,13 @@ int scmx_moe_mm_w4(const int8_t* xq, int64_t R, const uint32_t* codes, const uin
                    const int32_t* off, int E, int64_t N, int64_t K, const scmx_format* fmt, int epi, const float* xscale,
                    void* out, int32_t* status, void* stream);
 
+/* scmx_moe_mm_w4 with the row-mapped epilogue of scmx_moe_mm_i8_ret (EPI 1; output row r stored at row ret_row[r] of
+ * out_peers[ret_rank[r]]): the down GEMM of the expert-parallel block when the weights are read packed. */
+int scmx_moe_mm_w4_ret(const int8_t* xq, int64_t R, const uint32_t* codes, const uint8_t* bcodes, const float* wscale,
+                       const int32_t* off, int E, int64_t N, int64_t K, const scmx_format* fmt, const float* xscale,
+                       const int32_t* ret_rank, const int32_t* ret_row, int world, void* const* out_peers, int32_t* status,
+                       void* stream);
+
 /* scmx_moe_mm without a scratch argument; it has no counterpart in the reference (whose arrays are allocated by MLX).
  * For hosts that cannot hand the library device memory at call time: a serving process that gave all of HBM to its own
  * pool at start-up (a cudaMalloc there would fail, or stall the device mid-request), or a foreign-language runtime bound

@@ -61,25 +61,23 @@ __global__ void __launch_bounds__(128) ep_dispatch_kernel(const int8_t* __restri
 __global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int world, int32_t* epoch, int32_t* status, uint64_t limit_ns) {
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ int s_epoch;
-    if (threadIdx.x == 0) s_epoch = *epoch + 1;
-    __syncthreads();
-    const int ep = s_epoch;
-    __threadfence_system();
+    const int ep = *epoch + 1;
     if (threadIdx.x < world) {
-        volatile int32_t* theirs = reinterpret_cast<volatile int32_t*>(flags.p[threadIdx.x]) + rank;
-        *theirs = ep;
-        __threadfence_system();
-        volatile int32_t* mine = reinterpret_cast<volatile int32_t*>(flags.p[rank]) + threadIdx.x;
+        // release: everything this GPU wrote before (earlier kernels of the stream included) is visible system-wide before the flag
+        int32_t* theirs = reinterpret_cast<int32_t*>(flags.p[threadIdx.x]) + rank;
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(theirs), "r"(ep) : "memory");
+        const int32_t* mine = reinterpret_cast<const int32_t*>(flags.p[rank]) + threadIdx.x;
         const uint64_t t0 = globaltimer_ns();
-        while (*mine < ep) {
+        for (;;) {
+            int v;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+            if (v >= ep) break;
             if (globaltimer_ns() - t0 > limit_ns) {
                 if (atomicCAS(status, 0, 20) == 0) { status[1] = rank; status[2] = threadIdx.x; }
                 break;
             }
             __nanosleep(100);
         }
-        __threadfence_system();
     }
     __syncthreads();
     if (threadIdx.x == 0) *epoch = ep;

@@ -444,3 +444,32 @@ extern "C" int scmx_moe_mm_w4(const int8_t* xq, int64_t R, const uint32_t* codes
     g.off = off; g.E = E; g.e_begin = 0; g.e_end = E; g.status = status;
     return run_w4(xq, R, codes, bcodes, (int64_t)E * N, f, g, (cudaStream_t)stream);
 }
+
+extern "C" int scmx_moe_mm_w4_ret(const int8_t* xq, int64_t R, const uint32_t* codes, const uint8_t* bcodes, const float* wscale,
+                                  const int32_t* off, int E, int64_t N, int64_t K, const scmx_format* fmt, const float* xscale,
+                                  const int32_t* ret_rank, const int32_t* ret_row, int world, void* const* out_peers,
+                                  int32_t* status, void* stream) {
+    int rc = check_common("moe_mm_w4_ret", N, K, 1, xscale, wscale, out_peers, status);
+    if (rc) return rc;
+    DevFormat f;
+    rc = make_dev_format(fmt, &f);
+    if (rc) return rc;
+    SCMX_REQUIRE(w4_supported(f, K), SCMX_EFORMAT, "moe_mm_w4_ret: needs K %% 128 == 0 and 8, 16 or 32 block-code bits per 128 weights");
+    SCMX_REQUIRE(E >= 1 && E <= W4_MAX_E && R >= 0 && R < (1ll << 30) && off, SCMX_EINVAL, "moe_mm_w4_ret: bad E (1..%d) / R / offsets", W4_MAX_E);
+    SCMX_REQUIRE((int64_t)E * N < (1ll << 31), SCMX_ELIMIT, "moe_mm_w4_ret: E*N too large");
+    SCMX_REQUIRE(ret_rank && ret_row && world >= 1 && world <= 8, SCMX_EINVAL, "moe_mm_w4_ret: return map / world (1..8)");
+    SCMX_REQUIRE(codes && bcodes && ((reinterpret_cast<uintptr_t>(xq) | reinterpret_cast<uintptr_t>(codes)) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(bcodes) & 3) == 0,
+                 SCMX_EINVAL, "moe_mm_w4_ret: xq and codes must be 16-byte aligned, bcodes 4-byte aligned");
+    if (R == 0) return SCMX_OK;
+    GemmArgs g = {};
+    g.M = (int)R; g.N = (int)N; g.K = (int)K; g.epi = 1; g.xscale = xscale; g.wscale = wscale; g.out = out_peers[0];
+    g.off = off; g.E = E; g.e_begin = 0; g.e_end = E; g.status = status;
+    g.ret_rank = ret_rank; g.ret_row = ret_row;
+    for (int i = 0; i < 8; ++i) {
+        g.peer_out[i] = i < world ? static_cast<uint16_t*>(out_peers[i]) : nullptr;
+        SCMX_REQUIRE(i >= world || (g.peer_out[i] != nullptr && (reinterpret_cast<uintptr_t>(g.peer_out[i]) & 15) == 0), SCMX_EINVAL,
+                     "moe_mm_w4_ret: return buffer of rank %d is NULL or not 16-byte aligned", i);
+    }
+    return run_w4(xq, R, codes, bcodes, (int64_t)E * N, f, g, (cudaStream_t)stream);
+}

@@ -221,6 +221,12 @@ class PeerExpertParallelMoe:
         # pull_combine: the down GEMM stores its rows by receive slot in a local buffer (the same epilogue scatter, local) and
         # after one barrier every rank's combine loads the rows of its tokens from the owners over peer memory: no return kernel
         self.pull_combine = True
+        # fused: the grouped GEMMs read the packed expert weights and expand them inside the kernel (scmx_moe_mm_w4): no per-step
+        # decode launches and no INT8 copy.  Per rank the block is a chain of short kernels, where two launches fewer count.
+        self.fused = bool(pkg.sc_moe.FUSED_UNPACK and block_local.E <= 512 and
+                          L_.lib().scmx_w4_supported(pkg.sc_format.DEFAULT.c_struct(), D) and
+                          L_.lib().scmx_w4_supported(pkg.sc_format.DEFAULT.c_struct(), block_local.F))
+        self.fmt = pkg.sc_format.DEFAULT
         if self.early_decode:
             self.side = torch.cuda.Stream(device=dev)
             self.gu8 = torch.empty((El * 2 * F, D), dtype=torch.int8, device=dev)
@@ -244,7 +250,8 @@ class PeerExpertParallelMoe:
         Lr, D = h.shape
         assert Lr == self.Lr
         R, TM, F = Lr * k, M_.TM, blk.F
-        if self.early_decode:
+        fused = self.fused and self.early_decode and self.pull_combine
+        if self.early_decode and not fused:
             main = torch.cuda.current_stream()
             self.side.wait_stream(main)
             with torch.cuda.stream(self.side):
@@ -265,7 +272,9 @@ class PeerExpertParallelMoe:
         L_.call("scmx_gather_rows_dyn", L_.ptr(self.rx_q), L_.ptr(self.rx_s), L_.ptr(self.tok2), L_.ptr(self.n_rows), self.r_cap, TM, D,
                 L_.ptr(xq_r), L_.ptr(xs_r), L_.stream())
         mt = -(-self.r_cap // TM) + blk.E
-        if self.early_decode:
+        if fused:
+            act = M_.moe_mm(xq_r, self.r_cap, *blk.gu, self.off2, self.ts2, mt, 2 * F, 3, xs_r)
+        elif self.early_decode:
             main.wait_event(decoded)
             act = M_.moe_mm_i8(xq_r, self.r_cap, self.gu8, blk.gu[2], self.off2, self.ts2, mt, 2 * F, 3, xs_r)
         else:
@@ -273,6 +282,16 @@ class PeerExpertParallelMoe:
         xq2 = torch.empty((self.r_cap + TM, F), dtype=torch.int8, device=h.device)
         xs2 = torch.empty(self.r_cap + TM, dtype=torch.float32, device=h.device)
         L_.call("scmx_act_quant_dyn", L_.ptr(act), L_.ptr(self.n_rows), self.r_cap, TM, F, L_.ptr(xq2), L_.ptr(xs2), L_.stream())
+        if fused:
+            own = (ctypes.c_void_p * 8)(self.y_slot.data_ptr(), *([None] * 7))
+            L_.call("scmx_moe_mm_w4_ret", L_.ptr(xq2), self.r_cap, L_.ptr(blk.dn[0]), L_.ptr(blk.dn[1]), L_.ptr(blk.dn[2]), L_.ptr(self.off2),
+                    blk.E, D, F, self.fmt.c_struct(), L_.ptr(xs2), L_.ptr(self.zero_rank), L_.ptr(self.tok2), 1, own,
+                    L_.ptr(L_.status_buffer()), L_.stream())
+            self._barrier()
+            hout = torch.empty((Lr, D), dtype=torch.bfloat16, device=h.device)
+            L_.call("scmx_moe_combine_pull", self._peers["y_slot"], G, self.rank, blk.E, self.cap, L_.ptr(es), L_.ptr(off), L_.ptr(pos),
+                    L_.ptr(scores), L_.ptr(h), L_.ptr(blk.nw), float(blk.eps), Lr, Lr, D, k, 0, L_.ptr(hout), None, None, L_.stream())
+            return hout
         if self.early_decode and self.pull_combine:
             own = (ctypes.c_void_p * 8)(self.y_slot.data_ptr(), *([None] * 7))
             L_.call("scmx_moe_mm_i8_ret", L_.ptr(xq2), self.r_cap, L_.ptr(self.dn8), L_.ptr(blk.dn[2]), L_.ptr(self.off2),

@@ -130,7 +130,11 @@ def _worker_body(rank, world, port, q):
         pep.early_decode = False
         o5 = pep.step(hl, ll)
         pep.early_decode, pep.pull_combine = True, True
-        o4 = o4 if torch.equal(o4, o6) else o6 * float("nan")
+        was_fused = pep.fused            # the default reads packed weights inside the GEMMs; also the decode-then-GEMM form
+        pep.fused = False
+        o7 = pep.step(hl, ll)
+        pep.fused = was_fused
+        o4 = o4 if torch.equal(o4, o6) and torch.equal(o4, o7) else o6 * float("nan")
         torch.cuda.synchronize()
         ok["peer_ep_variants"] = bool(torch.equal(o4, o1)) and bool(torch.equal(o5, o1))
         graph = torch.cuda.CUDAGraph()
