@@ -250,7 +250,8 @@ class PeerExpertParallelMoe:
         Lr, D = h.shape
         assert Lr == self.Lr
         R, TM, F = Lr * k, M_.TM, blk.F
-        fused = self.fused and self.early_decode and self.pull_combine
+        # packed-weight GEMMs only where a local expert sees few rows (expected rows per expert = tokens * topk / experts)
+        fused = self.fused and self.early_decode and self.pull_combine and (Lr * k * G) // self.E < blk.FUSED_BELOW
         if self.early_decode and not fused:
             main = torch.cuda.current_stream()
             self.side.wait_stream(main)
