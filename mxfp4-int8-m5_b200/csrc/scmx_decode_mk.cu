@@ -211,23 +211,23 @@ __device__ __forceinline__ void compute_chunk(const RowChunk& c, const int8_t* x
             const uint4 xa = *reinterpret_cast<const uint4*>(xq + k0);
             const uint4 xb = *reinterpret_cast<const uint4*>(xq + k0 + 16);
             const uint32_t x[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-            uint32_t xn[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) xn[j] = neg4(x[j]);
             const int sh = ((k0 >> 5) & 3) * 2;               // the lane's 32-block inside its block-code byte
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const uint32_t ww[4] = {c.w[u][q].x, c.w[u][q].y, c.w[u][q].z, c.w[u][q].w};
                 const uint32_t code = (__shfl_sync(0xffffffffu, c.bc[u], (lane & ~3) | q) >> sh) & 3u;
-                int bs = 0;
+                // magnitudes of the positive and of the negative codes by sign-replicating byte permutes (a selector nibble with
+                // its top bit set yields the replicated top bit of the selected byte, 0 for a magnitude), two DP4A chains
+                int bp = 0, bn = 0;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const uint32_t sel = ww[j] & 0x77777777u;
-                    const uint32_t ssel = ((ww[j] >> 1) & 0x44444444u) | 0x32103210u;
-                    bs = dp4a_ss(prmt(x[2 * j], xn[2 * j], ssel), prmt(mlo, mhi, sel), bs);
-                    bs = dp4a_ss(prmt(x[2 * j + 1], xn[2 * j + 1], ssel >> 16), prmt(mlo, mhi, sel >> 16), bs);
+                    const uint32_t w = ww[j], wx = w ^ 0x88888888u;
+                    bp = dp4a_ss(x[2 * j], prmt(mlo, mhi, w), bp);
+                    bn = dp4a_ss(x[2 * j], prmt(mlo, mhi, wx), bn);
+                    bp = dp4a_ss(x[2 * j + 1], prmt(mlo, mhi, w >> 16), bp);
+                    bn = dp4a_ss(x[2 * j + 1], prmt(mlo, mhi, wx >> 16), bn);
                 }
-                tot[q] += bs << code;
+                tot[q] += (bp - bn) << code;
             }
         }
     }

@@ -40,6 +40,18 @@ struct GemvArgs {
 };
 
 
+// The 8 codes of word w against activations xa (codes 0..3) and xb (codes 4..7).  The byte permute's selector nibble is the code
+// itself: with its top bit (the sign) set, the permute returns the replicated top bit of the selected byte, i.e. 0 for a
+// magnitude; so prmt(LUT, w) holds the magnitudes of the positive codes and prmt(LUT, w ^ 0x88888888) those of the negative
+// ones.  Two DP4A chains, subtracted by the caller: no negated copy of the activations, no sign-select permute.
+__device__ __forceinline__ void word_pn(uint32_t w, uint32_t xa, uint32_t xb, uint32_t mlo, uint32_t mhi, int& ap, int& an) {
+    const uint32_t wx = w ^ 0x88888888u;
+    ap = dp4a_ss(xa, prmt(mlo, mhi, w), ap);
+    an = dp4a_ss(xa, prmt(mlo, mhi, wx), an);
+    ap = dp4a_ss(xb, prmt(mlo, mhi, w >> 16), ap);
+    an = dp4a_ss(xb, prmt(mlo, mhi, wx >> 16), an);
+}
+
 // PRO 0: INT8 input row and its scale are given.  PRO 1 / 2: the input is a bf16 row; every CTA first computes the
 // per-token INT8 row (PRO 2: of its RMSNorm) in shared memory with the arithmetic of the row kernels (act_quant,
 // rmsnorm_quant), after the weight loads are in flight, so the separate kernel and its launch disappear from the chain.
@@ -161,36 +173,24 @@ __global__ void __launch_bounds__(256) gemv_kernel(const GemvArgs a) {
         const uint4 xa = *reinterpret_cast<const uint4*>(xq + k0s[s]);
         const uint4 xb = *reinterpret_cast<const uint4*>(xq + k0s[s] + 16);
         const uint32_t x[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-        uint32_t xn[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) xn[j] = neg4(x[j]);
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
             const uint32_t ww[4] = {w[s][r].x, w[s][r].y, w[s][r].z, w[s][r].w};
             if (B32) {
                 const int blk = block_of(a.f, k0s[s]);
                 const uint32_t code = (bc[s][r] >> ((blk & a.f.pb_mask) << a.f.bc_shift)) & a.f.bc_mask;
-                int bs = 0;
+                int bp = 0, bn = 0;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint32_t sel = ww[j] & 0x77777777u;
-                    const uint32_t ssel = ((ww[j] >> 1) & 0x44444444u) | 0x32103210u;
-                    bs = __dp4a((int)__byte_perm(x[2 * j], xn[2 * j], ssel), (int)__byte_perm(a.f.mag_lo, a.f.mag_hi, sel), bs);
-                    bs = __dp4a((int)__byte_perm(x[2 * j + 1], xn[2 * j + 1], ssel >> 16),
-                                (int)__byte_perm(a.f.mag_lo, a.f.mag_hi, sel >> 16), bs);
-                }
-                tot[r] += a.f.pow2 ? (bs << code) : bs * (int)fmt_mult(a.f, code);
+                for (int j = 0; j < 4; ++j) word_pn(ww[j], x[2 * j], x[2 * j + 1], a.f.mag_lo, a.f.mag_hi, bp, bn);
+                tot[r] += a.f.pow2 ? ((bp - bn) << code) : (bp - bn) * (int)fmt_mult(a.f, code);
             } else {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int bi = (8 * j) >> a.f.block_shift;   // block index inside the lane's 32 codes
                     const uint32_t code = (bc[s][r] >> (bi << a.f.bc_shift)) & a.f.bc_mask;
-                    const uint32_t sel = ww[j] & 0x77777777u;
-                    const uint32_t ssel = ((ww[j] >> 1) & 0x44444444u) | 0x32103210u;
-                    int bs = __dp4a((int)__byte_perm(x[2 * j], xn[2 * j], ssel), (int)__byte_perm(a.f.mag_lo, a.f.mag_hi, sel), 0);
-                    bs = __dp4a((int)__byte_perm(x[2 * j + 1], xn[2 * j + 1], ssel >> 16),
-                                (int)__byte_perm(a.f.mag_lo, a.f.mag_hi, sel >> 16), bs);
-                    tot[r] += bs * (int)fmt_mult(a.f, code);
+                    int bp = 0, bn = 0;
+                    word_pn(ww[j], x[2 * j], x[2 * j + 1], a.f.mag_lo, a.f.mag_hi, bp, bn);
+                    tot[r] += (bp - bn) * (int)fmt_mult(a.f, code);
                 }
             }
         }
