@@ -87,3 +87,42 @@ def test_no_cpu_fallback(scmx):
     import torch
     with pytest.raises(TypeError):
         scmx.sc_kernels.act_quant(torch.zeros(4, 64, dtype=torch.bfloat16))
+
+
+def test_gemv_list_plan_geometry(scmx):
+    """scmx_gemv_multi_plan is host code: tile shapes must respect the stage size (64 KB of codes, 2 KB of block codes), use at
+    most 16 consumer warps, and number the tiles of the jobs consecutively.  Pointers only need to be non-NULL and aligned."""
+    import ctypes
+    L = scmx._lib
+    shapes = [(4096, 2048), (2048, 2048), (12288, 2048), (2048, 6144), (100, 1024), (64, 8192), (1024, 3072), (4, 512)]
+    jobs = (L.ScmxGemvJob * len(shapes))()
+    for rec, (n, k) in zip(jobs, shapes):
+        rec.codes = rec.bcodes = rec.wscale = rec.xq = rec.xscale = rec.out = 0x1000
+        rec.N, rec.K, rec.epi = n, k, 1
+    fmt = scmx.sc_format.DEFAULT.c_struct()
+    assert L.lib().scmx_gemv_multi_plan(ctypes.byref(jobs), len(shapes), fmt) == 0, L.lib().scmx_last_error_string()
+    tile0 = 0
+    for rec, (n, k) in zip(jobs, shapes):
+        tr, rg, sk, t0, nt, bcrow, kw = (rec.plan[i] for i in range(7))
+        assert tr == 4 * rg and 1 <= rg * sk <= 16 and tr * k // 2 <= 65536 and tr * bcrow <= 2048
+        assert kw * sk == k and kw % 32 == 0 and bcrow == k // 128
+        assert t0 == tile0 and nt == -(-n // tr)
+        tile0 += nt
+    assert all(rec.plan[8] == tile0 for rec in jobs)
+    assert jobs[0].plan[0] == 64 and jobs[3].plan[1] * jobs[3].plan[2] == 15      # K = 2048: 64-row tiles; K = 6144: 5 x 3 warps
+    jobs[1].K = 128                                                                # one block-code byte per row: not a multiple of 4
+    assert L.lib().scmx_gemv_multi_plan(ctypes.byref(jobs), len(shapes), fmt) == -5
+    jobs[1].K = 100                                                                # not a multiple of 128
+    assert L.lib().scmx_gemv_multi_plan(ctypes.byref(jobs), len(shapes), fmt) == -1
+    jobs[1].K = 16384                                                              # beyond the activation slot of a stage
+    assert L.lib().scmx_gemv_multi_plan(ctypes.byref(jobs), len(shapes), fmt) == -1
+
+
+def test_packed_weight_gemm_format_rule(scmx):
+    """scmx_w4_supported: the block codes of 128 weights must form one field of 8, 16 or 32 bits, K a multiple of 128."""
+    F, L = scmx.sc_format, scmx._lib
+    ok = lambda fmt, k: L.lib().scmx_w4_supported(fmt.c_struct(), k)   # noqa: E731
+    assert ok(F.Format(), 2048) and ok(F.Format(block=16), 768) and ok(F.Format(block=16, mult=(1, 2, 3, 4, 5, 6, 8, 10), bc_bits=4), 2048)
+    assert not ok(F.Format(), 2048 + 64)
+    assert not ok(F.Format(block=64), 2048)            # 4 bits per 128 weights
+    assert not ok(F.Format(block=8), 2048)             # 32 bits only with 2-bit codes: 16 blocks x 2 bits
