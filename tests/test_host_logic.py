@@ -125,4 +125,5 @@ def test_packed_weight_gemm_format_rule(scmx):
     assert ok(F.Format(), 2048) and ok(F.Format(block=16), 768) and ok(F.Format(block=16, mult=(1, 2, 3, 4, 5, 6, 8, 10), bc_bits=4), 2048)
     assert not ok(F.Format(), 2048 + 64)
     assert not ok(F.Format(block=64), 2048)            # 4 bits per 128 weights
-    assert not ok(F.Format(block=8), 2048)             # 32 bits only with 2-bit codes: 16 blocks x 2 bits
+    assert ok(F.Format(block=8), 2048)                 # 16 blocks x 2 bits = 32 bits
+    assert not ok(F.Format(block=8, mult=(1, 2, 3, 4, 5, 6, 8, 10), bc_bits=4), 2048)      # 64 bits
