@@ -258,6 +258,13 @@ int scmx_ep_plan(const int32_t* rx_meta, int world, int El, int64_t cap, int tm,
 /* Stores expert output row p (bf16 [D]) into rank ret_rank[p]'s y_back at row ret_row[p], for p < n_rows[0]. */
 int scmx_ep_return(const uint16_t* y, const int32_t* ret_rank, const int32_t* ret_row, const int32_t* n_rows, int64_t r_cap,
                    int64_t D, int world, const void* const* y_back_peers, void* stream);
+/* scmx_mm_i8 whose epilogue IS the all-gather of tensor parallelism: every output line is stored at the same row and column
+ * of out_peers[0 .. world) (HOST array of device pointers: each GPU's copy of the output segment of THIS rank, this GPU's own
+ * included; peer buffers are peer-mapped memory), straight from the staged epilogue in full 128-byte lines.  Follow with
+ * scmx_peer_barrier before any rank reads.  epi 1, 2 or 3; M > 128 and N >= 256 (the CTA-pair kernel).  Replaces
+ * scmx_mm_i8 + scmx_peer_put.  No counterpart in the single-device reference. */
+int scmx_mm_i8_bcast(const int8_t* xq, const int8_t* wq, int64_t M, int64_t N, int64_t K, int epi, const float* xscale,
+                     const float* wscale, const uint16_t* res, void* const* out_peers, int world, int32_t* status, void* stream);
 /* scmx_moe_mm_i8 with EPI 1 whose epilogue IS the return exchange of expert parallelism: bf16 output row r of the grouped
  * GEMM is stored at row ret_row[r] of out_peers[ret_rank[r]] (bf16 [*, N] buffers of the `world` GPUs, this GPU's own
  * included; peer buffers are device pointers of peer-mapped memory), straight from the TMEM accumulators, instead of being

@@ -62,6 +62,7 @@ SIGNATURES = {
     "scmx_moe_mm_w4": [c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, _FMT_P, c_int, c_vp, c_vp, c_vp, c_vp],
     "scmx_moe_mm_w4_ret": [c_vp, c_i64, c_vp, c_vp, c_vp, c_vp, c_int, c_i64, c_i64, _FMT_P, c_vp, c_vp, c_vp, c_int, c_vp, c_vp,
                            c_vp],
+    "scmx_mm_i8_bcast": [c_vp, c_vp, c_i64, c_i64, c_i64, c_int, c_vp, c_vp, c_vp, c_vp, c_int, c_vp, c_vp],
     "scmx_set_gemm_tile": [c_int],
     "scmx_set_gemm_pair": [c_int],
     "scmx_set_pdl": [c_int],

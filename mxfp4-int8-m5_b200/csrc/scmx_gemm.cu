@@ -337,6 +337,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(CTA_THREADS, 1)
             a.status[2] = threadIdx.x;
         }
     }
+    if (a.bcast > 0 && warp >= 2) __threadfence_system();      // this thread's stores into the peers' buffers are performed
     __syncwarp();
     tc_fence_before();
     __syncthreads();
@@ -541,6 +542,30 @@ extern "C" int scmx_mm_i8(const int8_t* xq, const int8_t* wq, int64_t M, int64_t
     GemmArgs a = {};
     a.M = (int)M; a.N = (int)N; a.K = (int)K; a.epi = epi; a.xscale = xscale; a.wscale = wscale; a.res = res; a.out = out;
     a.status = status;
+    return run_gemm(xq, M, wq, N, a, (cudaStream_t)stream);
+}
+
+extern "C" int scmx_mm_i8_bcast(const int8_t* xq, const int8_t* wq, int64_t M, int64_t N, int64_t K, int epi, const float* xscale,
+                                const float* wscale, const uint16_t* res, void* const* out_peers, int world, int32_t* status,
+                                void* stream) {
+    int rc = check_common("mm_i8_bcast", N, K, epi, xscale, wscale, out_peers, status);
+    if (rc) return rc;
+    SCMX_REQUIRE(epi >= 1 && epi <= 3, SCMX_EINVAL, "mm_i8_bcast: epi must be 1, 2 or 3");
+    SCMX_REQUIRE(M > BM && M < (1ll << 30) && N >= PAIR_BN, SCMX_ELIMIT, "mm_i8_bcast: needs M > %d and N >= %d (the CTA-pair kernel)", BM, PAIR_BN);
+    SCMX_REQUIRE(epi != 2 || res, SCMX_EINVAL, "mm_i8_bcast: epi 2 needs res");
+    SCMX_REQUIRE(world >= 1 && world <= 8, SCMX_EINVAL, "mm_i8_bcast: world=%d outside 1..8", world);
+    SCMX_REQUIRE((reinterpret_cast<uintptr_t>(xq) & 15) == 0 && (reinterpret_cast<uintptr_t>(wq) & 15) == 0 &&
+                     (!res || (reinterpret_cast<uintptr_t>(res) & 15) == 0),
+                 SCMX_EINVAL, "mm_i8_bcast: xq, wq and res must be 16-byte aligned");
+    GemmArgs a = {};
+    a.M = (int)M; a.N = (int)N; a.K = (int)K; a.epi = epi; a.xscale = xscale; a.wscale = wscale; a.res = res; a.out = out_peers[0];
+    a.status = status; a.bcast = world;
+    for (int g = 0; g < 8; ++g) {
+        a.peer_out[g] = g < world ? static_cast<uint16_t*>(out_peers[g]) : nullptr;
+        SCMX_REQUIRE(g >= world || (a.peer_out[g] != nullptr && (reinterpret_cast<uintptr_t>(a.peer_out[g]) & 15) == 0), SCMX_EINVAL,
+                     "mm_i8_bcast: output buffer of rank %d is NULL or not 16-byte aligned", g);
+    }
+    SCMX_REQUIRE(g_use_pair && !g_bn_override, SCMX_EINVAL, "mm_i8_bcast: the CTA-pair kernel is switched off");
     return run_gemm(xq, M, wq, N, a, (cudaStream_t)stream);
 }
 

@@ -32,6 +32,7 @@ struct GemmArgs {
     // EPI 1 with a return map (expert parallelism): output row r is stored at row ret_row[r] of peer_out[ret_rank[r]], the
     // buffer of the GPU the token came from, instead of row r of `out`: the GEMM's epilogue is the return exchange.
     const int32_t* ret_rank;
+    int bcast;                   // > 0 (tensor parallelism): every output row is stored into peer_out[0 .. bcast) at the same row / column
     const int32_t* ret_row;
     uint16_t* peer_out[8];
 };
@@ -200,8 +201,16 @@ __device__ __forceinline__ void epi_drain(const GemmArgs& a, const uint8_t* stg,
         const uint4 v = *reinterpret_cast<const uint4*>(stg + rl * EPI_PITCH + piece * 16);
         const int row = row0 + rl;
         if (row < row_end && piece * 16 < valid) {
-            uint8_t* p = out_row_ptr(a, row, row_bytes);
-            if (p != nullptr) *reinterpret_cast<uint4*>(p + col_byte0 + piece * 16) = v;
+            if (a.bcast > 0) {
+                // the all-gather of tensor parallelism issued from the epilogue: the same full line into every GPU's buffer
+                const size_t o = (size_t)row * row_bytes + col_byte0 + piece * 16;
+#pragma unroll
+                for (int g = 0; g < 8; ++g)
+                    if (g < a.bcast) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(a.peer_out[g]) + o) = v;
+            } else {
+                uint8_t* p = out_row_ptr(a, row, row_bytes);
+                if (p != nullptr) *reinterpret_cast<uint4*>(p + col_byte0 + piece * 16) = v;
+            }
         }
     }
 }

@@ -1,4 +1,4 @@
-// Instruction-level helpers of the decode GEMV kernels: streaming 128-bit loads, per-byte negation, byte permute, DP4A.
+// Instruction-level helpers of the decode GEMV kernels: streaming 128-bit loads, byte permute, DP4A.
 #pragma once
 #include <stdint.h>
 
@@ -10,15 +10,8 @@ __device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
     return v;
 }
 
-// Per-byte two's-complement negation of four INT8 without carries between bytes:
-// -b = ~b + 1; the low seven bits of ~b plus one never overflow the byte, and the top bit is folded in with an XOR.
-__device__ __forceinline__ uint32_t neg4(uint32_t x) {
-    const uint32_t nx = ~x;
-    return ((nx & 0x7F7F7F7Fu) + 0x01010101u) ^ (nx & 0x80808080u);
-}
-
-// prmt.b32 in its default mode: selector nibble bits 0-2 pick one of the eight source bytes (every selector built below
-// has bit 3 of each nibble clear, so no sanitising AND is needed).
+// prmt.b32 in its default mode: selector nibble bits 0-2 pick one of the eight source bytes; with bit 3 set the result byte
+// is the replicated top bit of the selected byte (0x00 for values below 128), which the kernels use to zero one sign's codes.
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     uint32_t d;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));

@@ -413,14 +413,11 @@ int launch_jobs(const scmx_gemv_job* jobs_host, const scmx_gemv_job* jobs_dev, i
         SCMX_CUDA_OK(cudaFuncSetAttribute(gemv_multi_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GM_SMEM));
         configured[dev] = true;
     }
-    const int keep = g_use_pdl;
-    g_use_pdl = pdl ? keep : 0;
     cudaError_t e;
-    if (b32) e = pow2 ? launch_pdl(gemv_multi_kernel<true, true>, dim3(grid), dim3(GM_THREADS), (size_t)GM_SMEM, st, a)
-                      : launch_pdl(gemv_multi_kernel<true, false>, dim3(grid), dim3(GM_THREADS), (size_t)GM_SMEM, st, a);
-    else e = pow2 ? launch_pdl(gemv_multi_kernel<false, true>, dim3(grid), dim3(GM_THREADS), (size_t)GM_SMEM, st, a)
-                  : launch_pdl(gemv_multi_kernel<false, false>, dim3(grid), dim3(GM_THREADS), (size_t)GM_SMEM, st, a);
-    g_use_pdl = keep;
+    if (b32) e = pow2 ? launch_pdl_opt(pdl, gemv_multi_kernel<true, true>, dim3(grid), dim3(GM_THREADS), (size_t)GM_SMEM, st, a)
+                      : launch_pdl_opt(pdl, gemv_multi_kernel<true, false>, dim3(grid), dim3(GM_THREADS), (size_t)GM_SMEM, st, a);
+    else e = pow2 ? launch_pdl_opt(pdl, gemv_multi_kernel<false, true>, dim3(grid), dim3(GM_THREADS), (size_t)GM_SMEM, st, a)
+                  : launch_pdl_opt(pdl, gemv_multi_kernel<false, false>, dim3(grid), dim3(GM_THREADS), (size_t)GM_SMEM, st, a);
     SCMX_PDL_OK("gemv_multi_kernel", e);
     return SCMX_OK;
 }

@@ -349,20 +349,66 @@ class PeerTensorParallelDense(TensorParallelDense):
         L_ = self.pkg_lib
         nbytes = local.numel() * local.element_size()
         L_.call("scmx_peer_put", L_.ptr(local), nbytes, self.rank * nbytes, self._peers[name], self.world, L_.stream())
-        L_.call("scmx_peer_barrier", self._peers["flags"], self.rank, self.world, L_.ptr(self.epoch), L_.ptr(L_.status_buffer()),
-                L_.stream())
+        self._barrier()
         return self.bufs[name]
 
+    def _barrier(self):
+        L_ = self.pkg_lib
+        L_.call("scmx_peer_barrier", self._peers["flags"], self.rank, self.world, L_.ptr(self.epoch), L_.ptr(L_.status_buffer()),
+                L_.stream())
+
+    def _segment_peers(self, name):
+        """Host array of pointers: this rank's segment inside every rank's copy of buffer `name`."""
+        import ctypes
+        if name not in self._seg_peers:
+            t = self.bufs[name]
+            seg_bytes = t[0].numel() * t.element_size()
+            ptrs = [v.data_ptr() + self.rank * seg_bytes for v in self._views[name]]
+            self._seg_peers[name] = (ctypes.c_void_p * 8)(*ptrs, *([None] * (8 - self.world)))
+        return self._seg_peers[name]
+
+    def _gemm_gather(self, g, xq, xs, epi, name, res=None):
+        """GEMM g of the step whose output columns are gathered into segment buffer `name` on every rank.  When the shard is
+        wide enough for the CTA-pair kernel the gather is the GEMM's own epilogue (scmx_mm_i8_bcast: full lines stored into every
+        GPU's buffer while other tiles compute) and only the barrier follows; otherwise GEMM, store kernel, barrier."""
+        L_, S = self.pkg_lib, self.S
+        _, _, ws, n, k = self.ring.seq[g]
+        wq = self.ring.weight(g)
+        M = xq.shape[0]
+        n_out = n // 2 if epi == 3 else n
+        if self.fused_gather and M > 128 and n >= 256:
+            L_.call("scmx_mm_i8_bcast", L_.ptr(xq), L_.ptr(wq), M, n, k, epi, L_.ptr(xs), L_.ptr(ws), L_.ptr(res) if epi == 2 else None,
+                    self._segment_peers(name), self.world, L_.ptr(L_.status_buffer()), L_.stream())
+            self.ring.released(g)
+            self._barrier()
+            return self.bufs[name]
+        y = S.mm_epi(xq, wq, xs, ws, epi, res=res)
+        self.ring.released(g)
+        assert y.shape[1] == n_out
+        return self.gather_to(y, name)
+
     def step(self, h_seg, o_local):
+        from . import fused_dense as FD
         S, M, r = self.S, self.M, self.rank
-        cur = h_seg
+        if not hasattr(self, "ring"):
+            big = max(n * k for lw in self.layers for (_, _, _, n, k) in lw.values())
+            self.ring = FD.DecodeRing(big, self.nw.device, overlap=True)
+            self._seg_peers = {}
+            self.fused_gather = True
+        ring = self.ring
+        ring.begin([lw[g] for lw in self.layers for g in FD.GROUPS])
+        cur, g = h_seg, 0
         for lw in self.layers:
             xq, xs = S.rmsnorm_quant_seg(cur, self.nw, self.eps, M)
-            self._gemm(lw, "qkv", xq, xs, 1)
+            _, _, ws, n, k = ring.seq[g]
+            S.mm_epi(xq, ring.weight(g), xs, ws, 1)               # this rank's heads; attention is outside the path
+            ring.released(g)
             oq, os_ = S.act_quant_seg(self.gather_to(o_local, "o"), M)
-            nxt = self.gather_to(self._gemm(lw, "o", oq, os_, 2, res=cur[r]), "h0")
+            nxt = self._gemm_gather(g + 1, oq, os_, 2, "h0", res=cur[r])
             xq, xs = S.rmsnorm_quant_seg(nxt, self.nw, self.eps, M)
-            act = self._gemm(lw, "gu", xq, xs, 3)
-            aq, as_ = S.act_quant_seg(self.gather_to(act, "act"), M)
-            cur = self.gather_to(self._gemm(lw, "down", aq, as_, 2, res=nxt[r]), "h1")
+            act = self._gemm_gather(g + 2, xq, xs, 3, "act")
+            aq, as_ = S.act_quant_seg(act, M)
+            cur = self._gemm_gather(g + 3, aq, as_, 2, "h1", res=nxt[r])
+            g += 4
+        ring.end()
         return cur
