@@ -4,9 +4,10 @@ reference builds in FusedQwen3._block_fns (e2e/fused_qwen3.py:161-173): per laye
     gate|up GEMM (SwiGLU, rows interleaved) -> act_quant -> down GEMM (+ residual).
 Attention itself (RoPE, KV cache, SDPA) is outside the W4A8 path; the caller supplies its output.
 
-Every GEMM reads an INT8 operand decoded from the packed 4-bit codes just before it.  The decode of GEMM g+1 runs on a
-side stream while GEMM g occupies the tensor cores (the reference overlaps the same two kernels through its `deps`
-arguments, e2e/sc_kernels.py:18-20); two rotating scratch buffers stay resident in L2."""
+Every GEMM reads an INT8 operand decoded from the packed 4-bit codes shortly before it.  The decodes of layer l+1 run on a
+side stream while the GEMMs of layer l occupy the tensor cores (the reference overlaps the same two kernels through its `deps`
+arguments, e2e/sc_kernels.py:18-20); two rotating sets of scratch buffers (two layers of INT8, about 100 MB for a
+Qwen3-1.7B-shaped layer) are rewritten every step."""
 import torch
 
 from . import sc_kernels as S
@@ -15,70 +16,97 @@ GROUPS = ("qkv", "o", "gu", "down")
 
 
 class DecodeRing:
-    """Schedules the 4-bit -> INT8 decode of a sequence of weights around the GEMMs that consume them: two rotating
-    scratch buffers, the decode of weight g + 1 issued on a side stream just before GEMM g is launched, events in both
-    directions (decoded -> GEMM may start; GEMM finished -> its buffer may be overwritten).  Capturable in a CUDA graph."""
+    """Schedules the 4-bit -> INT8 decode of a sequence of weights around the GEMMs that consume them.  The sequence is cut into
+    groups of `group` consecutive weights; two rotating sets of scratch buffers hold the current and the next group.  The decode
+    of group j + 1 is issued on a side stream when group j is joined, events in both directions (group decoded -> its GEMMs may
+    start; last GEMM of a group launched -> its buffers may be overwritten).  Capturable in a CUDA graph.
 
-    def __init__(self, max_elems, device, overlap=True):
-        self.bufs = [torch.empty(max_elems, dtype=torch.int8, device=device) for _ in range(2)]
+    The main stream waits on the side stream once per group (join), so with group = 4 only the first launch of a layer has two
+    predecessors in a captured graph; every other launch keeps its single predecessor and with it the programmatic
+    (launch-overlapping) edge.  group = 1 joins before every GEMM."""
+
+    def __init__(self, max_elems, device, overlap=True, group=1):
+        self.group, self.device = group, device
+        self.sizes = [max_elems] * group if isinstance(max_elems, int) else list(max_elems)
+        assert len(self.sizes) == group
+        self.bufs = [[torch.empty(n, dtype=torch.int8, device=device) for n in self.sizes] for _ in range(2)]
         self.overlap = overlap
         self.side = torch.cuda.Stream(device=device) if overlap else None
 
     def begin(self, seq):
         """seq: list of (codes, bcodes, wscale, N, K) in the order the GEMMs run."""
-        self.seq, n = seq, len(seq)
-        self.ready, self.done = [None] * n, [None] * n
+        self.seq, self._joined = seq, None
+        ng = -(-len(seq) // self.group)
+        self.ready, self.done = [None] * ng, [None] * ng
         self.main = torch.cuda.current_stream()
         if self.overlap:
             self.side.wait_stream(self.main)
-            self._decode(0)
+            self._decode_group(0)
 
     def _view(self, g):
         _, _, _, N, K = self.seq[g]
-        return self.bufs[g % 2][:N * K].view(N, K)
+        j, p = divmod(g, self.group)
+        assert N * K <= self.sizes[p]
+        return self.bufs[j % 2][p][:N * K].view(N, K)
 
-    def _decode(self, g):
-        codes, bc, _, N, K = self.seq[g]
+    def _decode_group(self, j):
+        lo, hi = j * self.group, min((j + 1) * self.group, len(self.seq))
         if not self.overlap:
-            S.unpack_i8(codes, bc, N, K, out=self._view(g))
+            for g in range(lo, hi):
+                codes, bc, _, N, K = self.seq[g]
+                S.unpack_i8(codes, bc, N, K, out=self._view(g))
             return
         with torch.cuda.stream(self.side):
-            if g >= 2:
-                self.side.wait_event(self.done[g - 2])       # the GEMM that last read this buffer
-            S.unpack_i8(codes, bc, N, K, out=self._view(g))
-            self.ready[g] = torch.cuda.Event()
-            self.ready[g].record(self.side)
+            if j >= 2:
+                self.side.wait_event(self.done[j - 2])       # the last GEMM that read this set of buffers
+            for g in range(lo, hi):
+                codes, bc, _, N, K = self.seq[g]
+                S.unpack_i8(codes, bc, N, K, out=self._view(g))
+            self.ready[j] = torch.cuda.Event()
+            self.ready[j].record(self.side)
+
+    def join(self, g):
+        """Make the main stream wait for the decode of g's group and start the next group's decode.  Called by weight() when
+        g opens a group; a caller may call it earlier (before the launches that precede the group's first GEMM)."""
+        j = g // self.group
+        if getattr(self, "_joined", None) == (id(self.seq), j):
+            return
+        self._joined = (id(self.seq), j)
+        if self.overlap:
+            if (j + 1) * self.group < len(self.seq):
+                self._decode_group(j + 1)                    # overlaps with the GEMMs of group j
+            self.main.wait_event(self.ready[j])
+        else:
+            self._decode_group(j)
 
     def weight(self, g):
         """INT8 operand of GEMM g; call right before launching it."""
-        if self.overlap:
-            if g + 1 < len(self.seq):
-                self._decode(g + 1)                          # overlaps with GEMM g
-            self.main.wait_event(self.ready[g])
-        else:
-            self._decode(g)
+        if g % self.group == 0:
+            self.join(g)
         return self._view(g)
 
     def released(self, g):
         """Call right after launching GEMM g."""
-        if self.overlap:
-            self.done[g] = torch.cuda.Event()
-            self.done[g].record(self.main)
+        if self.overlap and (g % self.group == self.group - 1 or g == len(self.seq) - 1):
+            self.done[g // self.group] = torch.cuda.Event()
+            self.done[g // self.group].record(self.main)
 
     def end(self):
+        self._joined = None
         if self.overlap:
             self.main.wait_stream(self.side)
 
 
 class DenseStack:
-    def __init__(self, layers, M, hidden, eps=1e-6, overlap=True):
+    def __init__(self, layers, M, hidden, eps=1e-6, overlap=True, ring_group=len(GROUPS)):
         """layers: list of {group: (codes, bcodes, wscale, N, K)} with gate|up rows already interleaved
         (sc_kernels.interleave_gate_up); M: rows (a multiple of 128); hidden: model width."""
         assert M % S.TM == 0
         self.layers, self.M, self.hidden, self.eps, self.overlap = layers, M, hidden, eps, overlap
         dev = layers[0]["qkv"][0].device
-        big = max(n * k for lw in layers for (_, _, _, n, k) in lw.values())
-        self.ring = DecodeRing(big, dev, overlap)
+        assert len(GROUPS) % ring_group == 0
+        sizes = [max(lw[g][3] * lw[g][4] for lw in layers for g in GROUPS[p::ring_group]) for p in range(ring_group)]
+        self.ring = DecodeRing(sizes, dev, overlap, group=ring_group)
         self.nw = torch.ones(hidden, dtype=torch.bfloat16, device=dev)
         self.launches_per_layer = 12
 
@@ -108,6 +136,7 @@ class DenseStack:
 
         g = 0
         for _ in self.layers:
+            ring.join(g)                                     # the layer's one wait on the decode stream
             xq, xs = S.rmsnorm_quant(h, self.nw, self.eps, M)
             gemm(g, xq, xs, 1)                               # q|k|v (consumed by attention, outside this path)
             oq, os_ = S.act_quant(o, M)

@@ -421,3 +421,31 @@ def test_pair_kernel_equals_single_cta_kernel(scmx, M, N, K, epi):
     assert torch.equal(a, b)
     if epi == 0:
         assert torch.equal(a, torch._int_mm(xq, wq.t()) if M > 32 and M % 8 == 0 else a)
+
+
+@pytest.mark.parametrize("M,N,K,epi", [(512, 1024, 2048, 2), (384, 768, 512, 3), (256, 256, 128, 1)])
+def test_gemm_with_gather_epilogue_one_rank(scmx, M, N, K, epi):
+    """scmx_mm_i8_bcast (the GEMM whose epilogue stores every output line into all ranks' buffers) with a world of one rank, and
+    with two output buffers on the same GPU standing in for two ranks: every copy equals the plain GEMM's output."""
+    import ctypes
+    S, L = scmx.sc_kernels, scmx._lib
+    g = torch.Generator(device="cuda").manual_seed(M + K)
+    xq = torch.randint(-127, 128, (M, K), dtype=torch.int8, device="cuda", generator=g)
+    wq = torch.randint(-96, 97, (N, K), dtype=torch.int8, device="cuda", generator=g)
+    xs = torch.rand(M, device="cuda", generator=g) * 1e-3
+    ws = torch.rand(N, device="cuda", generator=g) * 1e-3
+    res = torch.randn((M, N), device="cuda", generator=g).to(torch.bfloat16)
+    ref = S.mm_epi(xq, wq, xs, ws, epi, res=res if epi == 2 else None)
+    for world in (1, 2):
+        outs = [torch.full_like(ref, -3) for _ in range(world)]
+        peers = (ctypes.c_void_p * 8)(*[o.data_ptr() for o in outs], *([None] * (8 - world)))
+        L.call("scmx_mm_i8_bcast", L.ptr(xq), L.ptr(wq), M, N, K, epi, L.ptr(xs), L.ptr(ws), L.ptr(res) if epi == 2 else None,
+               peers, world, L.ptr(L.status_buffer()), L.stream())
+        _status_ok(scmx)
+        for o in outs:
+            assert torch.equal(o, ref)
+    # shapes the CTA-pair kernel does not take are refused, not silently run elsewhere
+    out = torch.empty_like(ref)
+    peers = (ctypes.c_void_p * 8)(out.data_ptr(), *([None] * 7))
+    assert L.lib().scmx_mm_i8_bcast(L.ptr(xq), L.ptr(wq), 128, N, K, 1, L.ptr(xs), L.ptr(ws), None, peers, 1,
+                                    L.ptr(L.status_buffer()), L.stream()) == -5

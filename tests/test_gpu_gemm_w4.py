@@ -21,7 +21,8 @@ def _pack(scmx, oracle, rng, N, K, fmt_kw):
 
 
 @pytest.mark.parametrize("fmt_kw", [dict(), dict(block=16), dict(block=16, mult=(1, 2, 3, 4, 5, 6, 8, 10), bc_bits=4),
-                                    dict(block=32, mult=(1, 2, 3, 4))])
+                                    dict(block=32, mult=(1, 2, 3, 4)), dict(block=8),
+                                    dict(block=32, code_mag=(0, 1, 2, 3, 4, 5, 6, 7), mult=(1, 3, 9, 15))])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 128), (256, 384, 2048), (384, 1024, 1024), (512, 2048, 6144), (640, 96, 256)])
 def test_dense_from_packed_exact(scmx, oracle, M, N, K, fmt_kw):
     S, F = scmx.sc_kernels, scmx.sc_format

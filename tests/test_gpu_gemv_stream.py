@@ -32,7 +32,8 @@ def _random_pack(scmx, oracle, rng, N, K, fmt_kw):
 SHAPES = [(64, 1024), (100, 2048), (2048, 2048), (516, 6144), (40, 8192), (4, 2048), (1028, 1024)]
 
 
-@pytest.mark.parametrize("fmt_kw", [dict(), dict(block=16), dict(block=32, mult=(1, 2, 3, 4))])
+@pytest.mark.parametrize("fmt_kw", [dict(), dict(block=16), dict(block=32, mult=(1, 2, 3, 4)), dict(block=8),
+                                    dict(block=16, mult=(1, 2, 3, 4, 5, 6, 8, 10), bc_bits=4), dict(block=64)])
 @pytest.mark.parametrize("N,K", SHAPES)
 def test_streaming_gemv_small_and_ragged(scmx, oracle, stream_always, N, K, fmt_kw):
     G, S, F = scmx.sc_decode, scmx.sc_kernels, scmx.sc_format
