@@ -153,7 +153,7 @@ __device__ __forceinline__ float pro_norm(const uint16_t* x, const uint16_t* nw,
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const float f0 = __uint_as_float(w[j] << 16), f1 = __uint_as_float(w[j] & 0xFFFF0000u);
-            ss += (double)f0 * (double)f0 + (double)f1 * (double)f1;
+            ss += sq_f64(f0) + sq_f64(f1);
         }
     }
     ss = block_sum(ss, sm.dred);
@@ -166,10 +166,9 @@ __device__ __forceinline__ float pro_norm(const uint16_t* x, const uint16_t* nw,
         uint32_t o[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const float f0 = rbf(__fmul_rn(__uint_as_float(w[j] << 16), rbf(__fmul_rn(__uint_as_float(x4[j] << 16), inv))));
-            const float f1 = rbf(__fmul_rn(__uint_as_float(w[j] & 0xFFFF0000u), rbf(__fmul_rn(__uint_as_float(x4[j] & 0xFFFF0000u), inv))));
-            amax = fmaxf(amax, fmaxf(fabsf(f0), fabsf(f1)));
-            o[j] = (__float_as_uint(f0) >> 16) | (__float_as_uint(f1) & 0xFFFF0000u);
+            const uint32_t t = pack_bf16x2(__fmul_rn(bf16_lo(x4[j]), inv), __fmul_rn(bf16_hi(x4[j]), inv));
+            o[j] = pack_bf16x2(__fmul_rn(bf16_lo(w[j]), bf16_lo(t)), __fmul_rn(bf16_hi(w[j]), bf16_hi(t)));
+            amax = fmaxf(amax, fmaxf(fabsf(bf16_lo(o[j])), fabsf(bf16_hi(o[j]))));
         }
         sm.xn[v] = make_uint4(o[0], o[1], o[2], o[3]);
     }

@@ -204,6 +204,9 @@ struct PairSmem {
     static constexpr int TOTAL = EPI_OFF + EPI_STAGE_BYTES + 1024;
 };
 
+// BCAST: the tensor-parallel form whose epilogue stores every output line into all ranks' buffers (a.bcast of them); an
+// instantiation of its own so that the ordinary kernel's drain loop carries none of it.
+template <bool BCAST>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(CTA_THREADS, 1)
     gemm_i8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmArgs a) {
     using L = PairSmem;
@@ -318,8 +321,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(CTA_THREADS, 1)
             epilogue_bar();
             if (*abort_flag) { if (!fail) fail = -1; break; }
             tc_fence_after();
-            epilogue_warp<BN>(a, tmem_base + acc * BN + chalf * (BN / 2) + ((uint32_t)(32 * q) << 16), ws + chalf * (BN / 2), wrow0, a.M,
-                              n0 + chalf * (BN / 2), smem + L::EPI_OFF + (warp - 2) * EPI_STAGE_WARP, lane, xs, rp);
+            epilogue_warp<BN, true, BCAST>(a, tmem_base + acc * BN + chalf * (BN / 2) + ((uint32_t)(32 * q) << 16), ws + chalf * (BN / 2),
+                                           wrow0, a.M, n0 + chalf * (BN / 2), smem + L::EPI_OFF + (warp - 2) * EPI_STAGE_WARP, lane, xs, rp);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -337,7 +340,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(CTA_THREADS, 1)
             a.status[2] = threadIdx.x;
         }
     }
-    if (a.bcast > 0 && warp >= 2) __threadfence_system();      // this thread's stores into the peers' buffers are performed
+    if (BCAST && warp >= 2) __threadfence_system();      // this thread's stores into the peers' buffers are performed
     __syncwarp();
     tc_fence_before();
     __syncthreads();
@@ -461,10 +464,14 @@ static int run_gemm(const int8_t* xq, int64_t a_rows, const int8_t* wq, int64_t 
         const int dev = current_device();
         SCMX_REQUIRE(dev >= 0, SCMX_ECUDA, "no current CUDA device (ordinal 0..63)");
         if (!configured[dev]) {
-            SCMX_CUDA_OK(cudaFuncSetAttribute(gemm_i8_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::TOTAL));
+            SCMX_CUDA_OK(cudaFuncSetAttribute(gemm_i8_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::TOTAL));
+            SCMX_CUDA_OK(cudaFuncSetAttribute(gemm_i8_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::TOTAL));
             configured[dev] = true;
         }
-        SCMX_PDL_OK("gemm_i8_pair_kernel", launch_pdl(gemm_i8_pair_kernel, dim3(2 * pairs), dim3(CTA_THREADS), (size_t)PairSmem::TOTAL, st, tmA, tmB, a));
+        if (a.bcast > 0)
+            SCMX_PDL_OK("gemm_i8_pair_kernel", launch_pdl(gemm_i8_pair_kernel<true>, dim3(2 * pairs), dim3(CTA_THREADS), (size_t)PairSmem::TOTAL, st, tmA, tmB, a));
+        else
+            SCMX_PDL_OK("gemm_i8_pair_kernel", launch_pdl(gemm_i8_pair_kernel<false>, dim3(2 * pairs), dim3(CTA_THREADS), (size_t)PairSmem::TOTAL, st, tmA, tmB, a));
         return SCMX_OK;
     }
     rc = make_map(&tmB, wq, b_rows, a.K, bn);

@@ -157,13 +157,6 @@ __device__ __forceinline__ Tile get_tile(const GemmArgs& a, int t, int tiles_m, 
 }
 
 // ---- epilogue of 32 consecutive columns of one row ----------------------------------------------------------------------
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-    uint32_t d;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
-    return d;
-}
-__device__ __forceinline__ float bf16_lo(uint32_t p) { return __uint_as_float(p << 16); }
-__device__ __forceinline__ float bf16_hi(uint32_t p) { return __uint_as_float(p & 0xFFFF0000u); }
 __device__ __forceinline__ float scale2(uint32_t acc, float xs, float w) { return __fmul_rn(__fmul_rn((float)(int)acc, xs), w); }
 
 // ---- epilogue of one warp: 32 rows x BN/2 accumulator columns ----------------------------------------------------------------
@@ -192,6 +185,7 @@ __device__ __forceinline__ uint8_t* out_row_ptr(const GemmArgs& a, int row, size
 }
 
 // Staged 32 x 128 bytes -> global memory; `valid` = bytes of the unit that lie inside the matrix (a multiple of 16).
+template <bool BCAST = false>
 __device__ __forceinline__ void epi_drain(const GemmArgs& a, const uint8_t* stg, int lane, int row0, int row_end, size_t row_bytes,
                                           size_t col_byte0, int valid) {
     const int piece = lane & 7, rsub = lane >> 3;
@@ -201,7 +195,7 @@ __device__ __forceinline__ void epi_drain(const GemmArgs& a, const uint8_t* stg,
         const uint4 v = *reinterpret_cast<const uint4*>(stg + rl * EPI_PITCH + piece * 16);
         const int row = row0 + rl;
         if (row < row_end && piece * 16 < valid) {
-            if (a.bcast > 0) {
+            if (BCAST) {
                 // the all-gather of tensor parallelism issued from the epilogue: the same full line into every GPU's buffer
                 const size_t o = (size_t)row * row_bytes + col_byte0 + piece * 16;
 #pragma unroll
@@ -283,7 +277,7 @@ __device__ __forceinline__ void epi_convert(const GemmArgs& a, const uint32_t (&
 // the first 64-column unit, loaded by the caller (epi_load_res) before it waited for the accumulators.
 // PIPE: keep the next chunk's tensor-memory load in flight while a chunk is converted (64 registers of accumulators instead
 // of 32); kernels with many other warps per CTA run it without.
-template <int BN, bool PIPE = true>
+template <int BN, bool PIPE = true, bool BCAST = false>
 __device__ __forceinline__ void epilogue_warp(const GemmArgs& a, uint32_t taddr, const float* ws, int row0, int row_end, int n0,
                                               uint8_t* stg, int lane, float xs, uint4 (&rp)[8]) {
     constexpr int CHUNKS = BN / 64;           // 32-column chunks per warp
@@ -302,7 +296,7 @@ __device__ __forceinline__ void epilogue_warp(const GemmArgs& a, uint32_t taddr,
         epi_convert(a, r0, ws + c * 32, xs, my, c);
         if (a.epi == 0) {
             __syncwarp();
-            epi_drain(a, stg, lane, row0, row_end, (size_t)a.N * 4, (size_t)(n0 + c * 32) * 4, min(128, (a.N - (n0 + c * 32)) * 4));
+            epi_drain<BCAST>(a, stg, lane, row0, row_end, (size_t)a.N * 4, (size_t)(n0 + c * 32) * 4, min(128, (a.N - (n0 + c * 32)) * 4));
             __syncwarp();
         }
         if (!PIPE) tmem_ld32(taddr + (c + 1) * 32, r0);
@@ -311,11 +305,11 @@ __device__ __forceinline__ void epilogue_warp(const GemmArgs& a, uint32_t taddr,
         epi_convert(a, PIPE ? reinterpret_cast<uint32_t(&)[32]>(r1) : r0, ws + (c + 1) * 32, xs, my, c + 1);
         if (a.epi == 0) {
             __syncwarp();
-            epi_drain(a, stg, lane, row0, row_end, (size_t)a.N * 4, (size_t)(n0 + (c + 1) * 32) * 4, min(128, (a.N - (n0 + (c + 1) * 32)) * 4));
+            epi_drain<BCAST>(a, stg, lane, row0, row_end, (size_t)a.N * 4, (size_t)(n0 + (c + 1) * 32) * 4, min(128, (a.N - (n0 + (c + 1) * 32)) * 4));
             __syncwarp();
         } else if (a.epi != 3) {
             __syncwarp();
-            epi_drain(a, stg, lane, row0, row_end, (size_t)a.N * 2, (size_t)(n0 + c * 32) * 2, min(128, (a.N - (n0 + c * 32)) * 2));
+            epi_drain<BCAST>(a, stg, lane, row0, row_end, (size_t)a.N * 2, (size_t)(n0 + c * 32) * 2, min(128, (a.N - (n0 + c * 32)) * 2));
             __syncwarp();
             if (a.epi == 2 && c + 2 < CHUNKS) {
                 epi_stage_res(stg, rp, lane);
@@ -327,7 +321,7 @@ __device__ __forceinline__ void epilogue_warp(const GemmArgs& a, uint32_t taddr,
     }
     if (a.epi == 3) {
         __syncwarp();
-        epi_drain(a, stg, lane, row0, row_end, (size_t)a.N, (size_t)n0, min(32 * CHUNKS, a.N - n0));
+        epi_drain<BCAST>(a, stg, lane, row0, row_end, (size_t)a.N, (size_t)n0, min(32 * CHUNKS, a.N - n0));
         __syncwarp();
     }
 }

@@ -71,7 +71,7 @@ __device__ __forceinline__ float gemv_prologue(const GemvArgs& a, int slot, int8
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const float f0 = __uint_as_float(w[j] << 16), f1 = __uint_as_float(w[j] & 0xFFFF0000u);
-            if (PRO == 2) ss += (double)f0 * (double)f0 + (double)f1 * (double)f1;
+            if (PRO == 2) ss += sq_f64(f0) + sq_f64(f1);
             else amax = fmaxf(amax, fmaxf(fabsf(f0), fabsf(f1)));
         }
     }
@@ -85,10 +85,9 @@ __device__ __forceinline__ float gemv_prologue(const GemvArgs& a, int slot, int8
             uint32_t o[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const float f0 = rbf(__fmul_rn(__uint_as_float(w[j] << 16), rbf(__fmul_rn(__uint_as_float(x[j] << 16), inv))));
-                const float f1 = rbf(__fmul_rn(__uint_as_float(w[j] & 0xFFFF0000u), rbf(__fmul_rn(__uint_as_float(x[j] & 0xFFFF0000u), inv))));
-                amax = fmaxf(amax, fmaxf(fabsf(f0), fabsf(f1)));
-                o[j] = (__float_as_uint(f0) >> 16) | (__float_as_uint(f1) & 0xFFFF0000u);
+                const uint32_t t = pack_bf16x2(__fmul_rn(bf16_lo(x[j]), inv), __fmul_rn(bf16_hi(x[j]), inv));
+                o[j] = pack_bf16x2(__fmul_rn(bf16_lo(w[j]), bf16_lo(t)), __fmul_rn(bf16_hi(w[j]), bf16_hi(t)));
+                amax = fmaxf(amax, fmaxf(fabsf(bf16_lo(o[j])), fabsf(bf16_hi(o[j]))));
             }
             xn_s[v] = make_uint4(o[0], o[1], o[2], o[3]);
         }

@@ -48,11 +48,26 @@ __device__ __forceinline__ void store8_i8(int8_t* p, const int q[8]) {
 }
 __device__ __forceinline__ void store8_bf16(uint16_t* p, const float v[8]) {
     uint4 o;
-    o.x = f32_to_bf16(v[0]) | ((uint32_t)f32_to_bf16(v[1]) << 16);
-    o.y = f32_to_bf16(v[2]) | ((uint32_t)f32_to_bf16(v[3]) << 16);
-    o.z = f32_to_bf16(v[4]) | ((uint32_t)f32_to_bf16(v[5]) << 16);
-    o.w = f32_to_bf16(v[6]) | ((uint32_t)f32_to_bf16(v[7]) << 16);
+    o.x = pack_bf16x2(v[0], v[1]);
+    o.y = pack_bf16x2(v[2], v[3]);
+    o.z = pack_bf16x2(v[4], v[5]);
+    o.w = pack_bf16x2(v[6], v[7]);
     *reinterpret_cast<uint4*>(p) = o;
+}
+
+// Eight elements of a row normalized in place: f[j] = T(w[j] * T(f[j] * inv)), T = round to bfloat16; returns them packed.
+// Roundings are taken two at a time (pack_bf16x2).
+__device__ __forceinline__ uint4 norm8(float (&f)[8], const uint4& wraw, float inv) {
+    const uint32_t w[4] = {wraw.x, wraw.y, wraw.z, wraw.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t t = pack_bf16x2(__fmul_rn(f[2 * j], inv), __fmul_rn(f[2 * j + 1], inv));
+        o[j] = pack_bf16x2(__fmul_rn(bf16_lo(w[j]), bf16_lo(t)), __fmul_rn(bf16_hi(w[j]), bf16_hi(t)));
+        f[2 * j] = bf16_lo(o[j]);
+        f[2 * j + 1] = bf16_hi(o[j]);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
 // ---- act_quant -------------------------------------------------------------------------------------------------------
@@ -118,32 +133,29 @@ __global__ void __launch_bounds__(256) rmsnorm_quant_kernel(const uint16_t* __re
         float v[8];
         load8_bf16(xrow + k, v);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) ss += (double)v[j] * (double)v[j];
+        for (int j = 0; j < 8; ++j) ss += sq_f64(v[j]);
     }
     ss = block_sum(ss, dred);
     const float inv = rms_inverse(ss, K, eps);
     float amax = 0.0f;
     for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
-        float v[8], w[8];
+        float v[8];
         load8_bf16(xrow + k, v);
-        load8_bf16(nw + k, w);
+        const uint4 o = norm8(v, *reinterpret_cast<const uint4*>(nw + k), inv);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            v[j] = rbf(__fmul_rn(w[j], rbf(__fmul_rn(v[j], inv))));
-            amax = fmaxf(amax, fabsf(v[j]));
-        }
-        if (xn) store8_bf16(xn + row * K + k, v);
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+        if (xn) *reinterpret_cast<uint4*>(xn + row * K + k) = o;
     }
     amax = block_max(amax, red);
     float s, qi;
     quant_scale(amax, s, qi);
     for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
-        float v[8], w[8];
+        float v[8];
         int q[8];
         load8_bf16(xrow + k, v);
-        load8_bf16(nw + k, w);
+        norm8(v, *reinterpret_cast<const uint4*>(nw + k), inv);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) q[j] = quant_code(rbf(__fmul_rn(w[j], rbf(__fmul_rn(v[j], inv)))), qi);
+        for (int j = 0; j < 8; ++j) q[j] = quant_code(v[j], qi);
         store8_i8(qrow + k, q);
     }
     if (threadIdx.x == 0) xs[row] = s;
@@ -210,14 +222,15 @@ __global__ void __launch_bounds__(256) row_quant_warp_kernel(const uint16_t* __r
     }
     float inv = 1.0f;
     if (NORM) {
-        double ss = 0.0;
+        double s4[4] = {0.0, 0.0, 0.0, 0.0};      // four chains instead of one: every partial sum is exact, so the grouping is free
 #pragma unroll
         for (int i = 0; i < MAXV; ++i) {
             float f[8];
             unpack8(raw[i], f);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) ss += (double)f[j] * (double)f[j];
+            for (int j = 0; j < 8; ++j) s4[j & 3] += sq_f64(f[j]);
         }
+        double ss = (s4[0] + s4[1]) + (s4[2] + s4[3]);
         ss = warp_sum(ss);
         inv = rms_inverse(ss, K, eps);
     }
@@ -228,15 +241,7 @@ __global__ void __launch_bounds__(256) row_quant_warp_kernel(const uint16_t* __r
         float f[8];
         unpack8(raw[i], f);
         if (NORM && v < nv) {
-            float w[8];
-            unpack8(reinterpret_cast<const uint4*>(nw)[v], w);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] = rbf(__fmul_rn(w[j], rbf(__fmul_rn(f[j], inv))));
-            uint4 o;
-            o.x = f32_to_bf16(f[0]) | ((uint32_t)f32_to_bf16(f[1]) << 16);
-            o.y = f32_to_bf16(f[2]) | ((uint32_t)f32_to_bf16(f[3]) << 16);
-            o.z = f32_to_bf16(f[4]) | ((uint32_t)f32_to_bf16(f[5]) << 16);
-            o.w = f32_to_bf16(f[6]) | ((uint32_t)f32_to_bf16(f[7]) << 16);
+            const uint4 o = norm8(f, reinterpret_cast<const uint4*>(nw)[v], inv);
             raw[i] = o;                        // keep the normalized row (bf16) for the quantization pass
             if (xn) reinterpret_cast<uint4*>(xn + row * K)[v] = o;
         }
@@ -291,14 +296,15 @@ __global__ void __launch_bounds__(256) row_quant_block_kernel(const uint16_t* __
     }
     float inv = 1.0f;
     if (NORM) {
-        double ss = 0.0;
+        double s4[4] = {0.0, 0.0, 0.0, 0.0};      // four chains instead of one: every partial sum is exact, so the grouping is free
 #pragma unroll
         for (int i = 0; i < MAXV; ++i) {
             float f[8];
             unpack8(raw[i], f);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) ss += (double)f[j] * (double)f[j];
+            for (int j = 0; j < 8; ++j) s4[j & 3] += sq_f64(f[j]);
         }
+        double ss = (s4[0] + s4[1]) + (s4[2] + s4[3]);
         ss = block_sum(ss, dred);
         inv = rms_inverse(ss, K, eps);
     }
@@ -309,15 +315,7 @@ __global__ void __launch_bounds__(256) row_quant_block_kernel(const uint16_t* __
         float f[8];
         unpack8(raw[i], f);
         if (NORM && v < nv) {
-            float w[8];
-            unpack8(reinterpret_cast<const uint4*>(nw)[v], w);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) f[j] = rbf(__fmul_rn(w[j], rbf(__fmul_rn(f[j], inv))));
-            uint4 o;
-            o.x = f32_to_bf16(f[0]) | ((uint32_t)f32_to_bf16(f[1]) << 16);
-            o.y = f32_to_bf16(f[2]) | ((uint32_t)f32_to_bf16(f[3]) << 16);
-            o.z = f32_to_bf16(f[4]) | ((uint32_t)f32_to_bf16(f[5]) << 16);
-            o.w = f32_to_bf16(f[6]) | ((uint32_t)f32_to_bf16(f[7]) << 16);
+            const uint4 o = norm8(f, reinterpret_cast<const uint4*>(nw)[v], inv);
             raw[i] = o;
             if (xn) reinterpret_cast<uint4*>(xn + row * K)[v] = o;
         }
@@ -495,19 +493,25 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t* __rest
                         const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
                         const float sc = s_sc[t0 + u];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            a[2 * j] = rbf(__fadd_rn(rbf(__fmul_rn(__uint_as_float(w[j] << 16), sc)), a[2 * j]));
-                            a[2 * j + 1] = rbf(__fadd_rn(rbf(__fmul_rn(__uint_as_float(w[j] & 0xFFFF0000u), sc)), a[2 * j + 1]));
+                        for (int j = 0; j < 4; ++j) {           // roundings two at a time
+                            const uint32_t t = pack_bf16x2(__fmul_rn(bf16_lo(w[j]), sc), __fmul_rn(bf16_hi(w[j]), sc));
+                            const uint32_t s2 = pack_bf16x2(__fadd_rn(bf16_lo(t), a[2 * j]), __fadd_rn(bf16_hi(t), a[2 * j + 1]));
+                            a[2 * j] = bf16_lo(s2);
+                            a[2 * j + 1] = bf16_hi(s2);
                         }
                     }
                 }
             }
 #pragma unroll
-            for (int j = 0; j < 8; ++j) r[j] = rbf(__fadd_rn(r[j], a[j]));
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t s2 = pack_bf16x2(__fadd_rn(r[2 * j], a[2 * j]), __fadd_rn(r[2 * j + 1], a[2 * j + 1]));
+                r[2 * j] = bf16_lo(s2);
+                r[2 * j + 1] = bf16_hi(s2);
+            }
         }
         store8_bf16(hrow + k, r);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) ss += (double)r[j] * (double)r[j];
+        for (int j = 0; j < 8; ++j) ss += sq_f64(r[j]);
     }
     if (!quant) return;
     int8_t* qrow = xq + row * K;
@@ -516,22 +520,22 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t* __rest
     const float inv = rms_inverse(ss, K, eps);
     float amax = 0.0f;
     for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
-        float v[8], w[8];
+        float v[8];
         load8_bf16(hrow + k, v);
-        load8_bf16(nw + k, w);
+        norm8(v, *reinterpret_cast<const uint4*>(nw + k), inv);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(rbf(__fmul_rn(w[j], rbf(__fmul_rn(v[j], inv))))));
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
     }
     amax = block_max(amax, red);
     float s, qi;
     quant_scale(amax, s, qi);
     for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
-        float v[8], w[8];
+        float v[8];
         int q[8];
         load8_bf16(hrow + k, v);
-        load8_bf16(nw + k, w);
+        norm8(v, *reinterpret_cast<const uint4*>(nw + k), inv);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) q[j] = quant_code(rbf(__fmul_rn(w[j], rbf(__fmul_rn(v[j], inv)))), qi);
+        for (int j = 0; j < 8; ++j) q[j] = quant_code(v[j], qi);
         store8_i8(qrow + k, q);
     }
     if (threadIdx.x == 0) xs[row] = s;
