@@ -487,7 +487,7 @@ def bench_moe(pkg, torch, dist=None, reps=5, weak=False, blk=None):
     if world > 1:
         try:
             layer = pkg.parallel.PeerExpertParallelMoe(pkg, blk, c["E"], c["topk"], Lr)
-            exchange = "dispatch by stores into peer memory, expert outputs pulled by the combine over NVLink, CUDA graph"
+            exchange = "dispatch by stores into peer memory, expert outputs returned by stores from the down GEMM's epilogue, CUDA graph"
         except Exception as e:   # noqa: BLE001
             print(f"# peer-memory path unavailable ({type(e).__name__}: {e}); using NCCL all-to-all, eager launches", file=sys.stderr)
             layer = pkg.parallel.ExpertParallelMoe(pkg, blk, c["E"], c["topk"])

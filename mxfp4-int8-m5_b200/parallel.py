@@ -204,6 +204,7 @@ class PeerExpertParallelMoe:
         # "pull" return: expert outputs stay here, ordered by receive slot; the token's owner reads them in its combine
         self.y_slot = torch.empty((G * self.cap, D), dtype=torch.bfloat16, device=dev)
         self.zero_rank = torch.zeros(G * self.cap + TM, **i32)
+        self._own_slot = (ctypes.c_void_p * 8)(self.y_slot.data_ptr(), *([None] * 7))
         for name in ("rx_q", "rx_s", "rx_meta", "y_back", "flags", "y_slot"):
             views = share_tensor(getattr(self, name), group)
             self._views[name] = views                      # keep the mappings alive
@@ -213,14 +214,15 @@ class PeerExpertParallelMoe:
         # side stream at the top of every step and overlaps routing, dispatch and the barrier (weights do not depend on them).
         F = block_local.F
         self.early_decode = El * 3 * F * D <= (1 << 30)
-        # fused_return: the down GEMM stores its rows straight into the senders' buffers (scmx_moe_mm_i8_ret) instead of a
-        # separate return kernel.  Off by default: measured slower on 2 GPUs (half-block 0.534 vs 0.390 ms) - an epilogue thread
-        # owns one row, so a warp's stores are 32 separate 64-byte pieces per instruction, which NVLink carries poorly, and the
-        # stalled epilogue holds the TMEM accumulators; the return kernel writes whole 4 KB rows.
-        self.fused_return = False
-        # pull_combine: the down GEMM stores its rows by receive slot in a local buffer (the same epilogue scatter, local) and
-        # after one barrier every rank's combine loads the rows of its tokens from the owners over peer memory: no return kernel
-        self.pull_combine = True
+        # How expert outputs travel back to the token's owner:
+        #   "push"   the down GEMM's epilogue stores every output row straight into the owner's buffer over NVLink (full
+        #            128-byte lines from the staged epilogue), so the transfer overlaps the GEMM; barrier; local combine.
+        #   "pull"   the down GEMM stores its rows by receive slot in a local buffer; barrier; every rank's combine loads
+        #            the rows of its tokens from the owners over peer memory.
+        #   "kernel" plain GEMM, then a return kernel (scmx_ep_return) storing whole rows; barrier; local combine.
+        # Measured on 2 GPUs, 4096 tokens per GPU: push 0.544 ms, pull 0.580 ms, kernel 0.611 ms (4096 tokens in total:
+        # 0.339 / 0.362 / 0.374 ms).  All three give the same bits.
+        self.return_mode = "push"
         # fused: the grouped GEMMs read the packed expert weights and expand them inside the kernel (scmx_moe_mm_w4): no per-step
         # decode launches and no INT8 copy.  Per rank the block is a chain of short kernels, where two launches fewer count.
         self.fused = bool(pkg.sc_moe.FUSED_UNPACK and block_local.E <= 512 and
@@ -251,7 +253,7 @@ class PeerExpertParallelMoe:
         assert Lr == self.Lr
         R, TM, F = Lr * k, M_.TM, blk.F
         # packed-weight GEMMs only where a local expert sees few rows (expected rows per expert = tokens * topk / experts)
-        fused = self.fused and self.early_decode and self.pull_combine and (Lr * k * G) // self.E < blk.FUSED_BELOW
+        fused = self.fused and self.early_decode and (Lr * k * G) // self.E < blk.FUSED_BELOW
         if self.early_decode and not fused:
             main = torch.cuda.current_stream()
             self.side.wait_stream(main)
@@ -273,49 +275,42 @@ class PeerExpertParallelMoe:
         L_.call("scmx_gather_rows_dyn", L_.ptr(self.rx_q), L_.ptr(self.rx_s), L_.ptr(self.tok2), L_.ptr(self.n_rows), self.r_cap, TM, D,
                 L_.ptr(xq_r), L_.ptr(xs_r), L_.stream())
         mt = -(-self.r_cap // TM) + blk.E
-        if fused:
+        if fused or not self.early_decode:
             act = M_.moe_mm(xq_r, self.r_cap, *blk.gu, self.off2, self.ts2, mt, 2 * F, 3, xs_r)
-        elif self.early_decode:
+        else:
             main.wait_event(decoded)
             act = M_.moe_mm_i8(xq_r, self.r_cap, self.gu8, blk.gu[2], self.off2, self.ts2, mt, 2 * F, 3, xs_r)
-        else:
-            act = M_.moe_mm(xq_r, self.r_cap, *blk.gu, self.off2, self.ts2, mt, 2 * F, 3, xs_r)
         xq2 = torch.empty((self.r_cap + TM, F), dtype=torch.int8, device=h.device)
         xs2 = torch.empty(self.r_cap + TM, dtype=torch.float32, device=h.device)
         L_.call("scmx_act_quant_dyn", L_.ptr(act), L_.ptr(self.n_rows), self.r_cap, TM, F, L_.ptr(xq2), L_.ptr(xs2), L_.stream())
-        if fused:
-            own = (ctypes.c_void_p * 8)(self.y_slot.data_ptr(), *([None] * 7))
-            L_.call("scmx_moe_mm_w4_ret", L_.ptr(xq2), self.r_cap, L_.ptr(blk.dn[0]), L_.ptr(blk.dn[1]), L_.ptr(blk.dn[2]), L_.ptr(self.off2),
-                    blk.E, D, F, self.fmt.c_struct(), L_.ptr(xs2), L_.ptr(self.zero_rank), L_.ptr(self.tok2), 1, own,
-                    L_.ptr(L_.status_buffer()), L_.stream())
-            self._barrier()
-            hout = torch.empty((Lr, D), dtype=torch.bfloat16, device=h.device)
-            L_.call("scmx_moe_combine_pull", self._peers["y_slot"], G, self.rank, blk.E, self.cap, L_.ptr(es), L_.ptr(off), L_.ptr(pos),
-                    L_.ptr(scores), L_.ptr(h), L_.ptr(blk.nw), float(blk.eps), Lr, Lr, D, k, 0, L_.ptr(hout), None, None, L_.stream())
-            return hout
-        if self.early_decode and self.pull_combine:
-            own = (ctypes.c_void_p * 8)(self.y_slot.data_ptr(), *([None] * 7))
-            L_.call("scmx_moe_mm_i8_ret", L_.ptr(xq2), self.r_cap, L_.ptr(self.dn8), L_.ptr(blk.dn[2]), L_.ptr(self.off2),
-                    L_.ptr(self.ts2), blk.E, D, F, L_.ptr(xs2), L_.ptr(self.zero_rank), L_.ptr(self.tok2), 1, own, TM,
-                    L_.ptr(L_.status_buffer()), L_.stream())
-            self._barrier()
-            hout = torch.empty((Lr, D), dtype=torch.bfloat16, device=h.device)
-            L_.call("scmx_moe_combine_pull", self._peers["y_slot"], G, self.rank, blk.E, self.cap, L_.ptr(es), L_.ptr(off), L_.ptr(pos),
-                    L_.ptr(scores), L_.ptr(h), L_.ptr(blk.nw), float(blk.eps), Lr, Lr, D, k, 0, L_.ptr(hout), None, None, L_.stream())
-            return hout
-        if self.early_decode and self.fused_return:
-            # the down GEMM's epilogue stores every output row into the buffer of the GPU its token came from
-            L_.call("scmx_moe_mm_i8_ret", L_.ptr(xq2), self.r_cap, L_.ptr(self.dn8), L_.ptr(blk.dn[2]), L_.ptr(self.off2),
-                    L_.ptr(self.ts2), blk.E, D, F, L_.ptr(xs2), L_.ptr(self.ret_rank), L_.ptr(self.ret_row), G,
-                    self._peers["y_back"], TM, L_.ptr(L_.status_buffer()), L_.stream())
-        else:
-            if self.early_decode:
-                yd = M_.moe_mm_i8(xq2, self.r_cap, self.dn8, blk.dn[2], self.off2, self.ts2, mt, D, 1, xs2)
-            else:
+        mode = self.return_mode if self.early_decode else "kernel"
+        if mode == "kernel":
+            if fused or not self.early_decode:
                 yd = M_.moe_mm(xq2, self.r_cap, *blk.dn, self.off2, self.ts2, mt, D, 1, xs2)
+            else:
+                yd = M_.moe_mm_i8(xq2, self.r_cap, self.dn8, blk.dn[2], self.off2, self.ts2, mt, D, 1, xs2)
             L_.call("scmx_ep_return", L_.ptr(yd), L_.ptr(self.ret_rank), L_.ptr(self.ret_row), L_.ptr(self.n_rows), self.r_cap, D, G,
                     self._peers["y_back"], L_.stream())
+        else:
+            # the down GEMM with a row-mapped epilogue: into the owners' y_back (push) or by receive slot into y_slot (pull)
+            if mode == "push":
+                rr, rw, world, dst = self.ret_rank, self.ret_row, G, self._peers["y_back"]
+            else:
+                rr, rw, world, dst = self.zero_rank, self.tok2, 1, self._own_slot
+            if fused:
+                L_.call("scmx_moe_mm_w4_ret", L_.ptr(xq2), self.r_cap, L_.ptr(blk.dn[0]), L_.ptr(blk.dn[1]), L_.ptr(blk.dn[2]),
+                        L_.ptr(self.off2), blk.E, D, F, self.fmt.c_struct(), L_.ptr(xs2), L_.ptr(rr), L_.ptr(rw), world, dst,
+                        L_.ptr(L_.status_buffer()), L_.stream())
+            else:
+                L_.call("scmx_moe_mm_i8_ret", L_.ptr(xq2), self.r_cap, L_.ptr(self.dn8), L_.ptr(blk.dn[2]), L_.ptr(self.off2),
+                        L_.ptr(self.ts2), blk.E, D, F, L_.ptr(xs2), L_.ptr(rr), L_.ptr(rw), world, dst, TM,
+                        L_.ptr(L_.status_buffer()), L_.stream())
         self._barrier()
+        if mode == "pull":
+            hout = torch.empty((Lr, D), dtype=torch.bfloat16, device=h.device)
+            L_.call("scmx_moe_combine_pull", self._peers["y_slot"], G, self.rank, blk.E, self.cap, L_.ptr(es), L_.ptr(off), L_.ptr(pos),
+                    L_.ptr(scores), L_.ptr(h), L_.ptr(blk.nw), float(blk.eps), Lr, Lr, D, k, 0, L_.ptr(hout), None, None, L_.stream())
+            return hout
         hout, _, _ = M_.moe_combine(self.y_back, pos, scores, h, blk.nw, blk.eps, Lr, quant=False)
         return hout
 

@@ -119,22 +119,20 @@ def _worker_body(rank, world, port, q):
         o2 = pep.step(hl, ll)
         torch.cuda.synchronize()
         ok["peer_ep"] = bool(torch.equal(o1, refm[rank * Lr:(rank + 1) * Lr])) and bool(torch.equal(o2, o1))
-        # variants of the return path: the default keeps the expert outputs on their GPU and the combine pulls them over
-        # peer memory; a separate return kernel; the return stores from the down GEMM's epilogue; the per-pass expert decode
-        assert pep.early_decode and pep.pull_combine and not pep.fused_return
-        pep.pull_combine = False
-        o4 = pep.step(hl, ll)
-        pep.fused_return = True
-        o6 = pep.step(hl, ll)
-        pep.fused_return = False
+        # variants: the three ways expert outputs return (default: stores from the down GEMM's epilogue), each with the
+        # packed-weight GEMMs (the default at this size) and with the decode-then-GEMM form; and the per-pass expert decode
+        assert pep.early_decode and pep.return_mode == "push"
+        outs = []
+        was_fused = pep.fused
+        for mode in ("push", "pull", "kernel"):
+            for f in ((was_fused, False) if was_fused else (False,)):
+                pep.return_mode, pep.fused = mode, f
+                outs.append(pep.step(hl, ll))
+        pep.return_mode, pep.fused = "push", was_fused
         pep.early_decode = False
         o5 = pep.step(hl, ll)
-        pep.early_decode, pep.pull_combine = True, True
-        was_fused = pep.fused            # the default reads packed weights inside the GEMMs; also the decode-then-GEMM form
-        pep.fused = False
-        o7 = pep.step(hl, ll)
-        pep.fused = was_fused
-        o4 = o4 if torch.equal(o4, o6) and torch.equal(o4, o7) else o6 * float("nan")
+        pep.early_decode = True
+        o4 = outs[0] if all(torch.equal(outs[0], o) for o in outs[1:]) else outs[0] * float("nan")
         torch.cuda.synchronize()
         ok["peer_ep_variants"] = bool(torch.equal(o4, o1)) and bool(torch.equal(o5, o1))
         graph = torch.cuda.CUDAGraph()
