@@ -995,6 +995,14 @@ def run_case(args):
         xs = torch.full((2048,), 1e-2, device="cuda")
         for _ in range(4):
             S.mm_w4_epi(xq, c, b, xs, ws, 12288, 3)
+    elif args.case == "rows":     # the row kernels between the GEMMs of a dense layer at M = 2048: RMSNorm + INT8 and act-quant
+        h = torch.randn((2048, 2048), generator=g, device="cuda").to(torch.bfloat16)
+        act = torch.randn((2048, 6144), generator=g, device="cuda").to(torch.bfloat16)
+        nw = torch.ones(2048, dtype=torch.bfloat16, device="cuda")
+        for _ in range(3):
+            S.rmsnorm_quant(h, nw, 1e-6, 2048)
+            S.act_quant(h, 2048)
+            S.act_quant(act, 2048)
     elif args.case == "gemv":     # 12 distinct gate|up weight sets (154 MB > L2), one GEMV each, two passes
         sets = []
         for _ in range(12):
@@ -1105,7 +1113,7 @@ def main():
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic stream serialization")
     ap.add_argument("--dense-only", action="store_true", help="skip the roofline / decode / MoE / CPU sections")
     ap.add_argument("--workload", default="all", choices=["all", "moe5"], help="moe5: only the large-MoE stress section")
-    ap.add_argument("--case", choices=["gemm", "gemmw4", "gemv", "gemvbig", "gemvlist", "moe", "ep1", "models", "decodestep", "decodechain"], help="run one small kernel case (for profiler captures) and exit")
+    ap.add_argument("--case", choices=["gemm", "gemmw4", "rows", "gemv", "gemvbig", "gemvlist", "moe", "ep1", "models", "decodestep", "decodechain"], help="run one small kernel case (for profiler captures) and exit")
     args = ap.parse_args()
     if args.case:
         run_case(args)
