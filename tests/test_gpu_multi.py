@@ -171,6 +171,24 @@ def test_tensor_and_expert_parallel_match_single_gpu():
     assert res == {0: want, 1: want}
 
 
+def test_peer_paths_as_a_world_of_one_rank():
+    """The peer-memory tensor-parallel stack and expert-parallel block (dispatch, plan, dynamic gather, grouped GEMMs with the
+    row-mapped epilogue in its three return forms, barriers, the gather epilogue of the dense GEMM) run as a world of ONE rank
+    on one GPU and equal the single-GPU stack / block bit for bit, eagerly and from a CUDA graph.  The same worker is the
+    2-GPU test's; here every box with a single GPU exercises those kernels."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_worker, args=(0, 1, 29653, q))
+    p.start()
+    res = q.get(timeout=200)
+    p.join(20)
+    if p.is_alive():
+        p.kill()
+    want = dict(tp=True, peer_tp=True, ep=True, peer_ep=True, peer_ep_variants=True, peer_ep_graph=True, two_pass=True)
+    assert res == (0, want)
+
+
 def test_dense_stack_overlap_equals_serial(scmx):
     """The side-stream weight decode changes scheduling only: results equal the single-stream chain bit for bit, also
     when replayed from a CUDA graph."""
