@@ -25,13 +25,16 @@ struct PeerPtrs {
     void* p[MAX_PEERS];
 };
 
-__global__ void __launch_bounds__(128) ep_dispatch_kernel(const int8_t* __restrict__ xq, const float* __restrict__ xs,
+// One warp per row (eight rows in flight per CTA, four 16-byte loads per lane issued before the stores): a row's copy starts
+// with three dependent index loads, which a CTA-per-row form exposes once per row.
+__global__ void __launch_bounds__(256) ep_dispatch_kernel(const int8_t* __restrict__ xq, const float* __restrict__ xs,
                                                           const int32_t* __restrict__ tok, const int32_t* __restrict__ esorted,
                                                           const int32_t* __restrict__ off, int R, int K, int E, int world, int rank,
                                                           int cap, PeerPtrs rx_q, PeerPtrs rx_s, PeerPtrs rx_meta) {
     pdl_launch_dependents();
     pdl_wait();
     const int El = E / world;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (blockIdx.x == gridDim.x - 1) {
         // the last CTA ships the count matrix: to rank d, the counts of its experts and the base row of that group here
         for (int i = threadIdx.x; i < world * (El + 1); i += blockDim.x) {
@@ -40,16 +43,27 @@ __global__ void __launch_bounds__(128) ep_dispatch_kernel(const int8_t* __restri
             reinterpret_cast<int32_t*>(rx_meta.p[d])[rank * (El + 1) + le] = v;
         }
     } else {
-        for (int p = blockIdx.x; p < R; p += gridDim.x - 1) {
+        const int nvec = K / 16;
+        const int wstride = ((int)gridDim.x - 1) * 8;
+        for (int p = (int)blockIdx.x * 8 + warp; p < R; p += wstride) {
             const int e = esorted[p];
-            const int d = e / El;
-            const int idx = p - off[d * El];                 // position among the rows this rank sends to rank d
             const int t = tok[p];
-            if (e < 0 || d >= world || idx < 0 || idx >= cap || t < 0) continue;   // inconsistent routing tables: touch nothing
+            const int d = e >= 0 ? e / El : world;
+            if (d >= world || t < 0) continue;                                     // inconsistent routing tables: touch nothing
+            const int idx = p - off[d * El];                 // position among the rows this rank sends to rank d
+            if (idx < 0 || idx >= cap) continue;
             const uint4* src = reinterpret_cast<const uint4*>(xq + (size_t)t * K);
             uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<int8_t*>(rx_q.p[d]) + ((size_t)rank * cap + idx) * K);
-            for (int i = threadIdx.x; i < K / 16; i += blockDim.x) dst[i] = src[i];
-            if (threadIdx.x == 0) reinterpret_cast<float*>(rx_s.p[d])[(size_t)rank * cap + idx] = xs[t];
+            for (int i0 = lane; i0 < nvec; i0 += 128) {
+                uint4 v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (i0 + 32 * u < nvec) v[u] = src[i0 + 32 * u];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (i0 + 32 * u < nvec) dst[i0 + 32 * u] = v[u];
+            }
+            if (lane == 0) reinterpret_cast<float*>(rx_s.p[d])[(size_t)rank * cap + idx] = xs[t];
         }
     }
     // one system-scope fence per CTA, after all of its threads' stores (the barrier kernel that follows publishes them)
@@ -266,8 +280,9 @@ extern "C" int scmx_ep_dispatch(const int8_t* xq, const float* xs, const int32_t
     if ((rc = fill_peers(&m, rx_meta_peers, world, "ep_dispatch"))) return rc;
     SCMX_REQUIRE(R >= 0 && R <= cap && K > 0 && K % 16 == 0 && E % world == 0 && E / world <= 128 && rank >= 0 && rank < world,
                  SCMX_EINVAL, "ep_dispatch: need R <= cap, K %% 16 == 0, E %% world == 0, E / world <= 128");
-    const unsigned dgrid = (unsigned)(R < 1184 ? R : 1184) + 1;     // row CTAs loop over the rows; the last CTA ships the counts
-    launch_pdl(ep_dispatch_kernel, dim3(dgrid), dim3(128), 0, (cudaStream_t)stream, xq, xs, tok, esorted, off, (int)R, (int)K,
+    const int64_t row_ctas = (R + 7) / 8;
+    const unsigned dgrid = (unsigned)(row_ctas < 1184 ? row_ctas : 1184) + 1;     // warps loop over the rows; the last CTA ships the counts
+    launch_pdl(ep_dispatch_kernel, dim3(dgrid), dim3(256), 0, (cudaStream_t)stream, xq, xs, tok, esorted, off, (int)R, (int)K,
                E, world, rank, (int)cap, q, s, m);
     SCMX_LAUNCH_OK("ep_dispatch_kernel");
     return SCMX_OK;

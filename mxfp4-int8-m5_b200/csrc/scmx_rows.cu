@@ -443,8 +443,11 @@ struct CombinePull {
     int El, cap, rank, world;
 };
 
+// Four CTAs per SM (63 registers): the kernel is a chain index loads -> barrier -> row loads -> sum -> store per CTA, hidden
+// only by other resident CTAs; with three per SM (67 registers) it ran at 42 % of DRAM throughput, 45 us against 39 us now
+// for 4096 tokens x 8 experts x 2048.
 template <int TOPK_MAX>
-__global__ void __launch_bounds__(256) moe_combine_kernel(const uint16_t* __restrict__ y, const int32_t* __restrict__ pos,
+__global__ void __launch_bounds__(256, 4) moe_combine_kernel(const uint16_t* __restrict__ y, const int32_t* __restrict__ pos,
                                                           const uint16_t* __restrict__ scores,
                                                           const uint16_t* __restrict__ res, const uint16_t* __restrict__ nw,
                                                           float eps, int64_t M, int K, int topk, int quant,
