@@ -79,9 +79,16 @@ class MoeBlock:
         L = h.shape[0]
         R = L * self.k
         decoded = self._start_decode() if (self.early and not self._fused(R)) else None
+        # routing (top-k, counting sort) does not depend on the quantized rows: it runs beside RMSNorm + INT8 on a stream of its own
+        main = torch.cuda.current_stream()
+        if not hasattr(self, "route_stream"):
+            self.route_stream = torch.cuda.Stream(device=h.device)
+        self.route_stream.wait_stream(main)
+        with torch.cuda.stream(self.route_stream):
+            inds, scores = M_.router_topk(logits, self.k)
+            pos, tok, _, off, ts, mt = M_.route_sort(inds, self.E, M_.TM)
         xq, xs = S.rmsnorm_quant(h, self.nw, self.eps, L)
-        inds, scores = M_.router_topk(logits, self.k)
-        pos, tok, _, off, ts, mt = M_.route_sort(inds, self.E, M_.TM)
+        main.wait_stream(self.route_stream)
         xq_s, xs_s = M_.gather_rows(xq, xs, tok, R)
         yd = self.experts(xq_s, xs_s, R, off, ts, mt, decoded)
         hout, _, _ = M_.moe_combine(yd, pos, scores, h, self.nw, self.eps, L, quant=False)

@@ -233,6 +233,7 @@ class PeerExpertParallelMoe:
             self.side = torch.cuda.Stream(device=dev)
             self.gu8 = torch.empty((El * 2 * F, D), dtype=torch.int8, device=dev)
             self.dn8 = torch.empty((El * D, F), dtype=torch.int8, device=dev)
+        self.route_stream = torch.cuda.Stream(device=dev)
         self.off2 = torch.empty(El + 1, **i32)
         self.ts2 = torch.empty(El + 1, **i32)
         self.tok2 = torch.empty(self.r_cap + TM, **i32)
@@ -262,9 +263,14 @@ class PeerExpertParallelMoe:
                 S.unpack_i8(blk.dn[0].reshape(-1), blk.dn[1].reshape(blk.E * D, -1), blk.E * D, F, out=self.dn8)
                 decoded = torch.cuda.Event()
                 decoded.record(self.side)
+        # routing (top-k, counting sort) does not depend on the quantized rows: it runs beside RMSNorm + INT8 on a stream of its own
+        cur = torch.cuda.current_stream()
+        self.route_stream.wait_stream(cur)
+        with torch.cuda.stream(self.route_stream):
+            inds, scores = M_.router_topk(logits, k)
+            pos, tok, es, off, _, _ = M_.route_sort(inds, self.E, TM)
         xq, xs = S.rmsnorm_quant(h, blk.nw, blk.eps, Lr)
-        inds, scores = M_.router_topk(logits, k)
-        pos, tok, es, off, _, _ = M_.route_sort(inds, self.E, TM)
+        cur.wait_stream(self.route_stream)
         L_.call("scmx_ep_dispatch", L_.ptr(xq), L_.ptr(xs), L_.ptr(tok), L_.ptr(es), L_.ptr(off), R, D, self.E, G, self.rank, self.cap,
                 self._peers["rx_q"], self._peers["rx_s"], self._peers["rx_meta"], L_.stream())
         self._barrier()
