@@ -189,35 +189,41 @@ __device__ __forceinline__ uint2 pack8_i8(const int q[8]) {
     return o;
 }
 
-template <int MAXV, bool NORM>
+// WPR warps share a row (WPR = 1, 2 or 4; 8 / WPR rows per CTA): each lane holds MAXV vectors, vector v = (i * WPR + part) * 32 +
+// lane.  With few rows (one warp per row leaves an SM a dozen warps) splitting a row shortens every warp's dependent chain and
+// doubles the warps that hide it; the partial sums and maxima meet through shared memory behind a barrier of the row's warps.
+template <int MAXV, bool NORM, int WPR>
 __global__ void __launch_bounds__(256) row_quant_warp_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ nw,
                                                              float eps, int64_t M, int64_t Mp, int K, RowSegs sg,
                                                              int8_t* __restrict__ xq, float* __restrict__ xs,
                                                              uint16_t* __restrict__ xn) {
     pdl_launch_dependents();
     pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= Mp) return;
+    __shared__ double s_ss[8];
+    __shared__ float s_am[8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int rin = warp / WPR, part = warp % WPR;          // row inside the CTA, this warp's part of it
+    const int64_t row = (int64_t)blockIdx.x * (8 / WPR) + rin;
+    if (row >= Mp) return;                                    // all warps of a row leave together
     const int nv = K / 8;                      // 16-byte vectors per row
     uint2* qrow = reinterpret_cast<uint2*>(xq + row * K);
     if (row >= M) {                            // padded rows: zero codes, zero scale
 #pragma unroll
         for (int i = 0; i < MAXV; ++i) {
-            const int v = i * 32 + lane;
+            const int v = (i * WPR + part) * 32 + lane;
             if (v < nv) {
                 qrow[v] = make_uint2(0, 0);
                 if (NORM && xn) reinterpret_cast<uint4*>(xn + row * K)[v] = make_uint4(0, 0, 0, 0);
             }
         }
-        if (lane == 0) xs[row] = 0.0f;
+        if (lane == 0 && part == 0) xs[row] = 0.0f;
         return;
     }
     const uint4* x4 = reinterpret_cast<const uint4*>(x);
     uint4 raw[MAXV];
 #pragma unroll
     for (int i = 0; i < MAXV; ++i) {
-        const int v = i * 32 + lane;
+        const int v = (i * WPR + part) * 32 + lane;
         raw[i] = v < nv ? x4[sg.index(row, v)] : make_uint4(0, 0, 0, 0);
     }
     float inv = 1.0f;
@@ -232,12 +238,19 @@ __global__ void __launch_bounds__(256) row_quant_warp_kernel(const uint16_t* __r
         }
         double ss = (s4[0] + s4[1]) + (s4[2] + s4[3]);
         ss = warp_sum(ss);
+        if (WPR > 1) {
+            if (lane == 0) s_ss[warp] = ss;
+            asm volatile("bar.sync %0, %1;" ::"r"(1 + rin), "n"(32 * WPR) : "memory");
+            ss = 0.0;
+#pragma unroll
+            for (int p = 0; p < WPR; ++p) ss += s_ss[rin * WPR + p];
+        }
         inv = rms_inverse(ss, K, eps);
     }
     float amax = 0.0f;
 #pragma unroll
     for (int i = 0; i < MAXV; ++i) {
-        const int v = i * 32 + lane;
+        const int v = (i * WPR + part) * 32 + lane;
         float f[8];
         unpack8(raw[i], f);
         if (NORM && v < nv) {
@@ -249,18 +262,25 @@ __global__ void __launch_bounds__(256) row_quant_warp_kernel(const uint16_t* __r
         for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
     }
     amax = warp_max(amax);
+    if (WPR > 1) {
+        if (lane == 0) s_am[warp] = amax;
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + rin), "n"(32 * WPR) : "memory");
+        amax = 0.0f;
+#pragma unroll
+        for (int p = 0; p < WPR; ++p) amax = fmaxf(amax, s_am[rin * WPR + p]);
+    }
     float s, qi;
     quant_scale(amax, s, qi);
 #pragma unroll
     for (int i = 0; i < MAXV; ++i) {
-        const int v = i * 32 + lane;
+        const int v = (i * WPR + part) * 32 + lane;
         if (v < nv) {
             float f[8];
             unpack8(raw[i], f);
             qrow[v] = make_uint2(quant4(f[0], f[1], f[2], f[3], qi), quant4(f[4], f[5], f[6], f[7], qi));
         }
     }
-    if (lane == 0) xs[row] = s;
+    if (lane == 0 && part == 0) xs[row] = s;
 }
 
 // CTA-per-row variant for wider rows (K <= 2048 * MAXV): each thread keeps MAXV 16-byte vectors of the row in registers.
@@ -348,11 +368,17 @@ static bool launch_row_quant_warp(const uint16_t* x, const uint16_t* nw, float e
     // (measured: at 2048+ rows the warp-per-row kernels are as fast or faster: 8.2 vs 8.6 us RMSNorm+INT8 at 2048 x 2048,
     // 16 vs 42 us act-quant at 32768 x 1024)
     constexpr int64_t block_rows = 32;
+    // a few thousand rows of 1024 - 2048 elements: several warps per row.  Measured inside the dense step at M = 2048 (the
+    // kernel alone, launched back to back, prefers one warp per row): RMSNorm + INT8 with 4 warps per row 3.754 -> 3.705 ms per
+    // step, act-quant with 2 warps per row a further 0.008 ms.
+    const int wpr = (Mp <= 4096 && K > 1024 && K <= 2048) ? (NORM ? 4 : 2) : 1;
     if (Mp <= block_rows && K <= 2048) launch_pdl(row_quant_block_kernel<1, NORM>, dim3((unsigned)Mp), dim3(256), 0, st, x, nw, eps, M, (int)K, sg, xq, xs, xn);
     else if (Mp <= block_rows && K <= 2048 * 4) launch_pdl(row_quant_block_kernel<4, NORM>, dim3((unsigned)Mp), dim3(256), 0, st, x, nw, eps, M, (int)K, sg, xq, xs, xn);
-    else if (K <= 256 * 4) launch_pdl(row_quant_warp_kernel<4, NORM>, dim3(grid), dim3(256), 0, st, x, nw, eps, M, Mp, (int)K, sg, xq, xs, xn);
-    else if (K <= 256 * 8) launch_pdl(row_quant_warp_kernel<8, NORM>, dim3(grid), dim3(256), 0, st, x, nw, eps, M, Mp, (int)K, sg, xq, xs, xn);
-    else if (K <= 256 * 16) launch_pdl(row_quant_warp_kernel<16, NORM>, dim3(grid), dim3(256), 0, st, x, nw, eps, M, Mp, (int)K, sg, xq, xs, xn);
+    else if (wpr == 2 && K <= 256 * 8) launch_pdl(row_quant_warp_kernel<4, NORM, 2>, dim3((unsigned)((Mp + 3) / 4)), dim3(256), 0, st, x, nw, eps, M, Mp, (int)K, sg, xq, xs, xn);
+    else if (wpr == 4 && K <= 256 * 8) launch_pdl(row_quant_warp_kernel<2, NORM, 4>, dim3((unsigned)((Mp + 1) / 2)), dim3(256), 0, st, x, nw, eps, M, Mp, (int)K, sg, xq, xs, xn);
+    else if (K <= 256 * 4) launch_pdl(row_quant_warp_kernel<4, NORM, 1>, dim3(grid), dim3(256), 0, st, x, nw, eps, M, Mp, (int)K, sg, xq, xs, xn);
+    else if (K <= 256 * 8) launch_pdl(row_quant_warp_kernel<8, NORM, 1>, dim3(grid), dim3(256), 0, st, x, nw, eps, M, Mp, (int)K, sg, xq, xs, xn);
+    else if (K <= 256 * 16) launch_pdl(row_quant_warp_kernel<16, NORM, 1>, dim3(grid), dim3(256), 0, st, x, nw, eps, M, Mp, (int)K, sg, xq, xs, xn);
     else if (K <= 2048 * 4) launch_pdl(row_quant_block_kernel<4, NORM>, dim3((unsigned)Mp), dim3(256), 0, st, x, nw, eps, M, (int)K, sg, xq, xs, xn);
     else return false;
     return true;
