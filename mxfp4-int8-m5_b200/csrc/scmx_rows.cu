@@ -371,9 +371,7 @@ static bool launch_row_quant_warp(const uint16_t* x, const uint16_t* nw, float e
     // a few thousand rows of 1024 - 2048 elements: several warps per row.  Measured inside the dense step at M = 2048 (the
     // kernel alone, launched back to back, prefers one warp per row): RMSNorm + INT8 with 4 warps per row 3.754 -> 3.705 ms per
     // step, act-quant with 2 warps per row a further 0.008 ms.
-    int wpr = (Mp <= 4096 && K > 1024 && K <= 2048) ? (NORM ? 4 : 2) : 1;
-    if (wpr > 1) { const char* e = getenv(NORM ? "SCMX_WPR_NORM" : "SCMX_WPR_ACT"); if (e) wpr = atoi(e); }
-    if (wpr == 8 && K <= 256 * 8) { launch_pdl(row_quant_warp_kernel<1, NORM, 8>, dim3((unsigned)Mp), dim3(256), 0, st, x, nw, eps, M, Mp, (int)K, sg, xq, xs, xn); return true; }
+    const int wpr = (Mp <= 4096 && K > 1024 && K <= 2048) ? (NORM ? 4 : 2) : 1;     // 8 / 4 warps per row measured slower: 3.70 - 3.73 ms
     if (Mp <= block_rows && K <= 2048) launch_pdl(row_quant_block_kernel<1, NORM>, dim3((unsigned)Mp), dim3(256), 0, st, x, nw, eps, M, (int)K, sg, xq, xs, xn);
     else if (Mp <= block_rows && K <= 2048 * 4) launch_pdl(row_quant_block_kernel<4, NORM>, dim3((unsigned)Mp), dim3(256), 0, st, x, nw, eps, M, (int)K, sg, xq, xs, xn);
     else if (wpr == 2 && K <= 256 * 8) launch_pdl(row_quant_warp_kernel<4, NORM, 2>, dim3((unsigned)((Mp + 3) / 4)), dim3(256), 0, st, x, nw, eps, M, Mp, (int)K, sg, xq, xs, xn);
