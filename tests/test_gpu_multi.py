@@ -216,6 +216,13 @@ def test_dense_stack_overlap_equals_serial(scmx):
     torch.cuda.synchronize()
     scmx._lib.check_status()
     assert torch.equal(a, b) and torch.equal(a, c)
+    # the ring may also join the decode stream once per 2 or 4 weights (a layer) instead of before every GEMM
+    for group in (2, 4):
+        for overlap in (True, False):
+            d = scmx.fused_dense.DenseStack(layers, M, hidden, overlap=overlap, ring_group=group).step(h, o)
+            torch.cuda.synchronize()
+            assert torch.equal(a, d), (group, overlap)
+    scmx._lib.check_status()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
