@@ -472,11 +472,13 @@ def gemv_bytes_fmt(n, k, block, bc_bits):
     return n * k // 2 + n * k * bc_bits // (8 * block) + 4 * n + k + 4 + 2 * n
 
 
-def bench_moe(pkg, torch, dist=None, reps=5, weak=False, blk=None):
+def bench_moe(pkg, torch, dist=None, reps=5, weak=False, blk=None, tokens=None):
     """OLMoE-shaped MoE half-block at 4096 tokens: quant -> route -> (dispatch) -> two grouped GEMMs -> (return) -> combine.
     With a process group: experts sharded by rank, tokens split by rank, dispatch and return over NVLink.
     weak: 4096 tokens PER RANK instead of in total."""
     c = dict(OLMOE)
+    if tokens:
+        c["tokens"] = tokens
     world = dist.get_world_size() if dist is not None else 1
     rank = dist.get_rank() if dist is not None else 0
     if weak:
@@ -1095,6 +1097,8 @@ def run_case(args):
     elif args.case == "models":
         print(json.dumps(dict(case="models", models=bench_models(pkg, torch))))
         return
+    elif args.case == "moe512":   # the half-block at 512 tokens: 64 rows per expert, the grouped GEMMs read the packed weights
+        bench_moe(pkg, torch, None, reps=1, tokens=512)
     else:
         bench_moe(pkg, torch, None, reps=1)
     torch.cuda.synchronize()
@@ -1113,7 +1117,7 @@ def main():
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic stream serialization")
     ap.add_argument("--dense-only", action="store_true", help="skip the roofline / decode / MoE / CPU sections")
     ap.add_argument("--workload", default="all", choices=["all", "moe5"], help="moe5: only the large-MoE stress section")
-    ap.add_argument("--case", choices=["gemm", "gemmw4", "rows", "gemv", "gemvbig", "gemvlist", "moe", "ep1", "models", "decodestep", "decodechain"], help="run one small kernel case (for profiler captures) and exit")
+    ap.add_argument("--case", choices=["gemm", "gemmw4", "rows", "gemv", "gemvbig", "gemvlist", "moe", "moe512", "ep1", "models", "decodestep", "decodechain"], help="run one small kernel case (for profiler captures) and exit")
     args = ap.parse_args()
     if args.case:
         run_case(args)
