@@ -31,20 +31,29 @@ constexpr int W4_UNPACK_WARPS = 8;
 constexpr int W4_THREADS = CTA_THREADS + 32 * W4_UNPACK_WARPS;      // 576
 constexpr int W4_MAX_E = 512;                                       // pair-tile table in shared memory
 
-struct W4Smem {
-    static constexpr int A_BYTES = BM * BK;                 // 16 KB
-    static constexpr int B_BYTES = (W4_BN / 2) * BK;        // 16 KB of INT8, written by the unpack warps
-    static constexpr int P_BYTES = (W4_BN / 2) * (BK / 2);  // 8 KB of packed codes
+// MT = row tiles (of 256 rows per CTA pair) that share one expanded weight tile.  MT = 1: 256 x 256 output tiles.  MT = 2:
+// "super tiles" of 512 rows x 128 columns: every expanded K block of 128 weight rows feeds the MMAs of two row tiles, so the
+// expansion per MMA halves; the two accumulators of a super tile sit side by side in tensor memory (2 x 128 columns) and the
+// second row tile is skipped where a segment ends inside the first.
+template <int MT>
+struct W4SmemT {
+    static constexpr int BN = W4_BN / MT;                   // output columns of a tile
+    static constexpr int BH = BN / 2;                       // weight rows expanded by one CTA
+    static constexpr int A_TILE = BM * BK;                  // 16 KB per row tile
+    static constexpr int A_BYTES = MT * A_TILE;
+    static constexpr int B_BYTES = BH * BK;                 // INT8, written by the unpack warps
+    static constexpr int P_BYTES = BH * (BK / 2);           // packed codes
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + P_BYTES;
     static constexpr int BAR_OFF = W4_STAGES * STAGE_BYTES;                 // loaded[S], full[S], empty[S], tfull[2], tempty[2]
     static constexpr int MISC_OFF = BAR_OFF + 8 * (3 * W4_STAGES + 4);
     static constexpr int WS_OFF = MISC_OFF + 16;
     static constexpr int EPI_OFF = WS_OFF + 2 * W4_BN * 4;
-    static constexpr int PT_OFF = EPI_OFF + EPI_STAGE_BYTES;               // pair-tile starts per expert [W4_MAX_E + 1]
+    static constexpr int PT_OFF = EPI_OFF + EPI_STAGE_BYTES;               // tile starts per expert [W4_MAX_E + 1]
     static constexpr int SIG_OFF = PT_OFF + 4 * (W4_MAX_E + 4);             // 16-byte aligned: 8 x 16 B signal source, 8 x 16 B sink
     static constexpr int TOTAL = SIG_OFF + 256 + 1024;
 };
-static_assert(W4Smem::TOTAL <= 232448, "shared memory of the packed-weight GEMM exceeds 227 KB");
+static_assert(W4SmemT<1>::TOTAL <= 232448 && W4SmemT<2>::TOTAL <= 232448, "shared memory of the packed-weight GEMM exceeds 227 KB");
+static_assert(W4SmemT<1>::STAGE_BYTES % 1024 == 0 && W4SmemT<2>::STAGE_BYTES % 1024 == 0, "stages must keep the swizzle alignment");
 
 struct W4Args {
     GemmArgs g;                   // M / R, N, K, epilogue, scales, output, expert segments (off; tstart unused), status
@@ -55,7 +64,8 @@ struct W4Args {
 };
 
 struct W4Tile {
-    int row0;        // first A row of this CTA
+    int nm;          // row tiles of this (super) tile that hold rows: 1 .. MT
+    int row0;        // first A row of this CTA (row tile 0; row tile m starts 256 m rows further)
     int row_end;     // rows >= row_end are not stored
     int n0;          // first output column of the tile
     int wbase;       // index of the tile's first weight row (expert * N + n0): wscale, packed rows and block codes
@@ -70,11 +80,12 @@ __device__ __forceinline__ void decode_word_pq(uint32_t w, uint32_t mlo, uint32_
     o1 = ((p1 | H) - q1) ^ H;
 }
 
-template <bool POW2>
+template <bool POW2, int MT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(W4_THREADS, 1)
     gemm_w4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmP, const W4Args wa) {
-    using L = W4Smem;
-    constexpr int STAGES = W4_STAGES, BN = W4_BN;
+    using L = W4SmemT<MT>;
+    constexpr int STAGES = W4_STAGES, BN = L::BN, BH = L::BH;
+    constexpr int SUPER = MT * 2 * BM;                      // rows of a (super) tile
     const GemmArgs& a = wa.g;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -85,7 +96,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(W4_THREADS, 1)
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::MISC_OFF + 4);
     float* ws_stage = reinterpret_cast<float*>(smem + L::WS_OFF);
     int* ptile = reinterpret_cast<int*>(smem + L::PT_OFF);            // grouped: pair-tile start of every expert
-    constexpr uint32_t TMEM_COLS = 2 * BN;
+    constexpr uint32_t ACC_COLS = MT * BN;                  // 256 either way: two accumulator sets fill tensor memory
+    constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
@@ -121,13 +133,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(W4_THREADS, 1)
     const int tiles_n = (a.N + BN - 1) / BN;
     int tiles_m;
     if (a.E == 0) {
-        tiles_m = (a.M + 2 * BM - 1) / (2 * BM);
+        tiles_m = (a.M + SUPER - 1) / SUPER;
     } else {
         if (warp == 2) {
             int run = 0;
             for (int b0 = 0; b0 < a.E; b0 += 32) {
                 const int e = b0 + lane;
-                const int c = e < a.E ? (a.off[e + 1] - a.off[e] + 2 * BM - 1) / (2 * BM) : 0;
+                const int c = e < a.E ? (a.off[e + 1] - a.off[e] + SUPER - 1) / SUPER : 0;
                 int sc = c;
 #pragma unroll
                 for (int d = 1; d < 32; d <<= 1) {
@@ -154,8 +166,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(W4_THREADS, 1)
         const int gm = min(gm_full, tiles_m - band * gm_full);
         const int nt = r / gm, mt = band * gm_full + r - nt * gm;
         tl.n0 = nt * BN;
+        int base;                                 // first row of the (super) tile
         if (a.E == 0) {
-            tl.row0 = mt * 2 * BM + (int)rank * BM;
+            base = mt * SUPER;
             tl.row_end = a.M;
             tl.wbase = tl.n0;
         } else {
@@ -164,10 +177,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(W4_THREADS, 1)
                 const int mid = (lo + hi) >> 1;
                 if (ptile[mid] <= mt) lo = mid; else hi = mid;
             }
-            tl.row0 = a.off[lo] + (mt - ptile[lo]) * 2 * BM + (int)rank * BM;
+            base = a.off[lo] + (mt - ptile[lo]) * SUPER;
             tl.row_end = a.off[lo + 1];
             tl.wbase = lo * a.N + tl.n0;
         }
+        tl.row0 = base + (int)rank * BM;
+        tl.nm = (MT == 2 && base + 2 * BM < tl.row_end) ? 2 : 1;
         return tl;
     };
     const uint32_t full_leader = mapa_u32(bar_full, 0), tempty_leader = mapa_u32(bar_tempty, 0);
@@ -180,12 +195,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(W4_THREADS, 1)
             uint32_t phase = 0;
             for (int t = pair; t < total && fail == 0; t += npairs) {
                 const W4Tile tl = get_tile(t);
-                const int prow = tl.wbase + (int)rank * (BN / 2);
+                const int prow = tl.wbase + (int)rank * BH;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (int w = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, a.wait_ns)) { fail = w == 1 ? 1 : -1; break; }
                     const uint32_t sa = sbase + stage * L::STAGE_BYTES, sp = sa + L::A_BYTES + L::B_BYTES;
-                    mbar_expect_tx(bar_loaded + 8 * stage, L::A_BYTES + L::P_BYTES);
+                    mbar_expect_tx(bar_loaded + 8 * stage, tl.nm * L::A_TILE + L::P_BYTES);
                     tma_load_2d(sa, &tmA, kb * BK, tl.row0, bar_loaded + 8 * stage);
+                    if (MT == 2 && tl.nm == 2) tma_load_2d(sa + L::A_TILE, &tmA, kb * BK, tl.row0 + 2 * BM, bar_loaded + 8 * stage);
                     tma_load_2d(sp, &tmP, kb * (BK / 2), prow, bar_loaded + 8 * stage);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -198,18 +214,25 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(W4_THREADS, 1)
             int stage = 0;
             uint32_t phase = 0, acc = 0, acc_phase = 0;
             for (int t = pair; t < total && fail == 0; t += npairs) {
+                const int nm = MT == 2 ? get_tile(t).nm : 1;
                 if (int w = mbar_wait_cluster(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, a.wait_ns)) { fail = w == 1 ? 2 : -1; break; }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * BN;
+                const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (int w = mbar_wait_cluster(bar_full + 8 * stage, phase, abort_flag, a.wait_ns)) { fail = w == 1 ? 3 : -1; break; }
                     tc_fence_after();
                     const uint32_t sa = sbase + stage * L::STAGE_BYTES, sb = sa + L::A_BYTES;
-                    const uint64_t da = umma_desc(sa), db = umma_desc(sb);
+                    const uint64_t db = umma_desc(sb);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k)
-                        umma_i8_pair(d_tmem, da + (uint64_t)(k * (UMMA_K >> 4)), db + (uint64_t)(k * (UMMA_K >> 4)), idesc,
-                                     (kb | k) != 0 ? 1u : 0u);
+                    for (int m = 0; m < MT; ++m) {
+                        if (m < nm) {                       // the row tiles of a super tile share the expanded weight tile
+                            const uint64_t da = umma_desc(sa + m * L::A_TILE);
+#pragma unroll
+                            for (int k = 0; k < BK / UMMA_K; ++k)
+                                umma_i8_pair(d_tmem + m * BN, da + (uint64_t)(k * (UMMA_K >> 4)), db + (uint64_t)(k * (UMMA_K >> 4)), idesc,
+                                             (kb | k) != 0 ? 1u : 0u);
+                        }
+                    }
                     umma_commit_pair(bar_empty + 8 * stage);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -227,20 +250,24 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(W4_THREADS, 1)
         uint32_t acc = 0, acc_phase = 0;
         for (int t = pair; t < total && fail == 0; t += npairs) {
             const W4Tile tl = get_tile(t);
-            float* ws = ws_stage + acc * BN;
+            float* ws = ws_stage + acc * W4_BN;
             if (a.epi != 0) {
                 for (int i = et; i < BN; i += EPI_THREADS) ws[i] = (tl.n0 + i < a.N) ? a.wscale[tl.wbase + i] : 0.0f;
             }
-            const int wrow0 = tl.row0 + 32 * q;
+            // a warp converts 128 accumulator columns of 32 rows: MT = 1: column half `chalf` of the tile's rows; MT = 2: all 128
+            // columns of row tile `chalf`.  Either way they are columns chalf * 128 .. + 127 of the accumulator set.
+            const int mtile = MT == 2 ? chalf : 0, coff = MT == 2 ? 0 : chalf * 128;
+            const int wrow0 = tl.row0 + mtile * 2 * BM + 32 * q;
             const float xs = (a.epi != 0 && wrow0 + lane < tl.row_end) ? a.xscale[wrow0 + lane] : 0.0f;
             uint4 rp[8];
-            if (a.epi == 2) epi_load_res(a, rp, lane, wrow0, tl.row_end, tl.n0 + chalf * (BN / 2));
+            if (a.epi == 2 && mtile < tl.nm) epi_load_res(a, rp, lane, wrow0, tl.row_end, tl.n0 + coff);
             if (int w = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, a.wait_ns)) fail = w == 1 ? 4 : -1;
             epilogue_bar();
             if (*abort_flag) { if (!fail) fail = -1; break; }
             tc_fence_after();
-            epilogue_warp<BN, false>(a, tmem_base + acc * BN + chalf * (BN / 2) + ((uint32_t)(32 * q) << 16), ws + chalf * (BN / 2), wrow0,
-                              tl.row_end, tl.n0 + chalf * (BN / 2), smem + L::EPI_OFF + (warp - 2) * EPI_STAGE_WARP, lane, xs, rp);
+            if (mtile < tl.nm)
+                epilogue_warp<256, false>(a, tmem_base + acc * ACC_COLS + chalf * 128 + ((uint32_t)(32 * q) << 16), ws + coff, wrow0,
+                                          tl.row_end, tl.n0 + coff, smem + L::EPI_OFF + (warp - 2) * EPI_STAGE_WARP, lane, xs, rp);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -253,7 +280,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(W4_THREADS, 1)
     } else {
         // ------------------------------------------------ unpack warps: thread (r, h) expands half h (64 weights) of weight row r
         const int ut = threadIdx.x - (64 + EPI_THREADS);            // 0..255
-        const int r = ut & 127, h = ut >> 7, uw = ut >> 5;          // uw: unpack warp 0..7
+        constexpr int CPT = 4 * BH / 256;                           // 16-byte chunks of a packed row per thread: 2 (MT = 1) or 1
+        const int r = ut % BH, h = ut / BH, uw = ut >> 5;           // weight row, part of its K block; uw: unpack warp 0..7
         const int fb = wa.field_bits;
         const uint32_t psw = (uint32_t)((r >> 1) & 3), bsw = (uint32_t)(r & 7);
         const bool big_block = wa.f.block_shift >= 5;               // one block code covers (at least) a whole 16-byte chunk
@@ -264,9 +292,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(W4_THREADS, 1)
         uint32_t phase = 0;
         for (int t = pair; t < total && fail == 0; t += npairs) {
             const W4Tile tl = get_tile(t);
-            const int ncol = tl.n0 + (int)rank * (BN / 2) + r;           // output column = weight row inside the matrix / expert
+            const int ncol = tl.n0 + (int)rank * BH + r;                 // output column = weight row inside the matrix / expert
             const bool valid = ncol < a.N;
-            const uint8_t* bcrow = wa.bcodes + (size_t)(tl.wbase + (int)rank * (BN / 2) + r) * wa.bc_row;
+            const uint8_t* bcrow = wa.bcodes + (size_t)(tl.wbase + (int)rank * BH + r) * wa.bc_row;
             uint32_t field_next = 0;
             if (valid) field_next = fb == 8 ? bcrow[0] : fb == 16 ? *reinterpret_cast<const uint16_t*>(bcrow) : *reinterpret_cast<const uint32_t*>(bcrow);
             for (int kb = 0; kb < num_kb; ++kb) {
@@ -284,8 +312,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(W4_THREADS, 1)
                 const uint8_t* prow = st + L::A_BYTES + L::B_BYTES + r * 64;
                 uint8_t* brow = st + L::A_BYTES + r * 128;
 #pragma unroll
-                for (int cc = 0; cc < 2; ++cc) {
-                    const int c = 2 * h + cc;                                  // 16-byte chunk of the packed row: weights 32c .. 32c+31
+                for (int cc = 0; cc < CPT; ++cc) {
+                    const int c = CPT * h + cc;                                // 16-byte chunk of the packed row: weights 32c .. 32c+31
                     uint4 pv = *reinterpret_cast<const uint4*>(prow + ((c ^ psw) << 4));
                     if (!valid) pv = make_uint4(0, 0, 0, 0);
                     const uint32_t ww[4] = {pv.x, pv.y, pv.z, pv.w};
@@ -360,26 +388,39 @@ static int run_w4(const int8_t* xq, int64_t a_rows, const uint32_t* codes, const
         if (rc3) return rc3;
     }
     wa.g = g;
+    // Super tiles (two row tiles per expanded weight tile) where a segment usually has more than one row tile: a dense problem
+    // of more than 256 rows, experts with more than 256 rows on average.
+    const bool super = g.E == 0 ? g.M > 2 * BM : (int64_t)g.M > (int64_t)g.E * 2 * BM;
+    const int bn = super ? W4SmemT<2>::BN : W4SmemT<1>::BN;
     CUtensorMap tmA, tmP;
     int rc = make_map_u8(&tmA, xq, a_rows, g.K, BK, BM, 128);
     if (rc) return rc;
-    rc = make_map_u8(&tmP, codes, rows_w, g.K / 2, BK / 2, W4_BN / 2, 64);
+    rc = make_map_u8(&tmP, codes, rows_w, g.K / 2, BK / 2, bn / 2, 64);
     if (rc) return rc;
     int pairs = sm_count() / 2;
     if (g.E == 0) {
-        const int64_t tiles = ((g.M + 2 * BM - 1) / (2 * BM)) * (int64_t)((g.N + W4_BN - 1) / W4_BN);
+        const int rows_tile = super ? 4 * BM : 2 * BM;
+        const int64_t tiles = ((g.M + rows_tile - 1) / rows_tile) * (int64_t)((g.N + bn - 1) / bn);
         if (tiles < pairs) pairs = (int)tiles;
     }
     static bool configured[64] = {};
     const int dev = current_device();
     SCMX_REQUIRE(dev >= 0, SCMX_ECUDA, "no current CUDA device (ordinal 0..63)");
     if (!configured[dev]) {
-        SCMX_CUDA_OK(cudaFuncSetAttribute(gemm_w4_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, W4Smem::TOTAL));
-        SCMX_CUDA_OK(cudaFuncSetAttribute(gemm_w4_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, W4Smem::TOTAL));
+        SCMX_CUDA_OK(cudaFuncSetAttribute(gemm_w4_pair_kernel<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, W4SmemT<1>::TOTAL));
+        SCMX_CUDA_OK(cudaFuncSetAttribute(gemm_w4_pair_kernel<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, W4SmemT<1>::TOTAL));
+        SCMX_CUDA_OK(cudaFuncSetAttribute(gemm_w4_pair_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, W4SmemT<2>::TOTAL));
+        SCMX_CUDA_OK(cudaFuncSetAttribute(gemm_w4_pair_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, W4SmemT<2>::TOTAL));
         configured[dev] = true;
     }
-    cudaError_t e = f.pow2 ? launch_pdl(gemm_w4_pair_kernel<true>, dim3(2 * pairs), dim3(W4_THREADS), (size_t)W4Smem::TOTAL, st, tmA, tmP, wa)
-                           : launch_pdl(gemm_w4_pair_kernel<false>, dim3(2 * pairs), dim3(W4_THREADS), (size_t)W4Smem::TOTAL, st, tmA, tmP, wa);
+    const dim3 grid(2 * pairs), block(W4_THREADS);
+    cudaError_t e;
+    if (super)
+        e = f.pow2 ? launch_pdl(gemm_w4_pair_kernel<true, 2>, grid, block, (size_t)W4SmemT<2>::TOTAL, st, tmA, tmP, wa)
+                   : launch_pdl(gemm_w4_pair_kernel<false, 2>, grid, block, (size_t)W4SmemT<2>::TOTAL, st, tmA, tmP, wa);
+    else
+        e = f.pow2 ? launch_pdl(gemm_w4_pair_kernel<true, 1>, grid, block, (size_t)W4SmemT<1>::TOTAL, st, tmA, tmP, wa)
+                   : launch_pdl(gemm_w4_pair_kernel<false, 1>, grid, block, (size_t)W4SmemT<1>::TOTAL, st, tmA, tmP, wa);
     SCMX_PDL_OK("gemm_w4_pair_kernel", e);
     return SCMX_OK;
 }
