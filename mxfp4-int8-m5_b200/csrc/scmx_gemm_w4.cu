@@ -16,10 +16,15 @@
 // awaited by its unpack warps), full (lives in the leader: its 8 unpack warps arrive after their stores and a proxy fence,
 // the peer's 8 warps each send a 16-byte asynchronous copy that completes on it; awaited by the MMA thread), empty (both
 // CTAs, signalled by the leader's tcgen05.commit).  All waits are bounded.
-// Measured on B200: the expansion (4 byte permutes per 8 weights on the quarter-rate permute pipe, ~1500 cycles per K block
-// per unpack warp against 512 cycles of MMA) bounds this kernel; it wins where an expert sees few rows (the decoded weights
-// would be used once) and loses to decode-then-GEMM where every decoded tile is reused by many row tiles, which is the
-// reference's own rule for choosing between its two forms (e2e/fused_olmoe.py:205).
+// Where a row segment spans more than one row tile the kernel works on "super tiles" (MT = 2): 512 rows x 128 columns, the two
+// row tiles sharing every expanded weight tile (half the expansion per MMA; the thread layout becomes weight row x quarter of
+// a K block and a stage holds two activation tiles).
+// Measured on B200 (gate|up 2048 x 12288 x 2048): 1600 cycles per K block with 256 x 256 tiles, 1277 with super tiles, against
+// 512 cycles of MMA and ~660 of the INT8 kernel; halving the expansion work removed only a fifth, and neither a second block in
+// flight per unpack warp group nor separate rings for activations / packed codes / expanded tiles shortened it (both
+// measured: equal and slower).  The kernel wins where an expert sees few rows (the decoded weights would be used once) and
+// loses to decode-then-GEMM where every decoded tile is reused by many row tiles, which is the reference's own rule for
+// choosing between its two forms (e2e/fused_olmoe.py:205).
 #include "scmx_gemm_core.cuh"
 #include "scmx_gemv_core.cuh"
 
