@@ -5,7 +5,7 @@
 //
 // A pair of CTAs shares a 256 x 256 output tile; per 128-wide K block each CTA needs ITS 128 rows of A (16 KB INT8 by TMA)
 // and ITS 128 of the tile's 256 weight rows, which arrive as 8 KB of packed codes (TMA, 64-byte swizzle so that a thread can
-// read "its" weight row without bank conflicts) and are expanded by four unpack warps, one thread per weight row:
+// read "its" weight row without bank conflicts) and are expanded by eight unpack warps, two threads per weight row:
 //     packed row (64 B) -> 16 code words -> byte-permute lookups of the magnitudes of positive and of negative codes
 //     (the sign bit of a code switches the permute to "replicate the top bit of the selected byte", i.e. to zero) ->
 //     signed bytes = ((P | 0x80..) - Q) ^ 0x80.. -> 128 B of INT8 written into the 128-byte-swizzled operand stage

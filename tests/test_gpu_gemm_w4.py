@@ -48,13 +48,15 @@ def test_dense_from_packed_exact(scmx, oracle, M, N, K, fmt_kw):
         S.set_format(F.Format())
 
 
+@pytest.mark.parametrize("R", [1500, 3300])
 @pytest.mark.parametrize("fmt_kw", [dict(), dict(block=16)])
-def test_grouped_from_packed_exact(scmx, oracle, fmt_kw):
+def test_grouped_from_packed_exact(scmx, oracle, fmt_kw, R):
     """Eight experts, two of them empty, segment ends inside tiles (e2e/sc_moe.py:209-244), all epilogues, against the oracle
-    and against the scratch-based form."""
+    and against the scratch-based form.  R = 1500: tiles of 256 rows; R = 3300 (more than 256 rows per expert on average):
+    super tiles of 512 rows whose second row tile is skipped where a segment ends inside the first."""
     S, M_, F = scmx.sc_kernels, scmx.sc_moe, scmx.sc_format
     rng = np.random.default_rng(3)
-    E, N, K, R = 8, 512, 1024, 1500
+    E, N, K = 8, 512, 1024
     packs = [_pack(scmx, oracle, rng, N, K, fmt_kw) for _ in range(E)]
     fmt = packs[0][0]
     ex = rng.integers(0, E, R)
