@@ -997,6 +997,39 @@ def run_case(args):
         xs = torch.full((2048,), 1e-2, device="cuda")
         for _ in range(4):
             S.mm_w4_epi(xq, c, b, xs, ws, 12288, 3)
+    elif args.case == "gemmlib":  # this repository's INT8 GEMM beside the library's (torch._int_mm = cuBLASLt) on the same operands
+        def per_launch(fn, n):
+            for _ in range(3):
+                fn()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                for _ in range(n):
+                    fn()
+            for _ in range(2):
+                gr.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(5):
+                gr.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / 5 / n * 1e3
+        rows = []
+        for (M, N, K) in [(2048, 4096, 2048), (2048, 2048, 2048), (2048, 12288, 2048), (2048, 2048, 6144), (8192, 8192, 8192)]:
+            xq = torch.randint(-127, 128, (M, K), dtype=torch.int8, device="cuda", generator=g)
+            wq = torch.randint(-96, 97, (N, K), dtype=torch.int8, device="cuda", generator=g)
+            xs = torch.rand(M, device="cuda", generator=g) * 1e-3
+            ws = torch.rand(N, device="cuda", generator=g) * 1e-3
+            wt = wq.t()
+            n = 4 if M >= 4096 else 10
+            same = bool(torch.equal(S.mm_i8_i32(xq, wq)[:M], torch._int_mm(xq, wt)))
+            ops = 2 * M * N * K
+            t = dict(int32=per_launch(lambda: S.mm_i8_i32(xq, wq), n), bf16_epilogue=per_launch(lambda: S.mm_epi(xq, wq, xs, ws, 1), n),
+                     library_int32=per_launch(lambda: torch._int_mm(xq, wt), n))
+            rows.append(dict(shape=[M, N, K], equal_int32=same, us=t, tops={k: ops / v / 1e6 for k, v in t.items()}))
+        print(json.dumps(dict(case="gemmlib", rows=rows)))
+        return
     elif args.case == "rows":     # the row kernels between the GEMMs of a dense layer at M = 2048: RMSNorm + INT8 and act-quant
         h = torch.randn((2048, 2048), generator=g, device="cuda").to(torch.bfloat16)
         act = torch.randn((2048, 6144), generator=g, device="cuda").to(torch.bfloat16)
@@ -1117,7 +1150,7 @@ def main():
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic stream serialization")
     ap.add_argument("--dense-only", action="store_true", help="skip the roofline / decode / MoE / CPU sections")
     ap.add_argument("--workload", default="all", choices=["all", "moe5"], help="moe5: only the large-MoE stress section")
-    ap.add_argument("--case", choices=["gemm", "gemmw4", "rows", "gemv", "gemvbig", "gemvlist", "moe", "moe512", "ep1", "models", "decodestep", "decodechain"], help="run one small kernel case (for profiler captures) and exit")
+    ap.add_argument("--case", choices=["gemm", "gemmw4", "gemmlib", "rows", "gemv", "gemvbig", "gemvlist", "moe", "moe512", "ep1", "models", "decodestep", "decodechain"], help="run one small kernel case (for profiler captures) and exit")
     args = ap.parse_args()
     if args.case:
         run_case(args)
