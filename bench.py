@@ -1016,7 +1016,7 @@ def run_case(args):
             torch.cuda.synchronize()
             return e0.elapsed_time(e1) / 5 / n * 1e3
         rows = []
-        for (M, N, K) in [(2048, 4096, 2048), (2048, 2048, 2048), (2048, 12288, 2048), (2048, 2048, 6144), (8192, 8192, 8192)]:
+        for (M, N, K) in [(2048, 4096, 2048), (2048, 2048, 2048), (2048, 12288, 2048), (2048, 2048, 6144), (8192, 8192, 8192), (4096, 14336, 4096)]:
             xq = torch.randint(-127, 128, (M, K), dtype=torch.int8, device="cuda", generator=g)
             wq = torch.randint(-96, 97, (N, K), dtype=torch.int8, device="cuda", generator=g)
             xs = torch.rand(M, device="cuda", generator=g) * 1e-3
