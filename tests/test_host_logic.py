@@ -127,3 +127,14 @@ def test_packed_weight_gemm_format_rule(scmx):
     assert not ok(F.Format(block=64), 2048)            # 4 bits per 128 weights
     assert ok(F.Format(block=8), 2048)                 # 16 blocks x 2 bits = 32 bits
     assert not ok(F.Format(block=8, mult=(1, 2, 3, 4, 5, 6, 8, 10), bc_bits=4), 2048)      # 64 bits
+
+
+def test_status_word_codes_have_texts(scmx):
+    """Every code a kernel can leave in the status word has a description that names the waiting party (what check_status()
+    raises with); unknown codes fall back to the number."""
+    L = scmx._lib
+    for code, word in ((1, "producer"), (2, "MMA"), (3, "MMA"), (4, "epilogue"), (6, "unpack"), (11, "GEMV"), (12, "GEMV"),
+                       (20, "peer barrier")):
+        assert word in L.describe_status(code), code
+    assert "grid barrier 3" in L.describe_status(103)
+    assert L.describe_status(77) == "code 77"
