@@ -31,7 +31,10 @@ class MoeBlock:
             self.dn8 = torch.empty((n_experts * D, F), dtype=torch.int8, device=dev)
             self.side = torch.cuda.Stream(device=dev)
 
-    FUSED_BELOW = 384      # measured on B200 (64 experts, 2048 x 1024): fused wins up to 256 rows per expert, ties at 512
+    # measured on B200 (64 experts, 2048 x 1024; half-block ms, packed-weight GEMMs / decode-then-GEMM): 128 rows per expert
+    # 0.190 / 0.275, 256: 0.286 / 0.330, 384: 0.356 / 0.394, 448: 0.367 / 0.419, 512: 0.478 / 0.449 (past 512 rows an expert
+    # needs a second super tile)
+    FUSED_BELOW = 480
 
     def _fused(self, R):
         return (not self.two_pass) and M_.FUSED_UNPACK and R // self.E < self.FUSED_BELOW
